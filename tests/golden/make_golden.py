@@ -1,0 +1,232 @@
+"""Generate the golden fixtures in this directory from the reference implementation itself.
+
+Run once in a container that has the reference checked out (default ``/root/reference``):
+
+    python tests/golden/make_golden.py [--reference /path/to/torch-harmonics] [--skip-large]
+
+The reference package's ``__init__`` imports compiled extensions that are not built there, so the
+SHT submodules (pure torch) are imported through synthetic package objects.  Inputs come from
+``oracle.sht_oracle.random_coeffs`` / numpy PCG64 so that the tests can regenerate them anywhere;
+only the reference's OUTPUTS (float64 path) are stored.
+"""
+
+import argparse
+import importlib
+import os
+import sys
+import types
+import warnings
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, ROOT)
+from oracle import sht_oracle as orc  # noqa: E402
+
+
+def import_reference(path):
+    for name, sub in (("torch_harmonics", "torch_harmonics"), ("torch_harmonics.distributed", "torch_harmonics/distributed")):
+        mod = types.ModuleType(name)
+        mod.__path__ = [os.path.join(path, sub)]
+        sys.modules[name] = mod
+    return importlib.import_module("torch_harmonics.sht")
+
+
+def t64(a):
+    return torch.from_numpy(np.ascontiguousarray(a))
+
+
+def tables(ref):
+    out = {}
+    for grid in ("equiangular", "legendre-gauss", "lobatto"):
+        for norm in ("ortho", "four-pi", "schmidt"):
+            for cs in (True, False):
+                key = f"{grid}|{norm}|{int(cs)}"
+                nlat, nlon, lmax = 12, 24, 9
+                out[key + "|w"] = ref.RealSHT(nlat, nlon, lmax=lmax, grid=grid, norm=norm, csphase=cs).weights.numpy()
+                out[key + "|p"] = ref.InverseRealSHT(nlat, nlon, lmax=lmax, grid=grid, norm=norm, csphase=cs).pct.numpy()
+                out[key + "|vw"] = ref.RealVectorSHT(nlat, nlon, lmax=lmax, grid=grid, norm=norm, csphase=cs).weights.numpy()
+                out[key + "|vp"] = ref.InverseRealVectorSHT(nlat, nlon, lmax=lmax, grid=grid, norm=norm, csphase=cs).dpct.numpy()
+    # default truncation + odd nlat
+    for grid in ("equiangular", "legendre-gauss", "lobatto"):
+        m = ref.RealSHT(33, 64, grid=grid)
+        out[f"default|{grid}|w"] = m.weights.numpy()
+        out[f"default|{grid}|lm"] = np.array([m.lmax, m.mmax])
+    np.savez_compressed(os.path.join(HERE, "tables.npz"), **out)
+
+
+def cfg1(ref):
+    """Equiangular 64x128, lmax=64, mmax=65 asked -> (64, 64); iid N(0,1) input, seed 0."""
+    rng = np.random.default_rng(0)
+    x = rng.standard_normal((4, 8, 64, 128))
+    sht = ref.RealSHT(64, 128, lmax=64, mmax=65, grid="equiangular", norm="ortho")
+    isht = ref.InverseRealSHT(64, 128, lmax=64, mmax=65, grid="equiangular", norm="ortho")
+    c = sht(t64(x))
+    rt = isht(c)
+    c32 = sht.float()(t64(x).float())
+    np.savez_compressed(
+        os.path.join(HERE, "cfg1_equiangular_64x128.npz"),
+        lm=np.array([sht.lmax, sht.mmax]),
+        coeffs=c.numpy()[:2, :2],
+        roundtrip=rt.numpy()[:2, :2],
+        coeffs_fp32_err=np.array(orc.max_normalised_error(c32.numpy(), c.numpy())),
+    )
+
+
+def cfg2(ref):
+    """Legendre-Gauss 256x512, lmax=256, mmax=257 asked -> (256, 256); band-limited, seed 1."""
+    a = orc.random_coeffs((2,), 256, 256, seed=1, power=1.0, offset=1.0)
+    sht = ref.RealSHT(256, 512, lmax=256, mmax=257, grid="legendre-gauss", norm="ortho")
+    isht = ref.InverseRealSHT(256, 512, lmax=256, mmax=257, grid="legendre-gauss", norm="ortho")
+    x = isht(t64(a))
+    c = sht(x)
+    np.savez_compressed(
+        os.path.join(HERE, "cfg2_legendre_gauss_256x512.npz"),
+        lm=np.array([sht.lmax, sht.mmax]),
+        field=x.numpy()[:1, ::4, :],
+        coeffs=c.numpy()[:1, ::4, :],
+    )
+
+
+ROWS_K = np.array([0, 1, 2, 179, 180, 359, 360, 361, 540, 718, 719, 720])
+ROWS_L = np.array([0, 1, 2, 3, 100, 101, 359, 360, 361, 600, 718, 719])
+
+
+def cfg3(ref):
+    """Equiangular 721x1440, lmax=mmax=720; spectrum (l(l+1)+25)^-2, seed 2; two fields."""
+    a = orc.random_coeffs((2,), 720, 720, seed=2, offset=25.0, zero_l0=True, mode="grf")
+    sht = ref.RealSHT(721, 1440, lmax=720, mmax=720, grid="equiangular", norm="ortho")
+    isht = ref.InverseRealSHT(721, 1440, lmax=720, mmax=720, grid="equiangular", norm="ortho")
+    x = isht(t64(a))
+    c = sht(x)
+    rt = isht(c)
+    x32 = x.float()
+    c32 = sht.float()(x32)
+    rt32 = isht.float()(c32)
+    np.savez_compressed(
+        os.path.join(HERE, "cfg3_equiangular_721x1440.npz"),
+        rows_k=ROWS_K,
+        rows_l=ROWS_L,
+        field_rows=x.numpy()[:, ROWS_K, :],
+        coeff_rows=c.numpy()[:, ROWS_L, :],
+        roundtrip_rows=rt.numpy()[:, ROWS_K, :],
+        field_absmax=np.array(float(x.abs().max())),
+        coeff_absmax=np.array(float(c.abs().max())),
+        ref_fp32_coeff_err=np.array(orc.max_normalised_error(c32.numpy(), c.numpy())),
+        ref_fp32_roundtrip_err=np.array(orc.max_normalised_error(rt32.numpy(), rt.numpy())),
+        ref_roundtrip_vs_input=np.array(orc.max_normalised_error(rt.numpy(), x.numpy())),
+        weights_rows=sht.weights.numpy()[[0, 1, 2, 359, 719]][:, ROWS_L][:, :, ::40],
+    )
+
+
+def vector_small(ref):
+    out = {}
+    for grid, nlat, nlon in (("equiangular", 33, 64), ("legendre-gauss", 32, 64), ("lobatto", 33, 66)):
+        vs = ref.RealVectorSHT(nlat, nlon, grid=grid) if grid != "equiangular" else ref.RealVectorSHT(nlat, nlon, lmax=20, grid=grid)
+        ivs = ref.InverseRealVectorSHT(nlat, nlon, lmax=vs.lmax, mmax=vs.mmax, grid=grid)
+        a = orc.random_coeffs((3, 2), vs.lmax, vs.mmax, seed=30, power=1.5, offset=1.0, zero_l0=True)
+        v = ivs(t64(a))
+        c = vs(v)
+        out[f"{grid}|lm"] = np.array([vs.lmax, vs.mmax])
+        out[f"{grid}|field"] = v.numpy()
+        out[f"{grid}|coeffs"] = c.numpy()
+    np.savez_compressed(os.path.join(HERE, "vector_small.npz"), **out)
+
+
+def cfg4(ref):
+    """Vector 721x1440; gradient + curl of two scalar random fields, amplitude (l+1)^-1.5, seed 3."""
+    a = orc.random_coeffs((1, 2), 720, 720, seed=3, power=1.5, offset=1.0, zero_l0=True)
+    ivs = ref.InverseRealVectorSHT(721, 1440, lmax=720, mmax=720, grid="equiangular")
+    vs = ref.RealVectorSHT(721, 1440, lmax=720, mmax=720, grid="equiangular")
+    v = ivs(t64(a))
+    c = vs(v)
+    np.savez_compressed(
+        os.path.join(HERE, "cfg4_vector_721x1440.npz"),
+        rows_k=ROWS_K,
+        rows_l=ROWS_L,
+        field_rows=v.numpy()[:, :, ROWS_K, :],
+        coeff_rows=c.numpy()[:, :, ROWS_L, :],
+        field_absmax=np.array(float(v.abs().max())),
+        coeff_absmax=np.array(float(c.abs().max())),
+    )
+
+
+def autograd_small(ref):
+    """Input gradients produced by the reference's autograd (scalar + vector, odd and even nlat)."""
+    out = {}
+    for tag, nlat, nlon, lmax, grid in (("eq", 17, 36, 12, "equiangular"), ("lg", 16, 30, 16, "legendre-gauss")):
+        sht = ref.RealSHT(nlat, nlon, lmax=lmax, grid=grid)
+        isht = ref.InverseRealSHT(nlat, nlon, lmax=lmax, grid=grid)
+        rng = np.random.default_rng(40)
+        x = rng.standard_normal((3, nlat, nlon))
+        g = rng.standard_normal((3, sht.lmax, sht.mmax)) + 1j * rng.standard_normal((3, sht.lmax, sht.mmax))
+        xt = t64(x).requires_grad_(True)
+        y = sht(xt)
+        y.backward(t64(g))
+        out[f"{tag}|sht_gx"] = xt.grad.numpy()
+        c = orc.random_coeffs((3,), sht.lmax, sht.mmax, seed=41) + 0j
+        c[..., :, 0] += 0.3j  # non-zero Im at m=0: the gradient there must vanish
+        gx = rng.standard_normal((3, nlat, nlon))
+        ct = t64(c).requires_grad_(True)
+        yy = isht(ct)
+        yy.backward(t64(gx))
+        out[f"{tag}|isht_gc"] = ct.grad.numpy()
+        out[f"{tag}|lm"] = np.array([sht.lmax, sht.mmax])
+        # vector
+        vs = ref.RealVectorSHT(nlat, nlon, lmax=lmax, grid=grid)
+        ivs = ref.InverseRealVectorSHT(nlat, nlon, lmax=lmax, grid=grid)
+        xv = rng.standard_normal((2, 2, nlat, nlon))
+        gv = rng.standard_normal((2, 2, vs.lmax, vs.mmax)) + 1j * rng.standard_normal((2, 2, vs.lmax, vs.mmax))
+        xvt = t64(xv).requires_grad_(True)
+        vs(xvt).backward(t64(gv))
+        out[f"{tag}|vsht_gx"] = xvt.grad.numpy()
+        cv = rng.standard_normal((2, 2, vs.lmax, vs.mmax)) + 1j * rng.standard_normal((2, 2, vs.lmax, vs.mmax))
+        gxv = rng.standard_normal((2, 2, nlat, nlon))
+        cvt = t64(cv).requires_grad_(True)
+        ivs(cvt).backward(t64(gxv))
+        out[f"{tag}|ivsht_gc"] = cvt.grad.numpy()
+    np.savez_compressed(os.path.join(HERE, "autograd_small.npz"), **out)
+
+
+def truncation_cases(ref):
+    """rfft/irfft mode padding and truncation: mmax above and below nlon//2+1, odd nlon."""
+    out = {}
+    for tag, nlat, nlon, lmax, mmax, grid in (
+        ("up", 12, 16, 12, 12, "legendre-gauss"),  # mmax 12 > nlon//2+1 = 9
+        ("odd", 13, 25, 10, 10, "lobatto"),
+        ("down", 16, 48, 6, 6, "equiangular"),
+        ("nyq", 20, 16, 9, 9, "legendre-gauss"),  # keeps the Nyquist bin m = 8
+    ):
+        sht = ref.RealSHT(nlat, nlon, lmax=lmax, mmax=mmax, grid=grid)
+        isht = ref.InverseRealSHT(nlat, nlon, lmax=lmax, mmax=mmax, grid=grid)
+        rng = np.random.default_rng(50)
+        x = rng.standard_normal((2, nlat, nlon))
+        c = sht(t64(x))
+        cin = rng.standard_normal((2, sht.lmax, sht.mmax)) + 1j * rng.standard_normal((2, sht.lmax, sht.mmax))
+        y = isht(t64(cin))
+        out[f"{tag}|lm"] = np.array([sht.lmax, sht.mmax])
+        out[f"{tag}|coeffs"] = c.numpy()
+        out[f"{tag}|field"] = y.numpy()
+    np.savez_compressed(os.path.join(HERE, "truncation_cases.npz"), **out)
+
+
+if __name__ == "__main__":
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--skip-large", action="store_true")
+    args = ap.parse_args()
+    warnings.simplefilter("ignore")
+    torch.set_grad_enabled(True)
+    ref = import_reference(args.reference)
+    tables(ref)
+    cfg1(ref)
+    cfg2(ref)
+    vector_small(ref)
+    autograd_small(ref)
+    truncation_cases(ref)
+    if not args.skip_large:
+        cfg3(ref)
+        cfg4(ref)
+    print("golden fixtures written to", HERE)

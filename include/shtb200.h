@@ -1,0 +1,129 @@
+/*
+ * shtb200 — C ABI of the B200 (sm_100a) spherical-harmonic-transform kernels.
+ *
+ * torch-harmonics has no FFI for this path: its SHT is a sequence of torch ops inside
+ * nn.Module.forward.  This header is the boundary a binding would target instead; each entry
+ * point names the reference method it replaces (paths relative to the torch-harmonics tree).
+ * Plain pointers and sizes only; no torch types.  All pointers named *_dev are CUDA device
+ * pointers on the plan's device; `stream` is a cudaStream_t passed as void* (NULL = default).
+ *
+ * Every function returns 0 on success and a negative SHTB200_E* code on failure;
+ * shtb200_last_error() returns a human-readable message for the calling thread's last failure.
+ */
+#ifndef SHTB200_H
+#define SHTB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SHTB200_OK 0
+#define SHTB200_EINVAL -1     /* bad argument (shape, null pointer, unsupported nlon factor ...) */
+#define SHTB200_ECUDA -2      /* a CUDA runtime / driver call failed */
+#define SHTB200_EWORKSPACE -3 /* workspace too small */
+#define SHTB200_EDEVICE -4    /* kernel reported a device-side error (bounded wait ran out ...) */
+
+/* What a plan computes.  The two ADJOINT kinds are the vector-Jacobian products autograd
+ * derives for the reference modules (they reuse the other direction's kernels with this
+ * direction's table). */
+enum shtb200_kind {
+    SHTB200_SHT = 0,          /* RealSHT.forward              torch_harmonics/sht.py:151-186 */
+    SHTB200_ISHT = 1,         /* InverseRealSHT.forward       torch_harmonics/sht.py:306-342 */
+    SHTB200_SHT_ADJOINT = 2,  /* d/dx of RealSHT.forward:  grad (.., lmax, mmax) c64 -> (.., nlat, nlon) */
+    SHTB200_ISHT_ADJOINT = 3, /* d/dc of InverseRealSHT.forward: grad (.., nlat, nlon) -> (.., lmax, mmax) c64 */
+    SHTB200_VSHT = 4,         /* RealVectorSHT.forward        torch_harmonics/sht.py:454-495 */
+    SHTB200_IVSHT = 5,        /* InverseRealVectorSHT.forward torch_harmonics/sht.py:606-649 */
+    SHTB200_VSHT_ADJOINT = 6,
+    SHTB200_IVSHT_ADJOINT = 7
+};
+
+/* Which Legendre contraction kernel a plan launches. */
+enum shtb200_engine {
+    SHTB200_ENGINE_AUTO = 0,   /* tensor-core kernel when the shape allows it */
+    SHTB200_ENGINE_SIMT = 1,   /* fp32 CUDA-core contraction */
+    SHTB200_ENGINE_TCGEN05 = 2 /* tcgen05 split-TF32 contraction, TMA-fed, TMEM accumulators */
+};
+
+typedef struct shtb200_plan shtb200_plan;
+
+int shtb200_version(void);
+const char *shtb200_last_error(void);
+
+/*
+ * Create a plan on CUDA device `device`.
+ *
+ * `table_dev` is the module's Legendre table in the reference's own dense layout, float32, on the device:
+ *   SHT, ISHT_ADJOINT   : RealSHT.weights-like   (mmax, lmax, nlat)         sht.py:141-146
+ *   ISHT, SHT_ADJOINT   : InverseRealSHT.pct-like (mmax, nlat, lmax)        sht.py:297-301
+ *     (for the ADJOINT kinds pass the table of the module being differentiated: SHT_ADJOINT takes
+ *      `weights` (mmax, lmax, nlat), ISHT_ADJOINT takes `pct` (mmax, nlat, lmax))
+ *   VSHT / IVSHT (+ adjoints): (2, mmax, lmax, nlat) / (2, mmax, nlat, lmax) sht.py:438-449, 597-601
+ * The table is repacked (l >= m band only, folded about the equator) into the plan; the caller may
+ * free it afterwards.  nlon must factor into primes <= 31 (2, 3, 5 take the fast butterflies).
+ * Replaces the constructors' buffer set-up, sht.py:113-146, 269-301, 411-449, 569-601.
+ */
+int shtb200_plan_create(shtb200_plan **plan, int kind, int nlat, int nlon, int lmax, int mmax, const float *table_dev, int device, int engine);
+int shtb200_plan_destroy(shtb200_plan *plan);
+
+/* Bytes of device scratch a call on `nfields` 2-D fields needs (vector kinds: nfields = number of (u,v) pairs). */
+size_t shtb200_workspace_bytes(const shtb200_plan *plan, int nfields);
+
+/*
+ * Run the plan: `in_dev` -> `out_dev`, both contiguous, on `nfields` fields.
+ *   grid -> spectral kinds (SHT, ISHT_ADJOINT, VSHT, IVSHT_ADJOINT):
+ *        in  float32   [nfields, (2,) nlat, nlon]
+ *        out complex64 [nfields, (2,) lmax, mmax]   (interleaved re, im; exact zeros where l < m)
+ *   spectral -> grid kinds (ISHT, SHT_ADJOINT, IVSHT, VSHT_ADJOINT): the reverse.
+ * `workspace_dev` must hold shtb200_workspace_bytes(plan, nfields) bytes and be 256-byte aligned.
+ * Work is enqueued on `stream`; the call does not synchronise.
+ * Replaces RealSHT.forward / InverseRealSHT.forward / RealVectorSHT.forward /
+ * InverseRealVectorSHT.forward (sht.py:151-186, 306-342, 454-495, 606-649) and their autograd.
+ */
+int shtb200_execute(shtb200_plan *plan, const void *in_dev, void *out_dev, int nfields, void *workspace_dev, size_t workspace_bytes, void *stream);
+
+/*
+ * Same transform on HOST buffers: copies `in_host` to the device, runs, copies the result back and
+ * synchronises `stream`.  Device staging buffers are kept in the plan and grown on demand.
+ * This is the call a host-side caller of the reference's CPU path would switch to.
+ */
+int shtb200_execute_host(shtb200_plan *plan, const void *in_host, void *out_host, int nfields, void *stream);
+
+/* Introspection used by the tests and the benchmark. */
+int shtb200_plan_info(const shtb200_plan *plan, int *nlat, int *nlon, int *lmax, int *mmax, int *kind, int *engine);
+/* Kernel launches the last shtb200_execute on this plan enqueued. */
+int shtb200_last_launch_count(const shtb200_plan *plan);
+/*
+ * Per-kernel device timing of one execute call.  With profiling on, shtb200_execute records a CUDA event on
+ * `stream` before its first kernel and after each kernel; shtb200_last_kernel_times waits for the last of them
+ * and writes the elapsed milliseconds between consecutive events into ms[0..capacity), returning how many it
+ * wrote.  Order for grid -> spectral kinds: zero-fill of l < m, longitude FFT, Legendre contraction; for
+ * spectral -> grid kinds: coefficient packing, Legendre contraction, longitude FFT.  (No counterpart in the
+ * reference, which times whole calls in benchmarks/bench.py:60-86.)
+ */
+int shtb200_plan_set_profiling(shtb200_plan *plan, int on);
+int shtb200_last_kernel_times(shtb200_plan *plan, float *ms, int capacity);
+/* Total bytes of packed Legendre table held by the plan. */
+size_t shtb200_plan_table_bytes(const shtb200_plan *plan);
+
+/*
+ * Stage entry points used by the spatially distributed transforms, where all-to-all transposes
+ * sit between the longitude FFT and the Legendre contraction (torch_harmonics/distributed/distributed_sht.py:172-222, 341-391).
+ *   shtb200_rfft_modes : float32 [nrows, nlon] -> complex64 [nrows, nmodes], 2*pi/nlon scaling folded in
+ *                        (rfft(norm="forward") * 2 pi, keep/zero-pad to nmodes: fft.py:52-68 + sht.py:171)
+ *   shtb200_irfft_modes: complex64 [nrows, nmodes] -> float32 [nrows, nlon], Im of DC/Nyquist ignored (fft.py:71-96)
+ *   shtb200_legendre   : the plan's contraction alone.  Analysis kinds: complex64 [nfields, nlat, mloc]
+ *                        (m fastest) -> complex64 [nfields, lmax, mloc]; synthesis kinds the reverse.  `m0` is
+ *                        the first global order held locally and `mloc` the number of local orders.
+ */
+int shtb200_rfft_modes(const float *in_dev, void *out_dev, long long nrows, int nlon, int nmodes, float scale, void *stream);
+int shtb200_irfft_modes(const void *in_dev, float *out_dev, long long nrows, int nlon, int nmodes, void *stream);
+int shtb200_legendre(shtb200_plan *plan, const void *in_dev, void *out_dev, int nfields, int m0, int mloc, void *workspace_dev, size_t workspace_bytes, void *stream);
+size_t shtb200_legendre_workspace_bytes(const shtb200_plan *plan, int nfields, int mloc);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SHTB200_H */

@@ -1,0 +1,247 @@
+"""GPU parity of the scalar transforms, called through the C ABI (ctypes) on seeded inputs and checked
+against the float64 oracle and the committed reference outputs.  Tolerance: max-normalised error <= 1e-5
+(``helpers.TOL``), the bound stated for the float32 path."""
+
+import os
+
+import numpy as np
+import pytest
+
+from oracle import sht_oracle as orc
+from tests.helpers import TOL, err, make_plan, oracle_tables, run_plan
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+
+ENGINES = ["simt", "auto"]
+
+# (nlat, nlon, lmax, mmax, grid, nfields): odd / even nlat, odd nlon, nlon with factors 7 and 11,
+# mmax above nlon//2+1 (zero-padded orders), tiny and ragged sizes, lmax > nlat
+SHAPES = [
+    (64, 128, 64, 65, "equiangular", 32),
+    (33, 64, 17, 17, "equiangular", 5),
+    (32, 64, None, None, "legendre-gauss", 3),
+    (33, 66, None, None, "lobatto", 2),
+    (13, 25, 10, 10, "lobatto", 1),
+    (12, 16, 12, 12, "legendre-gauss", 4),
+    (20, 16, 9, 9, "legendre-gauss", 2),
+    (16, 48, 6, 6, "equiangular", 7),
+    (9, 14, 5, 5, "legendre-gauss", 3),
+    (8, 16, 12, 9, "legendre-gauss", 2),
+    (91, 180, 90, 90, "equiangular", 9),
+    (2, 4, 2, 2, "legendre-gauss", 1),
+]
+
+
+@pytest.mark.parametrize("engine", ENGINES)
+@pytest.mark.parametrize("nlat,nlon,lmax,mmax,grid,nf", SHAPES)
+def test_sht_matches_oracle(nlat, nlon, lmax, mmax, grid, nf, engine):
+    import torch
+
+    from torch_harmonics_b200 import _lib
+
+    w, p, L, M = oracle_tables(nlat, nlon, lmax, mmax, grid)
+    x = np.random.default_rng(nlat * 1000 + nlon).standard_normal((nf, nlat, nlon)).astype(np.float32)
+    plan = make_plan(_lib.SHT, nlat, nlon, L, M, w, engine)
+    c = run_plan(plan, x, (nf, L, M), torch.complex64, nf)
+    ref = orc.sht_forward(x.astype(np.float64), w)
+    assert not np.isnan(c).any()
+    assert err(c, ref) <= TOL
+    # exact zeros above the diagonal, like the reference's dense table produces
+    ll, mm = np.meshgrid(np.arange(L), np.arange(M), indexing="ij")
+    assert np.all(c[:, ll < mm] == 0)
+
+
+@pytest.mark.parametrize("engine", ENGINES)
+@pytest.mark.parametrize("nlat,nlon,lmax,mmax,grid,nf", SHAPES)
+def test_isht_matches_oracle(nlat, nlon, lmax, mmax, grid, nf, engine):
+    import torch
+
+    from torch_harmonics_b200 import _lib
+
+    w, p, L, M = oracle_tables(nlat, nlon, lmax, mmax, grid)
+    rng = np.random.default_rng(nlat * 1000 + nlon + 1)
+    c = (rng.standard_normal((nf, L, M)) + 1j * rng.standard_normal((nf, L, M))).astype(np.complex64)
+    plan = make_plan(_lib.ISHT, nlat, nlon, L, M, p, engine)
+    x = run_plan(plan, c, (nf, nlat, nlon), torch.float32, nf)
+    ref = orc.sht_inverse(c.astype(np.complex128), p, nlon)
+    assert not np.isnan(x).any()
+    assert err(x, ref) <= TOL
+
+
+@pytest.mark.parametrize("engine", ENGINES)
+@pytest.mark.parametrize("nlat,nlon,lmax,grid", [(17, 36, 12, "equiangular"), (16, 30, 16, "legendre-gauss"), (33, 64, 20, "equiangular")])
+def test_adjoints_match_oracle(nlat, nlon, lmax, grid, engine):
+    import torch
+
+    from torch_harmonics_b200 import _lib
+
+    w, p, L, M = oracle_tables(nlat, nlon, lmax, None, grid)
+    rng = np.random.default_rng(5)
+    g = (rng.standard_normal((3, L, M)) + 1j * rng.standard_normal((3, L, M))).astype(np.complex64)
+    plan = make_plan(_lib.SHT_ADJOINT, nlat, nlon, L, M, w, engine)
+    gx = run_plan(plan, g, (3, nlat, nlon), torch.float32, 3)
+    assert err(gx, orc.sht_forward_vjp(g.astype(np.complex128), w, nlon)) <= TOL
+    gxx = rng.standard_normal((3, nlat, nlon)).astype(np.float32)
+    plan = make_plan(_lib.ISHT_ADJOINT, nlat, nlon, L, M, p, engine)
+    gc = run_plan(plan, gxx, (3, L, M), torch.complex64, 3)
+    assert err(gc, orc.sht_inverse_vjp(gxx.astype(np.float64), p)) <= TOL
+
+
+@pytest.mark.parametrize("engine", ENGINES)
+def test_cfg1_reference_outputs(engine):
+    """Equiangular 64x128, lmax 64, mmax 65 asked (resolves to 64, 64), N(0,1) input of seed 0: coefficients and
+    round trip against the reference's own float64 outputs."""
+    import torch
+
+    from torch_harmonics_b200 import _lib
+
+    g = np.load(os.path.join(GOLD, "cfg1_equiangular_64x128.npz"))
+    x = np.random.default_rng(0).standard_normal((4, 8, 64, 128)).astype(np.float32)
+    w, p, L, M = oracle_tables(64, 128, 64, 65, "equiangular")
+    assert (L, M) == (64, 64)
+    sht = make_plan(_lib.SHT, 64, 128, L, M, w, engine)
+    isht = make_plan(_lib.ISHT, 64, 128, L, M, p, engine)
+    c = run_plan(sht, x.reshape(32, 64, 128), (32, 64, 64), torch.complex64, 32).reshape(4, 8, 64, 64)
+    assert err(c[:2, :2], g["coeffs"]) <= TOL
+    rt = run_plan(isht, c.reshape(32, 64, 64), (32, 64, 128), torch.float32, 32).reshape(4, 8, 64, 128)
+    assert err(rt[:2, :2], g["roundtrip"]) <= TOL
+
+
+@pytest.mark.parametrize("engine", ENGINES)
+def test_cfg2_reference_outputs(engine):
+    """Legendre-Gauss 256x512, (256, 256): band-limited field synthesised from seeded coefficients."""
+    import torch
+
+    from torch_harmonics_b200 import _lib
+
+    g = np.load(os.path.join(GOLD, "cfg2_legendre_gauss_256x512.npz"))
+    a = orc.random_coeffs((2,), 256, 256, seed=1, power=1.0, offset=1.0)
+    w, p, L, M = oracle_tables(256, 512, 256, 257, "legendre-gauss")
+    isht = make_plan(_lib.ISHT, 256, 512, L, M, p, engine)
+    sht = make_plan(_lib.SHT, 256, 512, L, M, w, engine)
+    x = run_plan(isht, a.astype(np.complex64), (2, 256, 512), torch.float32, 2)
+    assert err(x[:1, ::4], g["field"]) <= TOL
+    c = run_plan(sht, x, (2, 256, 256), torch.complex64, 2)
+    assert err(c[:1, ::4], g["coeffs"]) <= TOL
+    assert err(c, a) <= 2 * TOL  # exact quadrature: the round trip recovers the coefficients
+
+
+@pytest.mark.parametrize("tag,nlat,nlon,lmax,mmax,grid", [
+    ("up", 12, 16, 12, 12, "legendre-gauss"),
+    ("odd", 13, 25, 10, 10, "lobatto"),
+    ("down", 16, 48, 6, 6, "equiangular"),
+    ("nyq", 20, 16, 9, 9, "legendre-gauss"),
+])
+def test_truncation_reference_outputs(tag, nlat, nlon, lmax, mmax, grid):
+    import torch
+
+    from torch_harmonics_b200 import _lib
+
+    g = np.load(os.path.join(GOLD, "truncation_cases.npz"))
+    w, p, L, M = oracle_tables(nlat, nlon, lmax, mmax, grid)
+    rng = np.random.default_rng(50)
+    x = rng.standard_normal((2, nlat, nlon))
+    cin = rng.standard_normal((2, L, M)) + 1j * rng.standard_normal((2, L, M))
+    c = run_plan(make_plan(_lib.SHT, nlat, nlon, L, M, w), x.astype(np.float32), (2, L, M), torch.complex64, 2)
+    assert err(c, g[f"{tag}|coeffs"]) <= TOL
+    y = run_plan(make_plan(_lib.ISHT, nlat, nlon, L, M, p), cin.astype(np.complex64), (2, nlat, nlon), torch.float32, 2)
+    assert err(y, g[f"{tag}|field"]) <= TOL
+
+
+def test_host_buffer_call_and_errors():
+    import ctypes
+
+    import torch
+
+    from torch_harmonics_b200 import _lib
+
+    w, p, L, M = oracle_tables(33, 64, 17, 17, "equiangular")
+    plan = make_plan(_lib.SHT, 33, 64, L, M, w)
+    x = np.random.default_rng(3).standard_normal((6, 33, 64)).astype(np.float32)
+    xt = torch.from_numpy(x).pin_memory()
+    out = torch.empty((6, L, M), dtype=torch.complex64).pin_memory()
+    plan.execute_host(xt, out, 6)
+    assert err(out.numpy(), orc.sht_forward(x.astype(np.float64), w)) <= TOL
+    assert plan.last_launch_count == 3
+    # empty batch is a no-op; undersized workspace is reported, not overrun
+    plan.execute_host(xt, out, 0)
+    xd = xt.cuda()
+    od = torch.empty((6, L, M), dtype=torch.complex64, device="cuda")
+    small = torch.empty(256, dtype=torch.uint8, device="cuda")
+    with pytest.raises(_lib.ShtLibraryError, match="workspace too small"):
+        plan.execute(xd, od, 6, small, 0)
+    lib = _lib.load()
+    h = ctypes.c_void_p()
+    t = torch.zeros(4, device="cuda")
+    assert lib.shtb200_plan_create(ctypes.byref(h), 0, 8, 2 * 37, 4, 4, ctypes.c_void_p(t.data_ptr()), 0, 0) == -1  # prime factor 37
+    assert b"prime factor" in lib.shtb200_last_error()
+    assert lib.shtb200_plan_create(ctypes.byref(h), 0, 8, 16, 4, 6, ctypes.c_void_p(t.data_ptr()), 0, 0) == -1  # mmax > lmax
+
+
+def test_linearity_and_batch_independence():
+    """Size-independent properties: T(a x + b y) = a T x + b T y, and a field's result does not depend on its batch."""
+    import torch
+
+    from torch_harmonics_b200 import _lib
+
+    w, p, L, M = oracle_tables(91, 180, 90, 90, "equiangular")
+    plan = make_plan(_lib.SHT, 91, 180, L, M, w)
+    rng = np.random.default_rng(9)
+    x = rng.standard_normal((4, 91, 180)).astype(np.float32)
+    y = rng.standard_normal((4, 91, 180)).astype(np.float32)
+    cx = run_plan(plan, x, (4, L, M), torch.complex64, 4)
+    cy = run_plan(plan, y, (4, L, M), torch.complex64, 4)
+    cz = run_plan(plan, (2 * x - 3 * y).astype(np.float32), (4, L, M), torch.complex64, 4)
+    assert err(cz, 2 * cx - 3 * cy) <= TOL
+    c1 = run_plan(plan, x[2:3], (1, L, M), torch.complex64, 1)
+    assert err(c1, cx[2:3]) <= 1e-6
+
+
+def test_stage_entry_points():
+    """rfft / irfft row transforms and the stand-alone Legendre stage used by the distributed modules."""
+    import ctypes
+
+    import torch
+
+    from torch_harmonics_b200 import _lib
+
+    lib = _lib.load()
+    rng = np.random.default_rng(11)
+    for nlon, nmodes, nrows in ((64, 33, 37), (30, 12, 5), (25, 13, 8), (16, 12, 3)):
+        x = rng.standard_normal((nrows, nlon)).astype(np.float32)
+        xd = torch.from_numpy(x).cuda()
+        out = torch.empty((nrows, nmodes), dtype=torch.complex64, device="cuda")
+        rc = lib.shtb200_rfft_modes(ctypes.c_void_p(xd.data_ptr()), ctypes.c_void_p(out.data_ptr()), nrows, nlon, nmodes, 2 * np.pi, None)
+        assert rc == 0
+        torch.cuda.synchronize()
+        assert err(out.cpu().numpy(), 2 * np.pi * orc.rfft_modes(x.astype(np.float64), nmodes)) <= TOL
+        c = (rng.standard_normal((nrows, nmodes)) + 1j * rng.standard_normal((nrows, nmodes))).astype(np.complex64)
+        cd = torch.from_numpy(c).cuda()
+        y = torch.empty((nrows, nlon), dtype=torch.float32, device="cuda")
+        rc = lib.shtb200_irfft_modes(ctypes.c_void_p(cd.data_ptr()), ctypes.c_void_p(y.data_ptr()), nrows, nlon, nmodes, None)
+        assert rc == 0
+        torch.cuda.synchronize()
+        assert err(y.cpu().numpy(), orc.irfft_modes(c.astype(np.complex128), nlon)) <= TOL
+
+    nlat, nlon, grid = 33, 64, "equiangular"
+    w, p, L, M = oracle_tables(nlat, nlon, 20, 20, grid)
+    nf, m0, mloc = 3, 5, 9
+    Xc = (rng.standard_normal((nf, nlat, mloc)) + 1j * rng.standard_normal((nf, nlat, mloc))).astype(np.complex64)
+    plan = make_plan(_lib.SHT, nlat, nlon, L, M, w)
+    xd = torch.from_numpy(Xc).cuda()
+    out = torch.full((nf, L, mloc), float("nan"), dtype=torch.complex64, device="cuda")
+    ws = torch.empty(plan.legendre_workspace_bytes(nf, mloc), dtype=torch.uint8, device="cuda")
+    plan.legendre(xd, out, nf, m0, mloc, ws, 0)
+    torch.cuda.synchronize()
+    ref = np.einsum("nkm,mlk->nlm", Xc.astype(np.complex128), w[m0:m0 + mloc])
+    assert err(out.cpu().numpy(), ref) <= TOL
+    plan = make_plan(_lib.ISHT, nlat, nlon, L, M, p)
+    c = (rng.standard_normal((nf, L, mloc)) + 1j * rng.standard_normal((nf, L, mloc))).astype(np.complex64)
+    cd = torch.from_numpy(c).cuda()
+    out = torch.full((nf, nlat, mloc), float("nan"), dtype=torch.complex64, device="cuda")
+    ws = torch.empty(plan.legendre_workspace_bytes(nf, mloc), dtype=torch.uint8, device="cuda")
+    plan.legendre(cd, out, nf, m0, mloc, ws, 0)
+    torch.cuda.synchronize()
+    ref = np.einsum("nlm,mkl->nkm", c.astype(np.complex128), p[m0:m0 + mloc])
+    assert err(out.cpu().numpy(), ref) <= TOL

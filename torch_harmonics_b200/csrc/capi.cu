@@ -1,0 +1,470 @@
+// C ABI of the shtb200 library: plan life cycle and the execute entry points.
+// Host-side glue only; the kernels live in fft_kernels.cu, legendre_*.cu and pack_kernels.cu.
+
+#include <math.h>
+#include <string.h>
+
+#include <algorithm>
+#include <mutex>
+
+#include "common.cuh"
+
+struct shtb200_plan : public shtb200::Plan {};
+
+namespace shtb200 {
+
+static thread_local std::string g_last_error;
+
+void set_error(const std::string &msg) { g_last_error = msg; }
+int fail(int code, const std::string &msg) {
+    g_last_error = msg;
+    return code;
+}
+
+namespace {
+
+bool is_analysis(int kind) { return kind == SHTB200_SHT || kind == SHTB200_ISHT_ADJOINT || kind == SHTB200_VSHT || kind == SHTB200_IVSHT_ADJOINT; }
+bool is_vector(int kind) { return kind >= SHTB200_VSHT; }
+
+template <typename T>
+int upload(T **dst, const std::vector<T> &src) {
+    SHT_CUDA_CHECK(cudaMalloc(dst, sizeof(T) * std::max<size_t>(src.size(), 1)));
+    if (!src.empty()) SHT_CUDA_CHECK(cudaMemcpy(*dst, src.data(), sizeof(T) * src.size(), cudaMemcpyHostToDevice));
+    return SHTB200_OK;
+}
+
+struct DeviceGuard {
+    int prev = -1;
+    bool ok = false;
+    explicit DeviceGuard(int dev) {
+        if (cudaGetDevice(&prev) == cudaSuccess && cudaSetDevice(dev) == cudaSuccess) ok = true;
+    }
+    ~DeviceGuard() {
+        if (prev >= 0) cudaSetDevice(prev);
+    }
+};
+
+size_t align256(size_t b) { return (b + 255) / 256 * 256; }
+
+struct WsLayout {
+    size_t op_bytes = 0;  // analysis: X; synthesis: packed coefficients
+    size_t y_bytes = 0;   // synthesis: latitude-row operand of the FFT
+    size_t extra_bytes = 0;
+    size_t total() const { return align256(op_bytes) + align256(y_bytes) + align256(extra_bytes); }
+};
+
+WsLayout ws_layout(const Plan &pl, int nfields, int m0, int mloc) {
+    WsLayout w;
+    const size_t ncols = (size_t)(pl.vector ? 4 : 2) * nfields;
+    if (pl.analysis) {
+        w.op_bytes = (size_t)2 * mloc * ncols * pl.ncomp * pl.Kp * sizeof(float);
+    } else {
+        const long long slabs = pl.group_b0[2 * (m0 + mloc)] - pl.group_b0[2 * m0];
+        w.op_bytes = (size_t)slabs * ncols * kBK * sizeof(float);
+        w.y_bytes = (size_t)2 * mloc * ncols * pl.Kp * sizeof(float);
+    }
+    return w;
+}
+
+GemmParams gemm_params(const Plan &pl, int nfields, int m0, int mloc, const float *B, float *out) {
+    GemmParams gp{};
+    gp.A = pl.d_table;
+    gp.B = B;
+    gp.a_pitch = pl.a_pitch;
+    gp.a_dx = pl.a_dx;
+    gp.a_kext = pl.a_kext;
+    gp.ncols = (pl.vector ? 4 : 2) * nfields;
+    gp.items = pl.d_items;
+    gp.nitems = (int)pl.items.size();
+    gp.out = out;
+    gp.lmax = pl.lmax;
+    gp.mmax_out = mloc;
+    gp.m0 = m0;
+    if (pl.analysis) {
+        gp.b_pitch = (long long)pl.ncomp * pl.Kp;
+        gp.b_dx = kBK;
+        gp.b_kext = pl.vector ? 2 * pl.Kp : pl.Kh;
+        gp.b_unit0 = 2 * m0;
+        gp.mode = EPI_COEFFS;
+    } else {
+        gp.b_pitch = kBK;
+        gp.b_dx = 0;
+        gp.b_kext = kBK;
+        gp.b_unit0 = pl.group_b0[2 * m0];
+        gp.mode = EPI_LATROWS;
+        gp.out_ld = pl.Kp;
+        gp.ngroups_cols = gp.ncols;
+    }
+    return gp;
+}
+
+void mark(Plan &pl, cudaStream_t st) {
+    if (!pl.profiling || pl.nev >= 8) return;
+    if (!pl.ev[pl.nev] && cudaEventCreate(&pl.ev[pl.nev]) != cudaSuccess) return;
+    cudaEventRecord(pl.ev[pl.nev++], st);
+}
+
+int run_gemm(Plan &pl, const GemmParams &gp, cudaStream_t st) {
+    bool tc = false;
+    if (pl.engine == SHTB200_ENGINE_TCGEN05) {
+        if (!gemm_tc_supported(pl, gp)) return fail(SHTB200_EINVAL, "tcgen05 engine requested but the shape is not supported by it");
+        tc = true;
+    } else if (pl.engine == SHTB200_ENGINE_AUTO) {
+        tc = gemm_tc_supported(pl, gp);
+    }
+    pl.last_launches += 1;
+    return tc ? launch_gemm_tc(pl, gp, st) : launch_gemm_simt(gp, st);
+}
+
+// Y slices of groups that contain no degree at all are never produced by the contraction.
+int clear_empty_groups(const Plan &pl, float *Y, int ncols, int m0, int mloc, cudaStream_t st) {
+    for (int g = 2 * m0; g < 2 * (m0 + mloc); ++g) {
+        if (pl.group_kblocks[g] == 0) {
+            SHT_CUDA_CHECK(cudaMemsetAsync(Y + (size_t)(g - 2 * m0) * ncols * pl.Kp, 0, sizeof(float) * (size_t)ncols * pl.Kp, st));
+        }
+    }
+    return SHTB200_OK;
+}
+
+int execute_full(Plan &pl, const void *in, void *out, int nfields, void *ws, size_t ws_bytes, cudaStream_t st) {
+    if (nfields < 0) return fail(SHTB200_EINVAL, "nfields must be >= 0");
+    pl.last_launches = 0;
+    if (nfields == 0) return SHTB200_OK;
+    if (!in || !out) return fail(SHTB200_EINVAL, "null input or output pointer");
+    WsLayout w = ws_layout(pl, nfields, 0, pl.mmax);
+    if (ws_bytes < w.total() || (!ws && w.total() > 0)) return fail(SHTB200_EWORKSPACE, "workspace too small: need " + std::to_string(w.total()) + " bytes");
+    if (((uintptr_t)ws & 255) != 0) return fail(SHTB200_EINVAL, "workspace must be 256-byte aligned");
+    int rc;
+    pl.nev = 0;
+    mark(pl, st);
+    if (pl.analysis) {
+        float *X = reinterpret_cast<float *>(ws);
+        if ((rc = launch_zero_upper(pl, reinterpret_cast<float2 *>(out), nfields, 0, pl.mmax, st))) return rc;
+        mark(pl, st);
+        if ((rc = launch_fft_analysis(pl, reinterpret_cast<const float *>(in), X, nfields, st))) return rc;
+        mark(pl, st);
+        pl.last_launches += 2;
+        GemmParams gp = gemm_params(pl, nfields, 0, pl.mmax, X, reinterpret_cast<float *>(out));
+        if ((rc = run_gemm(pl, gp, st))) return rc;
+        mark(pl, st);
+    } else {
+        float *Ct = reinterpret_cast<float *>(ws);
+        float *Y = reinterpret_cast<float *>(reinterpret_cast<char *>(ws) + align256(w.op_bytes));
+        const int ncols = (pl.vector ? 4 : 2) * nfields;
+        if ((rc = launch_pack_coeffs(pl, reinterpret_cast<const float2 *>(in), Ct, nfields, 0, pl.mmax, st))) return rc;
+        if ((rc = clear_empty_groups(pl, Y, ncols, 0, pl.mmax, st))) return rc;
+        mark(pl, st);
+        GemmParams gp = gemm_params(pl, nfields, 0, pl.mmax, Ct, Y);
+        if ((rc = run_gemm(pl, gp, st))) return rc;
+        mark(pl, st);
+        if ((rc = launch_fft_synthesis(pl, Y, reinterpret_cast<float *>(out), nfields, st))) return rc;
+        mark(pl, st);
+        pl.last_launches += 2;
+    }
+    return SHTB200_OK;
+}
+
+int grow(void **p, size_t *have, size_t need) {
+    if (*have >= need) return SHTB200_OK;
+    if (*p) cudaFree(*p);
+    *p = nullptr;
+    *have = 0;
+    SHT_CUDA_CHECK(cudaMalloc(p, need));
+    *have = need;
+    return SHTB200_OK;
+}
+
+}  // namespace
+}  // namespace shtb200
+
+using namespace shtb200;
+
+extern "C" {
+
+int shtb200_version(void) { return 100; }
+
+const char *shtb200_last_error(void) { return g_last_error.c_str(); }
+
+int shtb200_plan_create(shtb200_plan **plan_out, int kind, int nlat, int nlon, int lmax, int mmax, const float *table_dev, int device, int engine) {
+    if (!plan_out) return fail(SHTB200_EINVAL, "plan_out is null");
+    *plan_out = nullptr;
+    if (kind < SHTB200_SHT || kind > SHTB200_IVSHT_ADJOINT) return fail(SHTB200_EINVAL, "unknown plan kind");
+    if (engine < SHTB200_ENGINE_AUTO || engine > SHTB200_ENGINE_TCGEN05) return fail(SHTB200_EINVAL, "unknown engine");
+    if (nlat < 2 || nlon < 2 || lmax < 1 || mmax < 1) return fail(SHTB200_EINVAL, "nlat, nlon >= 2 and lmax, mmax >= 1 required");
+    if (mmax > lmax) return fail(SHTB200_EINVAL, "mmax must not exceed lmax (triangular truncation)");
+    if (!table_dev) return fail(SHTB200_EINVAL, "table_dev is null");
+    int ndev = 0;
+    if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) return fail(SHTB200_ECUDA, "no CUDA device available: this library has no CPU path");
+    if (device < 0 || device >= ndev) return fail(SHTB200_EINVAL, "device index out of range");
+    DeviceGuard guard(device);
+    if (!guard.ok) return fail(SHTB200_ECUDA, "cudaSetDevice failed");
+
+    shtb200_plan *pl = new shtb200_plan();
+    pl->kind = kind;
+    pl->engine = engine;
+    pl->device = device;
+    pl->nlat = nlat;
+    pl->nlon = nlon;
+    pl->lmax = lmax;
+    pl->mmax = mmax;
+    pl->analysis = is_analysis(kind);
+    pl->vector = is_vector(kind);
+    pl->ncomp = pl->vector ? 2 : 1;
+    pl->Kh = (nlat + 1) / 2;
+    pl->Kp = (int)round_up(pl->Kh, 8);
+    pl->Lh = (lmax + 1) / 2;
+    pl->negate_seg1 = (kind == SHTB200_VSHT_ADJOINT || kind == SHTB200_IVSHT_ADJOINT) ? 1 : 0;
+
+    int rc = build_fft_plan(nlon, &pl->fft, &pl->d_tw, &pl->d_perm);
+    if (rc) { shtb200_plan_destroy(pl); return rc; }
+
+    // per-order scale applied inside the FFT kernels
+    {
+        std::vector<float> ms(mmax);
+        for (int m = 0; m < mmax; ++m) {
+            const bool edge = (m == 0) || (2 * m == nlon);
+            double s = 1.0;
+            switch (kind) {
+                case SHTB200_SHT: case SHTB200_VSHT: s = 2.0 * M_PI / nlon; break;                       // sht.py:171
+                case SHTB200_ISHT: case SHTB200_IVSHT: s = 1.0; break;                                     // irfft(norm="forward")
+                case SHTB200_SHT_ADJOINT: case SHTB200_VSHT_ADJOINT: s = (2.0 * M_PI / nlon) * (edge ? 1.0 : 0.5); break;
+                case SHTB200_ISHT_ADJOINT: case SHTB200_IVSHT_ADJOINT: s = edge ? 1.0 : 2.0; break;
+            }
+            ms[m] = (float)s;
+        }
+        if ((rc = upload(&pl->d_mscale, ms))) { shtb200_plan_destroy(pl); return rc; }
+        pl->zero_imag_edges = (kind == SHTB200_ISHT_ADJOINT || kind == SHTB200_IVSHT_ADJOINT) ? 1 : 0;
+    }
+
+    // groups g = 2 m + p
+    const int ngroups = 2 * mmax;
+    pl->group_rows.assign(ngroups, 0);
+    for (int m = 0; m < mmax; ++m)
+        for (int p = 0; p < 2; ++p) {
+            int cnt = lmax - m - p;
+            pl->group_rows[2 * m + p] = cnt > 0 ? (cnt + 1) / 2 : 0;
+        }
+    pl->group_a0.assign(ngroups + 1, 0);
+    pl->group_kblocks.assign(ngroups, 0);
+    pl->group_b0.assign(ngroups + 1, 0);
+    std::vector<int> kb0(ngroups, 0);
+    if (pl->analysis) {
+        pl->a_pitch = (long long)pl->ncomp * pl->Kp;
+        pl->a_dx = kBK;
+        pl->a_kext = pl->vector ? 2 * pl->Kp : pl->Kh;
+        for (int g = 0; g < ngroups; ++g) pl->group_a0[g + 1] = pl->group_a0[g] + pl->group_rows[g];
+        pl->table_floats = (size_t)(pl->group_a0[ngroups] + kItemRowsMax) * pl->a_pitch;
+        const int kblocks = ceil_div(pl->vector ? 2 * pl->Kp : pl->Kh, kBK);
+        for (int g = 0; g < ngroups; ++g)
+            for (int r0 = 0; r0 < pl->group_rows[g]; r0 += kItemRowsMax) {
+                GemmItem it{};
+                it.a_y0 = (int)(pl->group_a0[g] + r0);
+                it.a_dy = 0;
+                it.b_y0 = g;
+                it.b_dy = 0;
+                it.kblocks = kblocks;
+                it.rows = std::min(kItemRowsMax, pl->group_rows[g] - r0);
+                it.m = g >> 1;
+                it.p = g & 1;
+                it.r0 = r0;
+                pl->items.push_back(it);
+            }
+    } else {
+        pl->a_pitch = kBK;
+        pl->a_dx = 0;
+        pl->a_kext = kBK;
+        for (int g = 0; g < ngroups; ++g) {
+            int nb = ceil_div(pl->group_rows[g], kBK);
+            if (pl->vector) {
+                kb0[g] = ceil_div(pl->group_rows[g ^ 1], kBK);
+                nb += kb0[g];
+            }
+            pl->group_kblocks[g] = nb;
+            pl->group_a0[g + 1] = pl->group_a0[g] + (long long)nb * pl->Kh;
+            pl->group_b0[g + 1] = pl->group_b0[g] + nb;
+        }
+        pl->total_b_slabs = pl->group_b0[ngroups];
+        pl->table_floats = (size_t)(pl->group_a0[ngroups] + kItemRowsMax) * kBK;
+        for (int g = 0; g < ngroups; ++g) {
+            if (pl->group_kblocks[g] == 0) continue;
+            for (int r0 = 0; r0 < pl->Kh; r0 += kItemRowsMax) {
+                GemmItem it{};
+                it.a_y0 = (int)(pl->group_a0[g] + r0);
+                it.a_dy = pl->Kh;
+                it.b_y0 = (int)pl->group_b0[g];
+                it.b_dy = 1;
+                it.kblocks = pl->group_kblocks[g];
+                it.rows = std::min(kItemRowsMax, pl->Kh - r0);
+                it.m = g >> 1;
+                it.p = g & 1;
+                it.r0 = r0;
+                pl->items.push_back(it);
+            }
+        }
+    }
+    if (pl->group_a0[ngroups] + kItemRowsMax > 0x7fffffffLL) { shtb200_plan_destroy(pl); return fail(SHTB200_EINVAL, "table too large for 32-bit row indices"); }
+    std::stable_sort(pl->items.begin(), pl->items.end(), [](const GemmItem &a, const GemmItem &b) {
+        return (long long)a.kblocks * a.rows > (long long)b.kblocks * b.rows;
+    });
+
+    if ((rc = upload(&pl->d_items, pl->items)) || (rc = upload(&pl->d_ga0, pl->group_a0)) || (rc = upload(&pl->d_gb0, pl->group_b0)) ||
+        (rc = upload(&pl->d_grows, pl->group_rows)) || (rc = upload(&pl->d_gkb, pl->group_kblocks)) || (rc = upload(&pl->d_gkb0, kb0))) {
+        shtb200_plan_destroy(pl);
+        return rc;
+    }
+    cudaError_t e = cudaMalloc(&pl->d_table, sizeof(float) * pl->table_floats);
+    if (e == cudaSuccess) e = cudaMemset(pl->d_table, 0, sizeof(float) * pl->table_floats);
+    if (e != cudaSuccess) { shtb200_plan_destroy(pl); return fail(SHTB200_ECUDA, std::string("table allocation: ") + cudaGetErrorString(e)); }
+    if ((rc = launch_pack_table(*pl, table_dev, 0))) { shtb200_plan_destroy(pl); return rc; }
+    *plan_out = pl;
+    return SHTB200_OK;
+}
+
+int shtb200_plan_destroy(shtb200_plan *pl) {
+    if (!pl) return SHTB200_OK;
+    DeviceGuard guard(pl->device);
+    cudaFree(pl->d_tw);
+    cudaFree(pl->d_perm);
+    cudaFree(pl->d_mscale);
+    cudaFree(pl->d_table);
+    cudaFree(pl->d_items);
+    cudaFree(pl->d_ga0);
+    cudaFree(pl->d_gb0);
+    cudaFree(pl->d_grows);
+    cudaFree(pl->d_gkb);
+    cudaFree(pl->d_gkb0);
+    cudaFree(pl->stage_in);
+    cudaFree(pl->stage_out);
+    cudaFree(pl->stage_ws);
+    for (auto &e : pl->ev)
+        if (e) cudaEventDestroy(e);
+    delete pl;
+    return SHTB200_OK;
+}
+
+size_t shtb200_workspace_bytes(const shtb200_plan *pl, int nfields) {
+    if (!pl || nfields <= 0) return 0;
+    return ws_layout(*pl, nfields, 0, pl->mmax).total();
+}
+
+int shtb200_execute(shtb200_plan *pl, const void *in_dev, void *out_dev, int nfields, void *workspace_dev, size_t workspace_bytes, void *stream) {
+    if (!pl) return fail(SHTB200_EINVAL, "plan is null");
+    DeviceGuard guard(pl->device);
+    if (!guard.ok) return fail(SHTB200_ECUDA, "cudaSetDevice failed");
+    return execute_full(*pl, in_dev, out_dev, nfields, workspace_dev, workspace_bytes, (cudaStream_t)stream);
+}
+
+int shtb200_execute_host(shtb200_plan *pl, const void *in_host, void *out_host, int nfields, void *stream) {
+    if (!pl) return fail(SHTB200_EINVAL, "plan is null");
+    if (nfields < 0) return fail(SHTB200_EINVAL, "nfields must be >= 0");
+    if (nfields == 0) return SHTB200_OK;
+    if (!in_host || !out_host) return fail(SHTB200_EINVAL, "null host pointer");
+    DeviceGuard guard(pl->device);
+    if (!guard.ok) return fail(SHTB200_ECUDA, "cudaSetDevice failed");
+    cudaStream_t st = (cudaStream_t)stream;
+    const size_t comp = pl->vector ? 2 : 1;
+    const size_t grid_bytes = (size_t)nfields * comp * pl->nlat * pl->nlon * sizeof(float);
+    const size_t spec_bytes = (size_t)nfields * comp * pl->lmax * pl->mmax * sizeof(float2);
+    const size_t in_bytes = pl->analysis ? grid_bytes : spec_bytes;
+    const size_t out_bytes = pl->analysis ? spec_bytes : grid_bytes;
+    const size_t ws_bytes = shtb200_workspace_bytes(pl, nfields);
+    int rc;
+    if ((rc = grow(&pl->stage_in, &pl->stage_in_bytes, in_bytes)) || (rc = grow(&pl->stage_out, &pl->stage_out_bytes, out_bytes)) ||
+        (rc = grow(&pl->stage_ws, &pl->stage_ws_bytes, ws_bytes)))
+        return rc;
+    SHT_CUDA_CHECK(cudaMemcpyAsync(pl->stage_in, in_host, in_bytes, cudaMemcpyHostToDevice, st));
+    if ((rc = execute_full(*pl, pl->stage_in, pl->stage_out, nfields, pl->stage_ws, pl->stage_ws_bytes, st))) return rc;
+    SHT_CUDA_CHECK(cudaMemcpyAsync(out_host, pl->stage_out, out_bytes, cudaMemcpyDeviceToHost, st));
+    SHT_CUDA_CHECK(cudaStreamSynchronize(st));
+    return SHTB200_OK;
+}
+
+int shtb200_plan_info(const shtb200_plan *pl, int *nlat, int *nlon, int *lmax, int *mmax, int *kind, int *engine) {
+    if (!pl) return fail(SHTB200_EINVAL, "plan is null");
+    if (nlat) *nlat = pl->nlat;
+    if (nlon) *nlon = pl->nlon;
+    if (lmax) *lmax = pl->lmax;
+    if (mmax) *mmax = pl->mmax;
+    if (kind) *kind = pl->kind;
+    if (engine) *engine = pl->engine;
+    return SHTB200_OK;
+}
+
+int shtb200_last_launch_count(const shtb200_plan *pl) { return pl ? pl->last_launches : 0; }
+
+int shtb200_plan_set_profiling(shtb200_plan *pl, int on) {
+    if (!pl) return fail(SHTB200_EINVAL, "plan is null");
+    pl->profiling = on ? 1 : 0;
+    pl->nev = 0;
+    return SHTB200_OK;
+}
+
+int shtb200_last_kernel_times(shtb200_plan *pl, float *ms, int capacity) {
+    if (!pl || !ms) return fail(SHTB200_EINVAL, "null argument");
+    if (pl->nev < 2) return 0;
+    DeviceGuard guard(pl->device);
+    if (cudaEventSynchronize(pl->ev[pl->nev - 1]) != cudaSuccess) return fail(SHTB200_ECUDA, "event synchronise failed");
+    int n = 0;
+    for (int i = 0; i + 1 < pl->nev && n < capacity; ++i, ++n) {
+        if (cudaEventElapsedTime(&ms[n], pl->ev[i], pl->ev[i + 1]) != cudaSuccess) return fail(SHTB200_ECUDA, "event elapsed time failed");
+    }
+    return n;
+}
+
+size_t shtb200_plan_table_bytes(const shtb200_plan *pl) { return pl ? pl->table_floats * sizeof(float) : 0; }
+
+int shtb200_rfft_modes(const float *in_dev, void *out_dev, long long nrows, int nlon, int nmodes, float scale, void *stream) {
+    if (nrows < 0 || nlon < 2 || nmodes < 1) return fail(SHTB200_EINVAL, "bad rfft shape");
+    if (nrows == 0) return SHTB200_OK;
+    if (!in_dev || !out_dev) return fail(SHTB200_EINVAL, "null pointer");
+    return launch_rfft_modes(in_dev, reinterpret_cast<float2 *>(out_dev), nrows, nlon, nmodes, scale, (cudaStream_t)stream);
+}
+
+int shtb200_irfft_modes(const void *in_dev, float *out_dev, long long nrows, int nlon, int nmodes, void *stream) {
+    if (nrows < 0 || nlon < 2 || nmodes < 1) return fail(SHTB200_EINVAL, "bad irfft shape");
+    if (nrows == 0) return SHTB200_OK;
+    if (!in_dev || !out_dev) return fail(SHTB200_EINVAL, "null pointer");
+    return launch_irfft_modes(reinterpret_cast<const float2 *>(in_dev), out_dev, nrows, nlon, nmodes, (cudaStream_t)stream);
+}
+
+size_t shtb200_legendre_workspace_bytes(const shtb200_plan *pl, int nfields, int mloc) {
+    if (!pl || nfields <= 0 || mloc <= 0) return 0;
+    // sized for the worst first order (m0 = 0 holds the longest groups)
+    return ws_layout(*pl, nfields, 0, std::min(mloc, pl->mmax)).total();
+}
+
+int shtb200_legendre(shtb200_plan *pl, const void *in_dev, void *out_dev, int nfields, int m0, int mloc, void *workspace_dev, size_t workspace_bytes, void *stream) {
+    if (!pl) return fail(SHTB200_EINVAL, "plan is null");
+    if (pl->vector) return fail(SHTB200_EINVAL, "stage-wise Legendre entry point supports the scalar kinds only");
+    if (nfields < 0 || m0 < 0 || mloc < 0 || m0 + mloc > pl->mmax) return fail(SHTB200_EINVAL, "bad (nfields, m0, mloc)");
+    pl->last_launches = 0;
+    if (nfields == 0 || mloc == 0) return SHTB200_OK;
+    if (!in_dev || !out_dev) return fail(SHTB200_EINVAL, "null pointer");
+    DeviceGuard guard(pl->device);
+    if (!guard.ok) return fail(SHTB200_ECUDA, "cudaSetDevice failed");
+    cudaStream_t st = (cudaStream_t)stream;
+    WsLayout w = ws_layout(*pl, nfields, m0, mloc);
+    if (workspace_bytes < w.total() || !workspace_dev) return fail(SHTB200_EWORKSPACE, "workspace too small: need " + std::to_string(w.total()) + " bytes");
+    if (((uintptr_t)workspace_dev & 255) != 0) return fail(SHTB200_EINVAL, "workspace must be 256-byte aligned");
+    int rc;
+    if (pl->analysis) {
+        float *X = reinterpret_cast<float *>(workspace_dev);
+        if ((rc = launch_fold_modes(*pl, reinterpret_cast<const float2 *>(in_dev), X, nfields, m0, mloc, st))) return rc;
+        if ((rc = launch_zero_upper(*pl, reinterpret_cast<float2 *>(out_dev), nfields, m0, mloc, st))) return rc;
+        pl->last_launches += 2;
+        GemmParams gp = gemm_params(*pl, nfields, m0, mloc, X, reinterpret_cast<float *>(out_dev));
+        if ((rc = run_gemm(*pl, gp, st))) return rc;
+    } else {
+        float *Ct = reinterpret_cast<float *>(workspace_dev);
+        float *Y = reinterpret_cast<float *>(reinterpret_cast<char *>(workspace_dev) + align256(w.op_bytes));
+        if ((rc = launch_pack_coeffs(*pl, reinterpret_cast<const float2 *>(in_dev), Ct, nfields, m0, mloc, st))) return rc;
+        if ((rc = clear_empty_groups(*pl, Y, 2 * nfields, m0, mloc, st))) return rc;
+        GemmParams gp = gemm_params(*pl, nfields, m0, mloc, Ct, Y);
+        if ((rc = run_gemm(*pl, gp, st))) return rc;
+        if ((rc = launch_unfold_modes(*pl, Y, reinterpret_cast<float2 *>(out_dev), nfields, m0, mloc, st))) return rc;
+        pl->last_launches += 2;
+    }
+    return SHTB200_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,169 @@
+// Shared declarations of the shtb200 library: plan object, device-side descriptors, launch helpers.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+#include <vector>
+
+#include "../../include/shtb200.h"
+
+namespace shtb200 {
+
+// ------------------------------------------------------------------------------------------------
+// error plumbing
+// ------------------------------------------------------------------------------------------------
+void set_error(const std::string &msg);
+int fail(int code, const std::string &msg);
+
+#define SHT_CUDA_CHECK(expr)                                                                              \
+    do {                                                                                                  \
+        cudaError_t _e = (expr);                                                                          \
+        if (_e != cudaSuccess) {                                                                          \
+            return ::shtb200::fail(SHTB200_ECUDA, std::string(#expr) + ": " + cudaGetErrorString(_e));    \
+        }                                                                                                 \
+    } while (0)
+
+// ------------------------------------------------------------------------------------------------
+// longitude FFT plan (device view passed by value to the kernels)
+// ------------------------------------------------------------------------------------------------
+constexpr int kMaxFftStages = 24;
+
+struct FftPlanDev {
+    int n;                        // nlon
+    int nstages;                  // number of radix passes
+    int radix[kMaxFftStages];     // radix of pass s (decimation in frequency order)
+    int sublen[kMaxFftStages];    // length L of the sub-transforms pass s splits (L_0 = n, L_{s+1} = L_s / radix_s)
+    const float2 *tw;             // n twiddles exp(-2 pi i k / n), computed in double
+    const unsigned short *perm;   // perm[k] = slot of output bin k after the in-place DIF passes
+};
+
+// ------------------------------------------------------------------------------------------------
+// Legendre contraction: one work item = one (order m, parity p) group x one block of table rows.
+//
+// Operands are addressed generically so that both packings share the kernels:
+//   element (row r, contraction index k) of an operand with origin row y0 lives at
+//       base[(y0 + (k / BK) * dy + r) * pitch + (k / BK) * dx + k % BK]
+//   "row-packed" (dx = BK, dy = 0): plain row-major rows, contraction index contiguous along a row;
+//   "block-packed" (dx = 0, dy = rows of a block): one [rows x BK] slab per BK-wide slice of k.
+// ------------------------------------------------------------------------------------------------
+constexpr int kBK = 32;  // contraction slice width (floats): one 128-byte swizzle row
+
+struct GemmItem {
+    int a_y0;      // first table row of this item
+    int a_dy;      // block-packed: rows per k-slab of this group; row-packed: 0
+    int b_y0;      // operand origin of this group in units of ncols rows (group index, or first k-slab of the group)
+    int b_dy;      // block-packed: 1 (ncols rows per k-slab); row-packed: 0
+    int kblocks;   // number of BK-wide slices of the contraction index
+    int rows;      // valid table rows in this item (<= kItemRowsMax)
+    int m;         // spherical harmonic order
+    int p;         // parity of l - m handled by this group (0 / 1)
+    int r0;        // index of the item's first row inside its group
+    int pad;
+};
+constexpr int kItemRowsMax = 384;  // three 128-row tensor-core tiles
+
+// How a finished tile leaves the contraction kernel.
+enum EpilogueMode : int {
+    EPI_COEFFS = 0,   // analysis: rows are degrees l = m + p + 2 r  -> complex64 out[n][l][m - m0]
+    EPI_LATROWS = 1,  // synthesis: rows are folded latitudes k'      -> float Y[group][col][k'] (row pitch ld)
+};
+
+struct GemmParams {
+    const float *A;       // packed Legendre table
+    const float *B;       // packed operand (FFT output / packed coefficients)
+    long long a_pitch;    // floats per table row
+    long long b_pitch;    // floats per operand row
+    int a_dx, b_dx;       // see above
+    int a_kext, b_kext;   // valid extent of the inner (k) axis of a row (reads beyond it yield 0)
+    int ncols;            // columns of the product = 2 * nfields (4 * pairs for vector kinds)
+    long long b_unit0;    // operand origin (same units as GemmItem::b_y0) of the first order held in B
+    const GemmItem *items;
+    int nitems;
+    int mode;             // EpilogueMode
+    float *out;           // destination
+    int lmax, mmax_out;   // EPI_COEFFS: out dims (mmax_out = number of orders stored = mloc)
+    int m0;               // first order stored in out (orders outside [m0, m0 + mmax_out) are skipped)
+    long long out_ld;     // EPI_LATROWS: floats per (group, col) row of Y
+    int ngroups_cols;     // EPI_LATROWS: columns per group in Y (= ncols)
+};
+
+// ------------------------------------------------------------------------------------------------
+// the plan
+// ------------------------------------------------------------------------------------------------
+struct Plan {
+    int kind = 0, engine = 0, device = 0;
+    int nlat = 0, nlon = 0, lmax = 0, mmax = 0;
+    int Kh = 0;   // folded latitude count, (nlat + 1) / 2
+    int Kp = 0;   // floats per row of a latitude-indexed operand (Kh rounded up to 8)
+    int Lh = 0;   // largest number of degrees of one parity, (lmax + 1) / 2
+    bool analysis = false;  // grid -> spectral
+    bool vector = false;
+    int ncomp = 1;          // latitude-axis multiplicity of the contraction (vector: 2 tables side by side)
+
+    // FFT
+    FftPlanDev fft{};
+    float2 *d_tw = nullptr;
+    unsigned short *d_perm = nullptr;
+    float *d_mscale = nullptr;  // per-order scale applied in the FFT kernel (2 pi / nlon, adjoint weights ...)
+    int zero_imag_edges = 0;    // analysis adjoint: force Im = 0 at m = 0 and Nyquist
+
+    // packed table
+    float *d_table = nullptr;
+    size_t table_floats = 0;
+    long long a_pitch = 0;
+    int a_dx = 0, a_kext = 0;
+    std::vector<int> group_rows;      // rows (degrees) in group g = 2 m + p
+    std::vector<long long> group_a0;  // first table row of group g
+    std::vector<int> group_kblocks;   // synthesis: BK-slabs of group g
+    std::vector<long long> group_b0;  // synthesis: first operand row of group g, per unit column (multiply by ncols)
+    long long total_b_slabs = 0;      // synthesis: sum of kblocks over groups
+
+    std::vector<GemmItem> items;      // host copy, longest first
+    GemmItem *d_items = nullptr;
+    // device copies of the per-group arrays
+    long long *d_ga0 = nullptr, *d_gb0 = nullptr;
+    int *d_grows = nullptr, *d_gkb = nullptr, *d_gkb0 = nullptr;
+    int negate_seg1 = 0;              // vector adjoints: the m/sin(theta) table enters with the opposite sign
+
+    // host-call staging
+    void *stage_in = nullptr, *stage_out = nullptr, *stage_ws = nullptr;
+    size_t stage_in_bytes = 0, stage_out_bytes = 0, stage_ws_bytes = 0;
+
+    int last_launches = 0;
+
+    // optional per-kernel timing (cudaEvents recorded between the launches of one execute call)
+    int profiling = 0;
+    cudaEvent_t ev[8] = {};
+    int nev = 0;
+};
+
+// ------------------------------------------------------------------------------------------------
+// kernel launchers (defined in the .cu files)
+// ------------------------------------------------------------------------------------------------
+int build_fft_plan(int nlon, FftPlanDev *out, float2 **d_tw, unsigned short **d_perm);
+
+// analysis: rows of x -> folded, order-major operand X[group][col][k'] (row pitch Kp)
+int launch_fft_analysis(const Plan &pl, const float *x, float *X, int nfields, cudaStream_t st);
+// synthesis: Y[group][col][k'] -> rows of x
+int launch_fft_synthesis(const Plan &pl, const float *Y, float *x, int nfields, cudaStream_t st);
+// plain row transforms for the distributed stages
+int launch_rfft_modes(const float *in, float2 *out, long long nrows, int nlon, int nmodes, float scale, cudaStream_t st);
+int launch_irfft_modes(const float2 *in, float *out, long long nrows, int nlon, int nmodes, cudaStream_t st);
+
+int launch_gemm_simt(const GemmParams &gp, cudaStream_t st);
+int launch_gemm_tc(const Plan &pl, const GemmParams &gp, cudaStream_t st);
+bool gemm_tc_supported(const Plan &pl, const GemmParams &gp);
+
+// table / operand packing
+int launch_pack_table(Plan &pl, const float *table, cudaStream_t st);
+int launch_pack_coeffs(const Plan &pl, const float2 *c, float *Ct, int nfields, int m0, int mloc, cudaStream_t st);
+int launch_zero_upper(const Plan &pl, float2 *c, int nfields, int m0, int mloc, cudaStream_t st);
+int launch_fold_modes(const Plan &pl, const float2 *Xc, float *X, int nfields, int m0, int mloc, cudaStream_t st);
+int launch_unfold_modes(const Plan &pl, const float *Y, float2 *Xc, int nfields, int m0, int mloc, cudaStream_t st);
+
+inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+inline long long round_up(long long a, long long b) { return (a + b - 1) / b * b; }
+
+}  // namespace shtb200

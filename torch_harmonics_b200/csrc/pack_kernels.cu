@@ -1,0 +1,233 @@
+// Repacking kernels around the Legendre contraction.
+//
+//  * pack_table_*   : once per plan, dense reference-layout Legendre table -> triangular (l >= m),
+//                     parity-split, equator-folded operand of the contraction.
+//  * pack_coeffs    : synthesis, per call: coefficients (field, l, m) -> order-major operand with the
+//                     degree index contiguous (replaces the transpose + real/imag split copies of
+//                     torch_harmonics/sht.py:326-328 and :630-633).
+//  * zero_upper     : analysis: exact zeros for l < m (the reference gets them from the zero half of its
+//                     dense table, torch_harmonics/legendre.py:77-78).
+//  * fold / unfold  : distributed stages: plain complex (field, k, m) <-> folded order-major operand.
+
+#include "common.cuh"
+
+namespace shtb200 {
+
+namespace {
+
+struct TableView {
+    const float *t;
+    int mmax, lmax, nlat;
+    int mkl;  // 0: (.., m, l, k)   1: (.., m, k, l)
+    __device__ float at(int seg, int m, int l, int k) const {
+        size_t base = (size_t)seg * mmax * lmax * nlat;
+        return mkl ? t[base + ((size_t)m * nlat + k) * lmax + l] : t[base + ((size_t)m * lmax + l) * nlat + k];
+    }
+};
+
+// rows = degrees, contraction index = folded latitude (row-packed): A[a0[g] + r][seg * Kp + k']
+__global__ void pack_table_rows_kernel(TableView tv, float *A, const long long *a0, const int *grows, int ngroups, int ncomp, int Kh, int Kp, int negate_seg1) {
+    const int g = blockIdx.y;
+    const int m = g >> 1, p = g & 1;
+    const int rows = grows[g];
+    const int pitch = ncomp * Kp;
+    const long long total = (long long)rows * pitch;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int r = (int)(i / pitch), c = (int)(i - (long long)r * pitch);
+        const int seg = c / Kp, k = c - seg * Kp;
+        const int l = m + p + 2 * r;
+        // scalar and the m/sin(theta) table share parity p with the rows; the d/dtheta table (seg 0 of a
+        // vector plan) has the opposite parity but is addressed the same way: the fold is chosen by the FFT kernel
+        float v = 0.f;
+        if (k < Kh) v = tv.at(ncomp == 2 ? seg : 0, m, l, k);
+        if (negate_seg1 && seg == 1) v = -v;
+        A[(a0[g] + r) * pitch + c] = v;
+    }
+}
+
+// rows = folded latitudes, contraction index = degree (block-packed): A[a0[g] + kb * Kh + k'][kk]
+// scalar: one segment, degrees of parity p.  vector: segment 0 = d/dtheta table with degrees of parity 1 - p,
+// segment 1 = m/sin(theta) table with degrees of parity p.
+__global__ void pack_table_blocks_kernel(TableView tv, float *A, const long long *a0, const int *gkb, const int *gkb0, int ngroups, int ncomp, int Kh,
+                                         int lmax, int negate_seg1) {
+    const int g = blockIdx.y;
+    const int m = g >> 1, p = g & 1;
+    const int nkb = gkb[g];
+    const int nkb0 = gkb0[g];  // slabs of segment 0 (0 for scalar)
+    const long long total = (long long)nkb * Kh * kBK;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int kk = (int)(i % kBK);
+        const long long t = i / kBK;
+        const int k = (int)(t % Kh);
+        const int kb = (int)(t / Kh);
+        int seg, r, par;
+        if (ncomp == 2 && kb < nkb0) { seg = 0; r = kb * kBK + kk; par = 1 - p; }
+        else { seg = ncomp == 2 ? 1 : 0; r = (kb - nkb0) * kBK + kk; par = p; }
+        const int l = m + par + 2 * r;
+        float v = 0.f;
+        if (l < lmax) v = tv.at(seg, m, l, k);
+        if (negate_seg1 && seg == 1) v = -v;
+        A[(a0[g] + (long long)kb * Kh + k) * kBK + kk] = v;
+    }
+}
+
+// Ct[((b0[g] - b0[2 m0]) + kb) * ncols + col][kk]
+__global__ void pack_coeffs_kernel(const float2 *__restrict__ c, float *__restrict__ Ct, const long long *b0, const int *gkb, const int *gkb0, int ncols,
+                                   int lmax, int mloc, int m0, int vector) {
+    const int gl = blockIdx.y;             // local group
+    const int g = gl + 2 * m0;
+    const int m = g >> 1, p = g & 1;
+    const int nkb = gkb[g], nkb0 = gkb0[g];
+    const long long base = (b0[g] - b0[2 * m0]) * ncols;
+    const long long total = (long long)nkb * ncols * kBK;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int kk = (int)(i % kBK);
+        const long long t = i / kBK;
+        const int col = (int)(t % ncols);
+        const int kb = (int)(t / ncols);
+        float v = 0.f;
+        if (!vector) {
+            const int l = m + p + 2 * (kb * kBK + kk);
+            if (l < lmax) {
+                float2 z = c[((size_t)(col >> 1) * lmax + l) * mloc + (m - m0)];
+                v = (col & 1) ? z.y : z.x;
+            }
+        } else {
+            const int pair = col >> 2, cc = col & 3;
+            const bool s0 = kb < nkb0;
+            const int l = s0 ? m + (1 - p) + 2 * (kb * kBK + kk) : m + p + 2 * ((kb - nkb0) * kBK + kk);
+            if (l < lmax) {
+                // which component / part / sign feeds (column cc, segment): torch_harmonics/sht.py:638-643
+                int comp, im;
+                float sg;
+                if (s0) {  // d/dtheta table
+                    comp = (cc < 2) ? 0 : 1; im = cc & 1; sg = (cc < 2) ? 1.f : -1.f;
+                } else {   // m / sin(theta) table
+                    comp = (cc < 2) ? 1 : 0; im = 1 - (cc & 1); sg = (cc == 0 || cc == 2) ? -1.f : 1.f;
+                }
+                float2 z = c[((size_t)(pair * 2 + comp) * lmax + l) * mloc + (m - m0)];
+                v = sg * (im ? z.y : z.x);
+            }
+        }
+        Ct[(base + (long long)kb * ncols + col) * kBK + kk] = v;
+    }
+}
+
+__global__ void zero_upper_kernel(float2 *c, long long nfl, int lmax, int mloc, int m0) {
+    // one thread per (field * l, m) element; only the l < m ones are written
+    const long long total = nfl * mloc;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int mi = (int)(i % mloc);
+        const int l = (int)((i / mloc) % lmax);
+        if (l < mi + m0) c[i] = make_float2(0.f, 0.f);
+    }
+}
+
+// Xc (field, k, mloc) complex -> X[(2 mi + p) * ncols + 2 f + ri][k'] (pitch Kp), zero in the pitch padding
+__global__ void fold_modes_kernel(const float2 *__restrict__ Xc, float *__restrict__ X, int nfields, int nlat, int Kh, int Kp, int mloc) {
+    const long long total = (long long)mloc * nfields * Kp;
+    const int ncols = 2 * nfields;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int k = (int)(i % Kp);
+        const long long t = i / Kp;
+        const int f = (int)(t % nfields);
+        const int mi = (int)(t / nfields);
+        float2 e = make_float2(0.f, 0.f), o = e;
+        if (k < Kh) {
+            const int ks = nlat - 1 - k;
+            float2 a = Xc[((size_t)f * nlat + k) * mloc + mi];
+            if (ks == k) { e = a; }
+            else {
+                float2 b = Xc[((size_t)f * nlat + ks) * mloc + mi];
+                e = make_float2(a.x + b.x, a.y + b.y);
+                o = make_float2(a.x - b.x, a.y - b.y);
+            }
+        }
+        float *g0 = X + ((size_t)(2 * mi) * ncols + 2 * f) * Kp + k;
+        float *g1 = X + ((size_t)(2 * mi + 1) * ncols + 2 * f) * Kp + k;
+        g0[0] = e.x; g0[Kp] = e.y; g1[0] = o.x; g1[Kp] = o.y;
+    }
+}
+
+// Y[(2 mi + p) * ncols + 2 f + ri][k'] -> Xc (field, k, mloc) complex
+__global__ void unfold_modes_kernel(const float *__restrict__ Y, float2 *__restrict__ Xc, int nfields, int nlat, int Kh, int Kp, int mloc) {
+    const long long total = (long long)nfields * Kh * mloc;
+    const int ncols = 2 * nfields;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int mi = (int)(i % mloc);
+        const long long t = i / mloc;
+        const int k = (int)(t % Kh);
+        const int f = (int)(t / Kh);
+        const float *g0 = Y + ((size_t)(2 * mi) * ncols + 2 * f) * Kp + k;
+        const float *g1 = Y + ((size_t)(2 * mi + 1) * ncols + 2 * f) * Kp + k;
+        float2 e = make_float2(g0[0], g0[Kp]), o = make_float2(g1[0], g1[Kp]);
+        const int ks = nlat - 1 - k;
+        Xc[((size_t)f * nlat + k) * mloc + mi] = make_float2(e.x + o.x, e.y + o.y);
+        if (ks != k) Xc[((size_t)f * nlat + ks) * mloc + mi] = make_float2(e.x - o.x, e.y - o.y);
+    }
+}
+
+}  // namespace
+
+static int grid_x_for(long long total) {
+    long long b = (total + 255) / 256;
+    if (b < 1) b = 1;
+    if (b > 4096) b = 4096;
+    return (int)b;
+}
+
+int launch_pack_table(Plan &pl, const float *table, cudaStream_t st) {
+    const int ngroups = 2 * pl.mmax;
+    TableView tv{table, pl.mmax, pl.lmax, pl.nlat, 0};
+    // dense layout handed over by the caller: (.., m, k, l) for the tables of the inverse modules
+    tv.mkl = (pl.kind == SHTB200_ISHT || pl.kind == SHTB200_ISHT_ADJOINT || pl.kind == SHTB200_IVSHT || pl.kind == SHTB200_IVSHT_ADJOINT) ? 1 : 0;
+    dim3 grid(64, ngroups);
+    if (pl.analysis) {
+        pack_table_rows_kernel<<<grid, 256, 0, st>>>(tv, pl.d_table, pl.d_ga0, pl.d_grows, ngroups, pl.ncomp, pl.Kh, pl.Kp, pl.negate_seg1);
+    } else {
+        pack_table_blocks_kernel<<<grid, 256, 0, st>>>(tv, pl.d_table, pl.d_ga0, pl.d_gkb, pl.d_gkb0, ngroups, pl.ncomp, pl.Kh, pl.lmax, pl.negate_seg1);
+    }
+    SHT_CUDA_CHECK(cudaGetLastError());
+    SHT_CUDA_CHECK(cudaStreamSynchronize(st));
+    return SHTB200_OK;
+}
+
+int launch_pack_coeffs(const Plan &pl, const float2 *c, float *Ct, int nfields, int m0, int mloc, cudaStream_t st) {
+    const int ncols = (pl.vector ? 4 : 2) * nfields;
+    if (mloc == 0 || ncols == 0) return SHTB200_OK;
+    const long long per_group = (long long)ceil_div(pl.Lh, kBK) * pl.ncomp * ncols * kBK;
+    dim3 grid(grid_x_for(per_group), 2 * mloc);
+    pack_coeffs_kernel<<<grid, 256, 0, st>>>(c, Ct, pl.d_gb0, pl.d_gkb, pl.d_gkb0, ncols, pl.lmax, mloc, m0, pl.vector ? 1 : 0);
+    SHT_CUDA_CHECK(cudaGetLastError());
+    return SHTB200_OK;
+}
+
+int launch_zero_upper(const Plan &pl, float2 *c, int nfields, int m0, int mloc, cudaStream_t st) {
+    const long long nfl = (long long)nfields * (pl.vector ? 2 : 1) * pl.lmax;
+    if (nfl == 0 || mloc == 0) return SHTB200_OK;
+    zero_upper_kernel<<<grid_x_for(nfl * mloc), 256, 0, st>>>(c, nfl, pl.lmax, mloc, m0);
+    SHT_CUDA_CHECK(cudaGetLastError());
+    return SHTB200_OK;
+}
+
+int launch_fold_modes(const Plan &pl, const float2 *Xc, float *X, int nfields, int m0, int mloc, cudaStream_t st) {
+    (void)m0;
+    if (pl.vector) return fail(SHTB200_EINVAL, "stage-wise Legendre entry point supports the scalar kinds only");
+    const long long total = (long long)mloc * nfields * pl.Kp;
+    if (total == 0) return SHTB200_OK;
+    fold_modes_kernel<<<grid_x_for(total), 256, 0, st>>>(Xc, X, nfields, pl.nlat, pl.Kh, pl.Kp, mloc);
+    SHT_CUDA_CHECK(cudaGetLastError());
+    return SHTB200_OK;
+}
+
+int launch_unfold_modes(const Plan &pl, const float *Y, float2 *Xc, int nfields, int m0, int mloc, cudaStream_t st) {
+    (void)m0;
+    if (pl.vector) return fail(SHTB200_EINVAL, "stage-wise Legendre entry point supports the scalar kinds only");
+    const long long total = (long long)nfields * pl.Kh * mloc;
+    if (total == 0) return SHTB200_OK;
+    unfold_modes_kernel<<<grid_x_for(total), 256, 0, st>>>(Y, Xc, nfields, pl.nlat, pl.Kh, pl.Kp, mloc);
+    SHT_CUDA_CHECK(cudaGetLastError());
+    return SHTB200_OK;
+}
+
+}  // namespace shtb200

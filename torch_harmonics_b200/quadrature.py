@@ -1,0 +1,91 @@
+"""Latitude quadrature rules in the cos(theta) domain, float64.
+
+Same nodes and weights as torch_harmonics/quadrature.py:176-204 (Gauss-Legendre, numpy ``leggauss``),
+:207-267 (Gauss-Lobatto by Newton iteration) and :270-325 (Clenshaw-Curtis by Waldvogel's FFT formula).
+"""
+
+import math
+from typing import Optional, Tuple
+
+import numpy as np
+import torch
+
+
+def _rescale(x: torch.Tensor, w: torch.Tensor, a: float, b: float):
+    half = (b - a) * 0.5
+    return half * x + (b + a) * 0.5, w * half
+
+
+def legendre_gauss_weights(n: int, a: Optional[float] = -1.0, b: Optional[float] = 1.0) -> Tuple[torch.Tensor, torch.Tensor]:
+    x, w = np.polynomial.legendre.leggauss(n)
+    return _rescale(torch.as_tensor(x).clone(), torch.as_tensor(w).clone(), a, b)
+
+
+def lobatto_weights(n: int, a: Optional[float] = -1.0, b: Optional[float] = 1.0, tol: Optional[float] = 1e-16, maxiter: Optional[int] = 100) -> Tuple[torch.Tensor, torch.Tensor]:
+    idx = torch.arange(n, dtype=torch.float64)
+    t = -torch.cos(math.pi * idx / (n - 1))
+    leg = torch.zeros((n, n), dtype=torch.float64)  # leg[:, k] = P_k(t)
+    for _ in range(maxiter):
+        prev = t
+        leg[:, 0] = 1.0
+        leg[:, 1] = t
+        for k in range(2, n):
+            leg[:, k] = ((2 * k - 1) * t * leg[:, k - 1] - (k - 1) * leg[:, k - 2]) / k
+        t = prev - (t * leg[:, n - 1] - leg[:, n - 2]) / (n * leg[:, n - 1])
+        if float((t - prev).abs().max()) < tol:
+            break
+    w = 2.0 / ((n * (n - 1)) * leg[:, n - 1] ** 2)
+    return _rescale(t, w, a, b)
+
+
+def clenshaw_curtiss_weights(n: int, a: Optional[float] = -1.0, b: Optional[float] = 1.0) -> Tuple[torch.Tensor, torch.Tensor]:
+    if n <= 1:
+        raise ValueError(f"n must be greater than 1, got {n}")
+    nodes = torch.cos(torch.linspace(math.pi, 0, n, dtype=torch.float64))
+    if n == 2:
+        w = torch.ones(2, dtype=torch.float64)
+    else:
+        n1 = n - 1
+        odd = torch.arange(1, n1, 2, dtype=torch.float64)
+        nodd = odd.numel()
+        rest = n1 - nodd
+        v = torch.cat([2.0 / odd / (odd - 2.0), 1.0 / odd[-1:], torch.zeros(rest, dtype=torch.float64)])
+        v = -v[:-1] - torch.flip(v[1:], dims=(0,))
+        g = -torch.ones(n1, dtype=torch.float64)
+        g[nodd] += n1
+        g[rest] += n1
+        g = g / (n1 * n1 - 1 + (n1 % 2))
+        w = torch.fft.ifft(v + g).real
+        w = torch.cat((w, w[:1]))
+    return _rescale(nodes, w, a, b)
+
+
+def precompute_longitudes(nlon: int) -> torch.Tensor:
+    return torch.linspace(0, 2 * math.pi, nlon + 1, dtype=torch.float64)[:-1]
+
+
+def _nodes(nlat: int, grid: str):
+    if grid == "legendre-gauss":
+        return legendre_gauss_weights(nlat, -1, 1)
+    if grid == "lobatto":
+        return lobatto_weights(nlat, -1, 1)
+    if grid == "equiangular":
+        return clenshaw_curtiss_weights(nlat, -1, 1)
+    raise ValueError("Unknown quadrature mode")
+
+
+def sht_colatitudes(nlat: int, grid: str):
+    """Colatitudes ascending from the north pole, and the rule's weights in the order the SHT
+    constructors use them (torch_harmonics/sht.py:124-143).  The rule itself is always evaluated on the
+    host; the result follows the ambient default device so that the tables built from it do too."""
+    with torch.device("cpu"):
+        cost, w = _nodes(nlat, grid)
+        tq = torch.flip(torch.arccos(cost), dims=(0,))
+    dev = torch.get_default_device()
+    return tq.to(dev), w.to(dev)
+
+
+def precompute_latitudes(nlat: int, grid: Optional[str] = "equiangular"):
+    """(colatitudes, weights), both flipped to run north to south (torch_harmonics/quadrature.py:109-137)."""
+    cost, w = _nodes(nlat, grid)
+    return torch.flip(torch.arccos(cost), dims=(0,)).clone(), torch.flip(w, dims=(0,)).clone()

@@ -111,7 +111,7 @@ size_t shtb200_plan_table_bytes(const shtb200_plan *plan);
 /*
  * Stage entry points used by the spatially distributed transforms, where all-to-all transposes
  * sit between the longitude FFT and the Legendre contraction (torch_harmonics/distributed/distributed_sht.py:172-222, 341-391).
- *   shtb200_rfft_modes : float32 [nrows, nlon] -> complex64 [nrows, nmodes], 2*pi/nlon scaling folded in
+ *   shtb200_rfft_modes : float32 [nrows, nlon] -> complex64 [nrows, nmodes] = scale * rfft(x, norm="forward"), pass scale = 2*pi
  *                        (rfft(norm="forward") * 2 pi, keep/zero-pad to nmodes: fft.py:52-68 + sht.py:171)
  *   shtb200_irfft_modes: complex64 [nrows, nmodes] -> float32 [nrows, nlon], Im of DC/Nyquist ignored (fft.py:71-96)
  *   shtb200_legendre   : the plan's contraction alone.  Analysis kinds: complex64 [nfields, nlat, mloc]

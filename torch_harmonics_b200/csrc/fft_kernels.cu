@@ -645,7 +645,7 @@ int launch_rfft_modes(const float *in, float2 *out, long long nrows, int nlon, i
     if ((rc = set_smem(rfft_rows_kernel<P>, smem)) != 0) return rc;
     long long blocks = (nrows + 2 * P - 1) / (2 * P);
     if (blocks == 0) return SHTB200_OK;
-    rfft_rows_kernel<P><<<(unsigned)blocks, 256, smem, st>>>(in, out, fp, nrows, nmodes, scale);
+    rfft_rows_kernel<P><<<(unsigned)blocks, 256, smem, st>>>(in, out, fp, nrows, nmodes, scale / (float)nlon);  // rfft(norm="forward") carries 1/nlon
     SHT_CUDA_CHECK(cudaGetLastError());
     return SHTB200_OK;
 }

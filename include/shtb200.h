@@ -105,6 +105,11 @@ int shtb200_last_launch_count(const shtb200_plan *plan);
  */
 int shtb200_plan_set_profiling(shtb200_plan *plan, int on);
 int shtb200_last_kernel_times(shtb200_plan *plan, float *ms, int capacity);
+/*
+ * Synchronise with the plan's device and report whether any kernel launched for this plan gave up on one of
+ * its bounded waits (returns SHTB200_EDEVICE once, then clears the flag).  No counterpart in the reference.
+ */
+int shtb200_device_status(shtb200_plan *plan);
 /* Total bytes of packed Legendre table held by the plan. */
 size_t shtb200_plan_table_bytes(const shtb200_plan *plan);
 

@@ -39,4 +39,5 @@ def run_plan(plan, x_np, out_shape, out_dtype, nfields):
     ws = torch.empty(max(plan.workspace_bytes(nfields), 1), dtype=torch.uint8, device="cuda")
     plan.execute(x, out, nfields, ws, torch.cuda.current_stream().cuda_stream)
     torch.cuda.synchronize()
+    plan.device_status()  # raises if a kernel gave up on a bounded wait
     return out.cpu().numpy()

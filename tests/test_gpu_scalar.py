@@ -13,7 +13,7 @@ from tests.helpers import TOL, err, make_plan, oracle_tables, run_plan
 pytestmark = pytest.mark.gpu
 GOLD = os.path.join(os.path.dirname(__file__), "golden")
 
-ENGINES = ["simt", "auto"]
+ENGINES = ["simt", "tcgen05"]
 
 # (nlat, nlon, lmax, mmax, grid, nfields): odd / even nlat, odd nlon, nlon with factors 7 and 11,
 # mmax above nlon//2+1 (zero-padded orders), tiny and ragged sizes, lmax > nlat

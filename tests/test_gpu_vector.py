@@ -14,7 +14,7 @@ pytestmark = pytest.mark.gpu
 GOLD = os.path.join(os.path.dirname(__file__), "golden")
 
 
-@pytest.mark.parametrize("engine", ["simt", "auto"])
+@pytest.mark.parametrize("engine", ["simt", "tcgen05"])
 @pytest.mark.parametrize("grid,nlat,nlon,lmax", [("equiangular", 33, 64, 20), ("legendre-gauss", 32, 64, None), ("lobatto", 33, 66, None)])
 def test_vector_reference_outputs(grid, nlat, nlon, lmax, engine):
     import torch

@@ -57,6 +57,8 @@ def load():
         lib.shtb200_plan_set_profiling.restype = ci
         lib.shtb200_last_kernel_times.argtypes = [vp, ctypes.POINTER(ctypes.c_float), ci]
         lib.shtb200_last_kernel_times.restype = ci
+        lib.shtb200_device_status.argtypes = [vp]
+        lib.shtb200_device_status.restype = ci
         lib.shtb200_plan_table_bytes.argtypes = [vp]
         lib.shtb200_plan_table_bytes.restype = cs
         lib.shtb200_rfft_modes.argtypes = [vp, vp, cll, ci, ci, ctypes.c_float, vp]
@@ -116,6 +118,10 @@ class Plan:
             self.handle, ctypes.c_void_p(inp.data_ptr()), ctypes.c_void_p(out.data_ptr()), nfields, m0, mloc, ctypes.c_void_p(workspace.data_ptr()), workspace.numel(), ctypes.c_void_p(stream)
         )
         check(rc, "shtb200_legendre")
+
+    def device_status(self):
+        """Synchronise and raise if a kernel of this plan gave up on a bounded wait."""
+        check(load().shtb200_device_status(self.handle), "shtb200_device_status")
 
     def set_profiling(self, on):
         check(load().shtb200_plan_set_profiling(self.handle, 1 if on else 0), "shtb200_plan_set_profiling")

@@ -312,6 +312,10 @@ int shtb200_plan_create(shtb200_plan **plan_out, int kind, int nlat, int nlon, i
         shtb200_plan_destroy(pl);
         return rc;
     }
+    if (cudaMalloc(&pl->d_err, sizeof(int)) != cudaSuccess || cudaMemset(pl->d_err, 0, sizeof(int)) != cudaSuccess) {
+        shtb200_plan_destroy(pl);
+        return fail(SHTB200_ECUDA, "error word allocation failed");
+    }
     cudaError_t e = cudaMalloc(&pl->d_table, sizeof(float) * pl->table_floats);
     if (e == cudaSuccess) e = cudaMemset(pl->d_table, 0, sizeof(float) * pl->table_floats);
     if (e != cudaSuccess) { shtb200_plan_destroy(pl); return fail(SHTB200_ECUDA, std::string("table allocation: ") + cudaGetErrorString(e)); }
@@ -336,6 +340,7 @@ int shtb200_plan_destroy(shtb200_plan *pl) {
     cudaFree(pl->stage_in);
     cudaFree(pl->stage_out);
     cudaFree(pl->stage_ws);
+    cudaFree(pl->d_err);
     for (auto &e : pl->ev)
         if (e) cudaEventDestroy(e);
     delete pl;
@@ -409,6 +414,19 @@ int shtb200_last_kernel_times(shtb200_plan *pl, float *ms, int capacity) {
         if (cudaEventElapsedTime(&ms[n], pl->ev[i], pl->ev[i + 1]) != cudaSuccess) return fail(SHTB200_ECUDA, "event elapsed time failed");
     }
     return n;
+}
+
+int shtb200_device_status(shtb200_plan *pl) {
+    if (!pl) return fail(SHTB200_EINVAL, "plan is null");
+    DeviceGuard guard(pl->device);
+    int v = 0;
+    cudaError_t e = cudaMemcpy(&v, pl->d_err, sizeof(int), cudaMemcpyDeviceToHost);  // waits for the work enqueued so far
+    if (e != cudaSuccess) return fail(SHTB200_ECUDA, std::string("device status: ") + cudaGetErrorString(e));
+    if (v != 0) {
+        cudaMemset(pl->d_err, 0, sizeof(int));
+        return fail(SHTB200_EDEVICE, "a kernel gave up on a bounded wait (device error word " + std::to_string(v) + ")");
+    }
+    return SHTB200_OK;
 }
 
 size_t shtb200_plan_table_bytes(const shtb200_plan *pl) { return pl ? pl->table_floats * sizeof(float) : 0; }

@@ -132,6 +132,7 @@ struct Plan {
     size_t stage_in_bytes = 0, stage_out_bytes = 0, stage_ws_bytes = 0;
 
     int last_launches = 0;
+    int *d_err = nullptr;             // device error word raised by kernels whose bounded waits ran out
 
     // optional per-kernel timing (cudaEvents recorded between the launches of one execute call)
     int profiling = 0;

@@ -35,7 +35,10 @@ struct FftPlanDev {
     int nstages;                  // number of radix passes
     int radix[kMaxFftStages];     // radix of pass s (decimation in frequency order)
     int sublen[kMaxFftStages];    // length L of the sub-transforms pass s splits (L_0 = n, L_{s+1} = L_s / radix_s)
-    const float2 *tw;             // n twiddles exp(-2 pi i k / n), computed in double
+    int twoff[kMaxFftStages];     // offset of pass s's twiddle table inside tw
+    int tw_pass_total;            // entries of all per-pass tables together
+    const float2 *tw;             // per-pass tables: entry (q - 1) * L/R + j of pass s = exp(-2 pi i q j / L_s), from double
+    const float2 *tw_full;        // n roots of unity exp(-2 pi i k / n) (generic prime-radix butterflies only)
     const unsigned short *perm;   // perm[k] = slot of output bin k after the in-place DIF passes
 };
 

@@ -99,7 +99,7 @@ int shtb200_last_launch_count(const shtb200_plan *plan);
  * Per-kernel device timing of one execute call.  With profiling on, shtb200_execute records a CUDA event on
  * `stream` before its first kernel and after each kernel; shtb200_last_kernel_times waits for the last of them
  * and writes the elapsed milliseconds between consecutive events into ms[0..capacity), returning how many it
- * wrote.  Order for grid -> spectral kinds: zero-fill of l < m, longitude FFT, Legendre contraction; for
+ * wrote.  Order for grid -> spectral kinds: longitude FFT, Legendre contraction, coefficient unpacking; for
  * spectral -> grid kinds: coefficient packing, Legendre contraction, longitude FFT.  (No counterpart in the
  * reference, which times whole calls in benchmarks/bench.py:60-86.)
  */

@@ -58,6 +58,7 @@ WsLayout ws_layout(const Plan &pl, int nfields, int m0, int mloc) {
     const size_t ncols = (size_t)(pl.vector ? 4 : 2) * nfields;
     if (pl.analysis) {
         w.op_bytes = (size_t)2 * mloc * ncols * pl.ncomp * pl.Kp * sizeof(float);
+        if (!pl.vector) w.y_bytes = (size_t)(pl.group_b0[2 * (m0 + mloc)] - pl.group_b0[2 * m0]) * ncols * kBK * sizeof(float);
     } else {
         const long long slabs = pl.group_b0[2 * (m0 + mloc)] - pl.group_b0[2 * m0];
         w.op_bytes = (size_t)slabs * ncols * kBK * sizeof(float);
@@ -85,7 +86,9 @@ GemmParams gemm_params(const Plan &pl, int nfields, int m0, int mloc, const floa
         gp.b_dx = kBK;
         gp.b_kext = pl.vector ? 2 * pl.Kp : pl.Kh;
         gp.b_unit0 = 2 * m0;
-        gp.mode = EPI_COEFFS;
+        gp.mode = pl.vector ? EPI_COEFFS : EPI_SLABS;
+        gp.slab0 = pl.d_gb0;
+        gp.slab_unit0 = pl.group_b0[2 * m0];
     } else {
         gp.b_pitch = kBK;
         gp.b_dx = 0;
@@ -139,13 +142,21 @@ int execute_full(Plan &pl, const void *in, void *out, int nfields, void *ws, siz
     mark(pl, st);
     if (pl.analysis) {
         float *X = reinterpret_cast<float *>(ws);
-        if ((rc = launch_zero_upper(pl, reinterpret_cast<float2 *>(out), nfields, 0, pl.mmax, st))) return rc;
-        mark(pl, st);
+        float *Z = reinterpret_cast<float *>(reinterpret_cast<char *>(ws) + align256(w.op_bytes));
+        if (pl.vector) {
+            if ((rc = launch_zero_upper(pl, reinterpret_cast<float2 *>(out), nfields, 0, pl.mmax, st))) return rc;
+            pl.last_launches += 1;
+        }
         if ((rc = launch_fft_analysis(pl, reinterpret_cast<const float *>(in), X, nfields, st))) return rc;
         mark(pl, st);
-        pl.last_launches += 2;
-        GemmParams gp = gemm_params(pl, nfields, 0, pl.mmax, X, reinterpret_cast<float *>(out));
+        pl.last_launches += 1;
+        GemmParams gp = gemm_params(pl, nfields, 0, pl.mmax, X, pl.vector ? reinterpret_cast<float *>(out) : Z);
         if ((rc = run_gemm(pl, gp, st))) return rc;
+        mark(pl, st);
+        if (!pl.vector) {
+            if ((rc = launch_unpack_coeffs(pl, Z, reinterpret_cast<float2 *>(out), nfields, 0, pl.mmax, st))) return rc;
+            pl.last_launches += 1;
+        }
         mark(pl, st);
     } else {
         float *Ct = reinterpret_cast<float *>(ws);
@@ -252,7 +263,13 @@ int shtb200_plan_create(shtb200_plan **plan_out, int kind, int nlat, int nlon, i
         pl->a_pitch = (long long)pl->ncomp * pl->Kp;
         pl->a_dx = kBK;
         pl->a_kext = pl->vector ? 2 * pl->Kp : pl->Kh;
-        for (int g = 0; g < ngroups; ++g) pl->group_a0[g + 1] = pl->group_a0[g] + pl->group_rows[g];
+        for (int g = 0; g < ngroups; ++g) {
+            pl->group_a0[g + 1] = pl->group_a0[g] + pl->group_rows[g];
+            // degree slabs of the contraction's output (same layout the synthesis side reads)
+            pl->group_kblocks[g] = ceil_div(pl->group_rows[g], kBK);
+            pl->group_b0[g + 1] = pl->group_b0[g] + pl->group_kblocks[g];
+        }
+        pl->total_b_slabs = pl->group_b0[ngroups];
         pl->table_floats = (size_t)(pl->group_a0[ngroups] + kItemRowsMax) * pl->a_pitch;
         const int kblocks = ceil_div(pl->vector ? 2 * pl->Kp : pl->Kh, kBK);
         for (int g = 0; g < ngroups; ++g)
@@ -467,11 +484,12 @@ int shtb200_legendre(shtb200_plan *pl, const void *in_dev, void *out_dev, int nf
     int rc;
     if (pl->analysis) {
         float *X = reinterpret_cast<float *>(workspace_dev);
+        float *Z = reinterpret_cast<float *>(reinterpret_cast<char *>(workspace_dev) + align256(w.op_bytes));
         if ((rc = launch_fold_modes(*pl, reinterpret_cast<const float2 *>(in_dev), X, nfields, m0, mloc, st))) return rc;
-        if ((rc = launch_zero_upper(*pl, reinterpret_cast<float2 *>(out_dev), nfields, m0, mloc, st))) return rc;
-        pl->last_launches += 2;
-        GemmParams gp = gemm_params(*pl, nfields, m0, mloc, X, reinterpret_cast<float *>(out_dev));
+        GemmParams gp = gemm_params(*pl, nfields, m0, mloc, X, Z);
         if ((rc = run_gemm(*pl, gp, st))) return rc;
+        if ((rc = launch_unpack_coeffs(*pl, Z, reinterpret_cast<float2 *>(out_dev), nfields, m0, mloc, st))) return rc;
+        pl->last_launches += 2;
     } else {
         float *Ct = reinterpret_cast<float *>(workspace_dev);
         float *Y = reinterpret_cast<float *>(reinterpret_cast<char *>(workspace_dev) + align256(w.op_bytes));

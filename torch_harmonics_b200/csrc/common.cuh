@@ -65,12 +65,14 @@ struct GemmItem {
     int r0;        // index of the item's first row inside its group
     int pad;
 };
-constexpr int kItemRowsMax = 384;  // three 128-row tensor-core tiles
+constexpr int kItemRowsMax = 128;  // one 128-row tensor-core tile
 
 // How a finished tile leaves the contraction kernel.
 enum EpilogueMode : int {
     EPI_COEFFS = 0,   // analysis: rows are degrees l = m + p + 2 r  -> complex64 out[n][l][m - m0]
     EPI_LATROWS = 1,  // synthesis: rows are folded latitudes k'      -> float Y[group][col][k'] (row pitch ld)
+    EPI_SLABS = 2,    // analysis: rows are degrees -> float Z[(slab0[g] + r / 32) * ncols + col][r % 32], the same
+                      // degree-slab layout the synthesis contraction reads its coefficients from
 };
 
 struct GemmParams {
@@ -90,6 +92,8 @@ struct GemmParams {
     int m0;               // first order stored in out (orders outside [m0, m0 + mmax_out) are skipped)
     long long out_ld;     // EPI_LATROWS: floats per (group, col) row of Y
     int ngroups_cols;     // EPI_LATROWS: columns per group in Y (= ncols)
+    const long long *slab0;  // EPI_SLABS: first slab of every group (device array, 2 * mmax + 1 entries)
+    long long slab_unit0;    // EPI_SLABS: slab0 of the first order held in the output
 };
 
 // ------------------------------------------------------------------------------------------------
@@ -163,6 +167,7 @@ bool gemm_tc_supported(const Plan &pl, const GemmParams &gp);
 // table / operand packing
 int launch_pack_table(Plan &pl, const float *table, cudaStream_t st);
 int launch_pack_coeffs(const Plan &pl, const float2 *c, float *Ct, int nfields, int m0, int mloc, cudaStream_t st);
+int launch_unpack_coeffs(const Plan &pl, const float *Z, float2 *c, int nfields, int m0, int mloc, cudaStream_t st);
 int launch_zero_upper(const Plan &pl, float2 *c, int nfields, int m0, int mloc, cudaStream_t st);
 int launch_fold_modes(const Plan &pl, const float2 *Xc, float *X, int nfields, int m0, int mloc, cudaStream_t st);
 int launch_unfold_modes(const Plan &pl, const float *Y, float2 *Xc, int nfields, int m0, int mloc, cudaStream_t st);

@@ -80,6 +80,14 @@ __global__ void __launch_bounds__(256) legendre_simt_kernel(GemmParams gp) {
                 float2 *o = reinterpret_cast<float2 *>(gp.out) + ((size_t)(c >> 1) * gp.lmax + l) * gp.mmax_out + (it.m - gp.m0);
                 *o = make_float2(acc[i][j], acc[i][j + 1]);
             }
+        } else if (gp.mode == EPI_SLABS) {
+            const long long slab = gp.slab0[2 * it.m + it.p] - gp.slab_unit0 + (rg >> 5);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int c = col0 + tx * 4 + j;
+                if (c >= gp.ncols) continue;
+                gp.out[((size_t)slab * gp.ncols + c) * kBK + (rg & 31)] = acc[i][j];
+            }
         } else {
             const int g = 2 * (it.m - gp.m0) + it.p;
 #pragma unroll

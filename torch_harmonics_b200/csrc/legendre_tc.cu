@@ -3,17 +3,18 @@
 // Per (order m, parity) group the contraction is a real GEMM  D[rows x cols] = A[rows x K] * B[cols x K]^T
 // with A the packed Legendre table (rows = degrees for analysis, folded latitudes for synthesis) and B the
 // operand produced by the FFT kernel / coefficient packing (cols = 2 x fields).  One persistent CTA per SM
-// walks a longest-first list of work units (item, column tile):
+// walks a longest-first list of work units (128-row item, column tile):
 //
-//   warp 0      TMA producer: cp.async.bulk.tensor loads of up to three 128-row A tiles and one B tile per 16-wide
-//               k-step into a 4-deep ring of 64-byte-swizzled shared-memory stages (full/empty mbarriers).
-//   warps 2-5   splitter: for each landed stage compute lo = x - tf32_trunc(x) for A and B into one of two "lo"
+//   warp 0      TMA producer: cp.async.bulk.tensor loads of one 128 x 32 A tile and one B tile per k-step into a
+//               4-deep ring of 128-byte-swizzled shared-memory stages (full/empty mbarriers).
+//   warps 2-9   splitter: for each landed stage compute lo = x - tf32_trunc(x) for A and B into one of two "lo"
 //               slots (same swizzled layout, so the pass is a straight elementwise sweep).
-//   warp 1      MMA issuer: per k-step and A tile three tcgen05.mma chains (A B, A_lo B, A B_lo; the tensor core
-//               reads fp32 words as TF32 by dropping the low mantissa bits), fp32 accumulation in TMEM
-//               (3 accumulators x up to 160 columns); tcgen05.commit releases stages / lo slots / accumulators.
-//   warps 6-9   epilogue: tcgen05.ld of the accumulators, direct stores to the coefficient array (analysis) or the
-//               latitude-row operand of the synthesis FFT.
+//   warp 1      MMA issuer: per k-step three tcgen05.mma chains (A_lo B, A B_lo, A B; the tensor core reads
+//               fp32 words as TF32 by dropping the low mantissa bits), fp32 accumulation in one of three
+//               tensor-memory accumulators; tcgen05.commit releases stages, lo slots and accumulators.
+//   warps 10-17 epilogue: tcgen05.ld of a finished accumulator while the next units are being multiplied,
+//               direct stores to the coefficient array (analysis) or the latitude-row operand of the
+//               synthesis FFT.
 //
 // Every mbarrier wait is bounded: when one runs out the CTA raises a device error word and unwinds.
 // Replaces torch.einsum -> aten::bmm at torch_harmonics/sht.py:180-181, :333-334 (vector :488-493, :638-643).
@@ -31,20 +32,24 @@ namespace shtb200 {
 
 namespace {
 
-constexpr int TK = 16;                 // floats per k-step (one 64-byte swizzle row)
+constexpr int TK = kBK;                // floats per k-step: one 128-byte swizzle row
 constexpr int TILE_M = 128;
-constexpr int MT_MAX = kItemRowsMax / TILE_M;  // 3
 constexpr int BN_MAX = 160;
-constexpr int NSTAGE = 4;
-constexpr int NLO = 2;
-constexpr int A_TILE_BYTES = TILE_M * TK * 4;                          // 8 KiB
-constexpr int STAGE_BYTES = MT_MAX * A_TILE_BYTES + BN_MAX * TK * 4;   // 34 KiB
-constexpr int B_OFF = MT_MAX * A_TILE_BYTES;
+constexpr int NSTAGE = 4;              // TMA ring
+constexpr int NLO = 2;                 // slots for the low-order parts
+constexpr int NACC = 3;                // accumulator buffers in tensor memory
+constexpr int A_TILE_BYTES = TILE_M * TK * 4;                // 16 KiB
+constexpr int STAGE_BYTES = A_TILE_BYTES + BN_MAX * TK * 4;  // 36 KiB
+constexpr int B_OFF = A_TILE_BYTES;
 constexpr int TMEM_COLS = 512;
-constexpr int NTHREADS = 320;
-constexpr long long WAIT_LIMIT = 4000000000LL;  // ~2 s of SM clock
+constexpr int NSPLIT_WARPS = 8, NEPI_WARPS = 8;
+constexpr int NTHREADS = 32 * (2 + NSPLIT_WARPS + NEPI_WARPS);  // 576
+constexpr long long WAIT_LIMIT = 4000000000LL;                  // ~2 s of SM clock
 
+constexpr int NBARS = 2 * NSTAGE + 2 * NLO + 2 * NACC;
 constexpr int SMEM_BYTES = (NSTAGE + NLO) * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+static_assert(NACC * BN_MAX <= TMEM_COLS, "accumulators must fit tensor memory");
+static_assert(kItemRowsMax == TILE_M, "one work item = one 128-row tensor-core tile");
 
 struct TcParams {
     GemmParams gp;
@@ -72,9 +77,9 @@ legendre_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     auto bar_empty = [&](int s) { return bar0 + 8u * (NSTAGE + s); };
     auto bar_lofull = [&](int c) { return bar0 + 8u * (2 * NSTAGE + c); };
     auto bar_loempty = [&](int c) { return bar0 + 8u * (2 * NSTAGE + NLO + c); };
-    const uint32_t bar_accfull = bar0 + 8u * (2 * NSTAGE + 2 * NLO);
-    const uint32_t bar_accempty = bar_accfull + 8u;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(base_ptr + (NSTAGE + NLO) * STAGE_BYTES + 8 * (2 * NSTAGE + 2 * NLO + 2));
+    auto bar_accfull = [&](int a) { return bar0 + 8u * (2 * NSTAGE + 2 * NLO + a); };
+    auto bar_accempty = [&](int a) { return bar0 + 8u * (2 * NSTAGE + 2 * NLO + NACC + a); };
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(base_ptr + (NSTAGE + NLO) * STAGE_BYTES + 8 * NBARS);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -82,9 +87,8 @@ legendre_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < NSTAGE; ++s) { ptx::mbar_init(bar_full(s), 1); ptx::mbar_init(bar_empty(s), 1); }
-        for (int c = 0; c < NLO; ++c) { ptx::mbar_init(bar_lofull(c), 128); ptx::mbar_init(bar_loempty(c), 1); }
-        ptx::mbar_init(bar_accfull, 1);
-        ptx::mbar_init(bar_accempty, 128);
+        for (int c = 0; c < NLO; ++c) { ptx::mbar_init(bar_lofull(c), 32 * NSPLIT_WARPS); ptx::mbar_init(bar_loempty(c), 1); }
+        for (int a = 0; a < NACC; ++a) { ptx::mbar_init(bar_accfull(a), 1); ptx::mbar_init(bar_accempty(a), 32 * NEPI_WARPS); }
         *abort_flag = 0;
         ptx::fence_barrier_init();
         ptx::prefetch_tensormap(&tmA);
@@ -102,13 +106,12 @@ legendre_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     const bool row_packed_a = gp.a_dx != 0, row_packed_b = gp.b_dx != 0;
 
     // ---- decode of work unit u (identical in every role) ----
-    struct Unit { GemmItem it; int ntile; int mt; int ksteps; bool skip; };
+    struct Unit { GemmItem it; int ntile; int ksteps; bool skip; };
     auto get_unit = [&](int u) {
         Unit w;
         w.it = gp.items[u / P.ntiles];
         w.ntile = u % P.ntiles;
-        w.mt = (w.it.rows + TILE_M - 1) / TILE_M;
-        w.ksteps = w.it.kblocks * (kBK / TK);
+        w.ksteps = w.it.kblocks;
         if (row_packed_a && w.ksteps > P.ksteps_cap) w.ksteps = P.ksteps_cap;
         w.skip = (w.it.m < gp.m0) || (w.it.m >= gp.m0 + gp.mmax_out);
         return w;
@@ -120,22 +123,18 @@ legendre_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             int s = 0;
             uint32_t ph = 0;
             bool ok = true;
+            const uint32_t bytes = (uint32_t)(A_TILE_BYTES + P.bn * TK * 4);
             for (int u = blockIdx.x; u < P.nunits && ok; u += gridDim.x) {
                 const Unit w = get_unit(u);
                 if (w.skip) continue;
-                const uint32_t bytes = (uint32_t)(w.mt * A_TILE_BYTES + P.bn * TK * 4);
                 const long long by0 = ((long long)w.it.b_y0 - gp.b_unit0) * gp.ncols + (long long)w.ntile * P.bn;
                 for (int ks = 0; ks < w.ksteps; ++ks) {
                     if (!(ok = ptx::mbar_wait_bounded(bar_empty(s), ph ^ 1u, abort_flag, WAIT_LIMIT))) break;
                     ptx::mbar_arrive_expect_tx(bar_full(s), bytes);
-                    const int kb = (ks * TK) / kBK, kin = (ks * TK) % kBK;
-                    const int ax = row_packed_a ? ks * TK : kin;
-                    const int ay = w.it.a_y0 + (row_packed_a ? 0 : kb * w.it.a_dy);
                     const uint32_t dst = stage0 + s * STAGE_BYTES;
-                    for (int t = 0; t < w.mt; ++t) ptx::tma_load_2d(dst + t * A_TILE_BYTES, &tmA, ax, ay + t * TILE_M, bar_full(s));
-                    const int bx = row_packed_b ? ks * TK : kin;
-                    const long long by = by0 + (row_packed_b ? 0 : (long long)kb * w.it.b_dy * gp.ncols);
-                    ptx::tma_load_2d(dst + B_OFF, &tmB, bx, (int)by, bar_full(s));
+                    ptx::tma_load_2d(dst, &tmA, row_packed_a ? ks * TK : 0, w.it.a_y0 + (row_packed_a ? 0 : ks * w.it.a_dy), bar_full(s));
+                    const long long by = by0 + (row_packed_b ? 0 : (long long)ks * w.it.b_dy * gp.ncols);
+                    ptx::tma_load_2d(dst + B_OFF, &tmB, row_packed_b ? ks * TK : 0, (int)by, bar_full(s));
                     if (++s == NSTAGE) { s = 0; ph ^= 1u; }
                 }
             }
@@ -143,32 +142,30 @@ legendre_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     } else if (warp == 1) {
         // =========================== MMA issuer ===========================
         if (lane == 0) {
-            int s = 0, c = 0;
-            uint32_t ph = 0, phc = 0, phacc = 0;
+            int s = 0, c = 0, a = 0;
+            uint32_t ph = 0, phc = 0, pha = 0;
             bool ok = true;
             const uint32_t idesc = ptx::idesc_tf32_m128((uint32_t)P.bn);
             for (int u = blockIdx.x; u < P.nunits && ok; u += gridDim.x) {
                 const Unit w = get_unit(u);
                 if (w.skip) continue;
-                // accumulators must have been drained by the epilogue of the previous unit
-                if (!(ok = ptx::mbar_wait_bounded(bar_accempty, phacc ^ 1u, abort_flag, WAIT_LIMIT))) break;
+                // this accumulator buffer must have been drained by the epilogue (NACC units ago)
+                if (!(ok = ptx::mbar_wait_bounded(bar_accempty(a), pha ^ 1u, abort_flag, WAIT_LIMIT))) break;
                 ptx::tc_fence_after();
+                const uint32_t d = tmem_base + (uint32_t)(a * BN_MAX);
                 for (int ks = 0; ks < w.ksteps; ++ks) {
                     if (!(ok = ptx::mbar_wait_bounded(bar_full(s), ph, abort_flag, WAIT_LIMIT))) break;
                     if (!(ok = ptx::mbar_wait_bounded(bar_lofull(c), phc, abort_flag, WAIT_LIMIT))) break;
                     ptx::tc_fence_after();
                     const uint32_t hi = stage0 + s * STAGE_BYTES, lo = lo0 + c * STAGE_BYTES;
-                    const uint64_t bh = ptx::smem_desc_sw64(hi + B_OFF), bl = ptx::smem_desc_sw64(lo + B_OFF);
-                    for (int t = 0; t < w.mt; ++t) {
-                        const uint64_t ah = ptx::smem_desc_sw64(hi + t * A_TILE_BYTES), al = ptx::smem_desc_sw64(lo + t * A_TILE_BYTES);
-                        const uint32_t d = tmem_base + (uint32_t)(t * P.bn);
+                    const uint64_t ah = ptx::smem_desc_sw128(hi), al = ptx::smem_desc_sw128(lo);
+                    const uint64_t bh = ptx::smem_desc_sw128(hi + B_OFF), bl = ptx::smem_desc_sw128(lo + B_OFF);
 #pragma unroll
-                        for (int k8 = 0; k8 < TK / 8; ++k8) {
-                            const uint64_t koff = (uint64_t)((k8 * 32) >> 4);  // 8 TF32 = 32 bytes along the swizzled row
-                            ptx::mma_tf32(d, al + koff, bh + koff, idesc, (ks | k8) ? 1u : 0u);  // small terms first
-                            ptx::mma_tf32(d, ah + koff, bl + koff, idesc, 1u);
-                            ptx::mma_tf32(d, ah + koff, bh + koff, idesc, 1u);
-                        }
+                    for (int k8 = 0; k8 < TK / 8; ++k8) {
+                        const uint64_t koff = (uint64_t)((k8 * 32) >> 4);  // 8 TF32 = 32 bytes along the swizzled row
+                        ptx::mma_tf32(d, al + koff, bh + koff, idesc, (ks | k8) ? 1u : 0u);  // small terms first
+                        ptx::mma_tf32(d, ah + koff, bl + koff, idesc, 1u);
+                        ptx::mma_tf32(d, ah + koff, bh + koff, idesc, 1u);
                     }
                     ptx::tc_commit(bar_empty(s));
                     ptx::tc_commit(bar_loempty(c));
@@ -176,36 +173,42 @@ legendre_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                     if (++c == NLO) { c = 0; phc ^= 1u; }
                 }
                 if (!ok) break;
-                ptx::tc_commit(bar_accfull);
-                phacc ^= 1u;
+                ptx::tc_commit(bar_accfull(a));
+                if (++a == NACC) { a = 0; pha ^= 1u; }
             }
         }
-    } else if (warp < 6) {
-        // =========================== splitter (128 threads) ===========================
+    } else if (warp < 2 + NSPLIT_WARPS) {
+        // =========================== splitter ===========================
         const int tid = threadIdx.x - 64;
+        constexpr int NT = 32 * NSPLIT_WARPS;
         int s = 0, c = 0;
         uint32_t ph = 0, phc = 0;
         bool ok = true;
+        const int na4 = A_TILE_BYTES / 16, nb4 = P.bn * TK * 4 / 16;
         for (int u = blockIdx.x; u < P.nunits && ok; u += gridDim.x) {
             const Unit w = get_unit(u);
             if (w.skip) continue;
-            const int na4 = w.mt * (A_TILE_BYTES / 16), nb4 = P.bn * TK * 4 / 16;
             for (int ks = 0; ks < w.ksteps; ++ks) {
                 if (!(ok = ptx::mbar_wait_bounded(bar_full(s), ph, abort_flag, WAIT_LIMIT))) break;
                 if (!(ok = ptx::mbar_wait_bounded(bar_loempty(c), phc ^ 1u, abort_flag, WAIT_LIMIT))) break;
                 float4 *src = reinterpret_cast<float4 *>(base_ptr + s * STAGE_BYTES);
                 float4 *dst = reinterpret_cast<float4 *>(base_ptr + (NSTAGE + c) * STAGE_BYTES);
-                for (int i = tid; i < na4; i += 128) {
-                    float4 v = src[i];
-                    dst[i] = make_float4(tf32_lo(v.x), tf32_lo(v.y), tf32_lo(v.z), tf32_lo(v.w));
-                    if (P.write_hi) src[i] = make_float4(tf32_hi(v.x), tf32_hi(v.y), tf32_hi(v.z), tf32_hi(v.w));
+                // the B tile follows the A tile directly; all loads of a thread are issued before the first store
+                constexpr int PER = (STAGE_BYTES / 16 + NT - 1) / NT;
+                const int n4 = na4 + nb4;
+                float4 v[PER];
+#pragma unroll
+                for (int j = 0; j < PER; ++j) {
+                    const int i = tid + j * NT;
+                    if (i < n4) v[j] = src[i];
                 }
-                float4 *srcb = src + B_OFF / 16;
-                float4 *dstb = dst + B_OFF / 16;
-                for (int i = tid; i < nb4; i += 128) {
-                    float4 v = srcb[i];
-                    dstb[i] = make_float4(tf32_lo(v.x), tf32_lo(v.y), tf32_lo(v.z), tf32_lo(v.w));
-                    if (P.write_hi) srcb[i] = make_float4(tf32_hi(v.x), tf32_hi(v.y), tf32_hi(v.z), tf32_hi(v.w));
+#pragma unroll
+                for (int j = 0; j < PER; ++j) {
+                    const int i = tid + j * NT;
+                    if (i < n4) {
+                        dst[i] = make_float4(tf32_lo(v[j].x), tf32_lo(v[j].y), tf32_lo(v[j].z), tf32_lo(v[j].w));
+                        if (P.write_hi) src[i] = make_float4(tf32_hi(v[j].x), tf32_hi(v[j].y), tf32_hi(v[j].z), tf32_hi(v[j].w));
+                    }
                 }
                 ptx::fence_proxy_async_smem();
                 ptx::mbar_arrive(bar_lofull(c));
@@ -214,49 +217,61 @@ legendre_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             }
         }
     } else {
-        // =========================== epilogue (128 threads) ===========================
-        const int q = warp & 3;            // TMEM lane quarter this warp may read
+        // =========================== epilogue (two warps per tensor-memory lane quarter) ===========================
+        const int ew = warp - (2 + NSPLIT_WARPS);
+        const int q = warp & 3;             // lane quarter this warp may read
+        const int half = ew >> 2;           // which half of the column chunks this warp handles
         const int row_in_tile = q * 32 + lane;
-        uint32_t phacc = 0;
+        int a = 0;
+        uint32_t pha = 0;
         bool ok = true;
+        const int nchunks = P.bn / 16;
+        const int c_begin = half ? (nchunks + 1) / 2 : 0, c_end = half ? nchunks : (nchunks + 1) / 2;
         for (int u = blockIdx.x; u < P.nunits && ok; u += gridDim.x) {
             const Unit w = get_unit(u);
             if (w.skip) continue;
-            if (!(ok = ptx::mbar_wait_bounded(bar_accfull, phacc, abort_flag, WAIT_LIMIT))) break;
-            phacc ^= 1u;
+            if (!(ok = ptx::mbar_wait_bounded(bar_accfull(a), pha, abort_flag, WAIT_LIMIT))) break;
             ptx::tc_fence_after();
             const int col0 = w.ntile * P.bn;
-            for (int t = 0; t < w.mt; ++t) {
-                const int r = t * TILE_M + row_in_tile;     // row inside the item
-                const bool rvalid = r < w.it.rows;
-                const int rg = w.it.r0 + r;                  // row inside the group
-                for (int cc = 0; cc < P.bn; cc += 16) {
-                    if (col0 + cc >= gp.ncols) break;        // warp-uniform
-                    float v[16];
-                    ptx::tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(t * P.bn + cc), v);
-                    if (!rvalid) continue;
-                    if (gp.mode == EPI_COEFFS) {
-                        const int l = w.it.m + w.it.p + 2 * rg;
-                        float2 *o = reinterpret_cast<float2 *>(gp.out) + (size_t)l * gp.mmax_out + (w.it.m - gp.m0);
-                        const size_t fstride = (size_t)gp.lmax * gp.mmax_out;
+            const bool rvalid = row_in_tile < w.it.rows;
+            const int rg = w.it.r0 + row_in_tile;  // row inside the group
+            const uint32_t trow = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * BN_MAX);
+            for (int ch = c_begin; ch < c_end; ++ch) {
+                const int cc = ch * 16;
+                if (col0 + cc >= gp.ncols) break;  // warp-uniform
+                float v[16];
+                ptx::tmem_ld16(trow + (uint32_t)cc, v);
+                if (!rvalid) continue;
+                if (gp.mode == EPI_COEFFS) {
+                    const int l = w.it.m + w.it.p + 2 * rg;
+                    float2 *o = reinterpret_cast<float2 *>(gp.out) + (size_t)l * gp.mmax_out + (w.it.m - gp.m0);
+                    const size_t fstride = (size_t)gp.lmax * gp.mmax_out;
 #pragma unroll
-                        for (int j = 0; j < 16; j += 2) {
-                            const int col = col0 + cc + j;
-                            if (col < gp.ncols) o[(size_t)(col >> 1) * fstride] = make_float2(v[j], v[j + 1]);
-                        }
-                    } else {
-                        const int g = 2 * (w.it.m - gp.m0) + w.it.p;
-                        float *o = gp.out + ((size_t)g * gp.ngroups_cols) * gp.out_ld + rg;
+                    for (int j = 0; j < 16; j += 2) {
+                        const int col = col0 + cc + j;
+                        if (col < gp.ncols) o[(size_t)(col >> 1) * fstride] = make_float2(v[j], v[j + 1]);
+                    }
+                } else if (gp.mode == EPI_SLABS) {
+                    const long long slab = gp.slab0[2 * w.it.m + w.it.p] - gp.slab_unit0 + (rg >> 5);
+                    float *o = gp.out + (size_t)slab * gp.ncols * kBK + (rg & 31);
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            const int col = col0 + cc + j;
-                            if (col < gp.ncols) o[(size_t)col * gp.out_ld] = v[j];
-                        }
+                    for (int j = 0; j < 16; ++j) {
+                        const int col = col0 + cc + j;
+                        if (col < gp.ncols) o[(size_t)col * kBK] = v[j];
+                    }
+                } else {
+                    const int g = 2 * (w.it.m - gp.m0) + w.it.p;
+                    float *o = gp.out + ((size_t)g * gp.ngroups_cols) * gp.out_ld + rg;
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int col = col0 + cc + j;
+                        if (col < gp.ncols) o[(size_t)col * gp.out_ld] = v[j];
                     }
                 }
             }
             ptx::tc_fence_before();
-            ptx::mbar_arrive(bar_accempty);
+            ptx::mbar_arrive(bar_accempty(a));
+            if (++a == NACC) { a = 0; pha ^= 1u; }
         }
     }
 
@@ -300,7 +315,7 @@ int make_map(CUtensorMap *tm, const float *base, long long inner, long long rows
     cuuint64_t strides[1] = {(cuuint64_t)pitch_floats * 4};
     cuuint32_t box[2] = {(cuuint32_t)TK, (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void *)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
+    CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void *)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                     CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(SHTB200_ECUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
     return SHTB200_OK;
@@ -337,7 +352,7 @@ int launch_gemm_tc(const Plan &pl, const GemmParams &gp, cudaStream_t st) {
     }
 
     // extents of the two operands as 2-D row-major tensors
-    const bool analysis = gp.mode == EPI_COEFFS;
+    const bool analysis = gp.mode != EPI_LATROWS;
     long long a_rows, a_inner, b_rows, b_inner;
     if (analysis) {
         a_inner = gp.a_kext;

@@ -113,6 +113,55 @@ __global__ void pack_coeffs_kernel(const float2 *__restrict__ c, float *__restri
     }
 }
 
+// Scalar fast path, both directions: tiled transpose between the coefficient array c[field][l][m] (m contiguous)
+// and the degree-slab layout S[(slab0[g] + r / 32) * ncols + 2 field + re/im][r % 32] with r = (l - m - p) / 2.
+// One CTA moves a 64 (degrees) x 32 (orders) tile of one field through shared memory so that both sides see
+// full 128- or 256-byte runs.  TO_SLABS also writes the zero padding of the last slab of every group;
+// the reverse direction also writes the exact zeros of the l < m triangle.
+template <bool TO_SLABS>
+__global__ void __launch_bounds__(256) coeff_slab_transpose_kernel(float2 *__restrict__ c, float *__restrict__ S, const long long *__restrict__ slab0,
+                                                                   const int *__restrict__ gkb, int ncols, int lmax, int mloc, int m0) {
+    __shared__ float tre[64][33], tim[64][33];
+    const int mb0 = blockIdx.x * 32, l0 = blockIdx.y * 64, f = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long unit0 = slab0[2 * m0];
+
+    if (TO_SLABS) {
+        for (int r = warp; r < 64; r += 8) {
+            const int l = l0 + r, mi = mb0 + lane;
+            float2 z = make_float2(0.f, 0.f);
+            if (l < lmax && mi < mloc) z = c[((size_t)f * lmax + l) * mloc + mi];
+            tre[r][lane] = z.x;
+            tim[r][lane] = z.y;
+        }
+        __syncthreads();
+    }
+    // 32 orders x 2 parities x (re, im) = 128 runs of up to 32 consecutive r
+    for (int task = warp; task < 128; task += 8) {
+        const int ml = task >> 2, p = (task >> 1) & 1, ri = task & 1;
+        const int mi = mb0 + ml;
+        if (mi >= mloc) continue;
+        const int m = m0 + mi, g = 2 * m + p;
+        const int l = l0 + ((m + p) & 1) + 2 * lane;  // l0 is even: degrees of this parity inside the tile
+        const int r = (l - m - p) >> 1;               // arithmetic shift: negative when l < m + p
+        float(*t)[33] = ri ? tim : tre;
+        if (TO_SLABS) {
+            if (l >= m + p && r < gkb[g] * kBK) S[((size_t)(slab0[g] - unit0 + (r >> 5)) * ncols + 2 * f + ri) * kBK + (r & 31)] = t[l - l0][ml];
+        } else {
+            float v = 0.f;
+            if (l >= m + p && l < lmax) v = S[((size_t)(slab0[g] - unit0 + (r >> 5)) * ncols + 2 * f + ri) * kBK + (r & 31)];
+            t[l - l0][ml] = v;
+        }
+    }
+    if (!TO_SLABS) {
+        __syncthreads();
+        for (int r = warp; r < 64; r += 8) {
+            const int l = l0 + r, mi = mb0 + lane;
+            if (l < lmax && mi < mloc) c[((size_t)f * lmax + l) * mloc + mi] = make_float2(tre[r][lane], tim[r][lane]);
+        }
+    }
+}
+
 __global__ void zero_upper_kernel(float2 *c, long long nfl, int lmax, int mloc, int m0) {
     // one thread per (field * l, m) element; only the l < m ones are written
     const long long total = nfl * mloc;
@@ -195,9 +244,25 @@ int launch_pack_table(Plan &pl, const float *table, cudaStream_t st) {
 int launch_pack_coeffs(const Plan &pl, const float2 *c, float *Ct, int nfields, int m0, int mloc, cudaStream_t st) {
     const int ncols = (pl.vector ? 4 : 2) * nfields;
     if (mloc == 0 || ncols == 0) return SHTB200_OK;
+    if (!pl.vector && nfields <= 65535) {
+        dim3 grid(ceil_div(mloc, 32), ceil_div(pl.lmax + 64, 64), nfields);
+        coeff_slab_transpose_kernel<true><<<grid, 256, 0, st>>>(const_cast<float2 *>(c), Ct, pl.d_gb0, pl.d_gkb, ncols, pl.lmax, mloc, m0);
+        SHT_CUDA_CHECK(cudaGetLastError());
+        return SHTB200_OK;
+    }
     const long long per_group = (long long)ceil_div(pl.Lh, kBK) * pl.ncomp * ncols * kBK;
     dim3 grid(grid_x_for(per_group), 2 * mloc);
     pack_coeffs_kernel<<<grid, 256, 0, st>>>(c, Ct, pl.d_gb0, pl.d_gkb, pl.d_gkb0, ncols, pl.lmax, mloc, m0, pl.vector ? 1 : 0);
+    SHT_CUDA_CHECK(cudaGetLastError());
+    return SHTB200_OK;
+}
+
+int launch_unpack_coeffs(const Plan &pl, const float *Z, float2 *c, int nfields, int m0, int mloc, cudaStream_t st) {
+    if (pl.vector) return fail(SHTB200_EINVAL, "slab output is implemented for the scalar kinds only");
+    if (mloc == 0 || nfields == 0) return SHTB200_OK;
+    if (nfields > 65535) return fail(SHTB200_EINVAL, "too many fields in one call (limit 65535)");
+    dim3 grid(ceil_div(mloc, 32), ceil_div(pl.lmax, 64), nfields);
+    coeff_slab_transpose_kernel<false><<<grid, 256, 0, st>>>(c, const_cast<float *>(Z), pl.d_gb0, pl.d_gkb, 2 * nfields, pl.lmax, mloc, m0);
     SHT_CUDA_CHECK(cudaGetLastError());
     return SHTB200_OK;
 }

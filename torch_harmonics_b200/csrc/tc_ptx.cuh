@@ -111,6 +111,16 @@ __device__ __forceinline__ uint64_t smem_desc_sw64(uint32_t smem_addr) {
     d |= (uint64_t)4 << 61;                        // layout type SWIZZLE_64B, bits [61, 64)
     return d;
 }
+// Same for the 128-byte swizzle (rows of 32 floats; 8-row groups 1024 bytes apart).
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024u >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;  // layout type SWIZZLE_128B
+    return d;
+}
 // Instruction descriptor: fp32 accumulator, TF32 x TF32, both K-major, M = 128, N = n.
 __device__ __forceinline__ uint32_t idesc_tf32_m128(uint32_t n) { return (1u << 4) | (2u << 7) | (2u << 10) | ((n >> 3) << 17) | ((128u >> 4) << 24); }
 

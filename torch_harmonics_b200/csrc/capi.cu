@@ -56,13 +56,14 @@ struct WsLayout {
 WsLayout ws_layout(const Plan &pl, int nfields, int m0, int mloc) {
     WsLayout w;
     const size_t ncols = (size_t)(pl.vector ? 4 : 2) * nfields;
+    const size_t ncp = (ncols + 3) / 4 * 4;  // row pitch of the column-contiguous operands
     if (pl.analysis) {
-        w.op_bytes = (size_t)2 * mloc * ncols * pl.ncomp * pl.Kp * sizeof(float);
+        w.op_bytes = (size_t)2 * mloc * pl.Ka * ncp * sizeof(float);
         if (!pl.vector) w.y_bytes = (size_t)(pl.group_b0[2 * (m0 + mloc)] - pl.group_b0[2 * m0]) * ncols * kBK * sizeof(float);
     } else {
         const long long slabs = pl.group_b0[2 * (m0 + mloc)] - pl.group_b0[2 * m0];
         w.op_bytes = (size_t)slabs * ncols * kBK * sizeof(float);
-        w.y_bytes = (size_t)2 * mloc * ncols * pl.Kp * sizeof(float);
+        w.y_bytes = (size_t)2 * mloc * pl.Kh * ncp * sizeof(float);
     }
     return w;
 }
@@ -82,9 +83,11 @@ GemmParams gemm_params(const Plan &pl, int nfields, int m0, int mloc, const floa
     gp.mmax_out = mloc;
     gp.m0 = m0;
     if (pl.analysis) {
-        gp.b_pitch = (long long)pl.ncomp * pl.Kp;
+        gp.b_mn = 1;
+        gp.b_krows = pl.Ka;
+        gp.b_pitch = round_up(gp.ncols, 4);
         gp.b_dx = kBK;
-        gp.b_kext = pl.vector ? 2 * pl.Kp : pl.Kh;
+        gp.b_kext = pl.Ka;
         gp.b_unit0 = 2 * m0;
         gp.mode = pl.vector ? EPI_COEFFS : EPI_SLABS;
         gp.slab0 = pl.d_gb0;
@@ -95,8 +98,8 @@ GemmParams gemm_params(const Plan &pl, int nfields, int m0, int mloc, const floa
         gp.b_kext = kBK;
         gp.b_unit0 = pl.group_b0[2 * m0];
         gp.mode = EPI_LATROWS;
-        gp.out_ld = pl.Kp;
-        gp.ngroups_cols = gp.ncols;
+        gp.out_ld = round_up(gp.ncols, 4);
+        gp.out_rows = pl.Kh;
     }
     return gp;
 }
@@ -123,7 +126,8 @@ int run_gemm(Plan &pl, const GemmParams &gp, cudaStream_t st) {
 int clear_empty_groups(const Plan &pl, float *Y, int ncols, int m0, int mloc, cudaStream_t st) {
     for (int g = 2 * m0; g < 2 * (m0 + mloc); ++g) {
         if (pl.group_kblocks[g] == 0) {
-            SHT_CUDA_CHECK(cudaMemsetAsync(Y + (size_t)(g - 2 * m0) * ncols * pl.Kp, 0, sizeof(float) * (size_t)ncols * pl.Kp, st));
+            const size_t slice = (size_t)pl.Kh * round_up(ncols, 4);
+            SHT_CUDA_CHECK(cudaMemsetAsync(Y + (size_t)(g - 2 * m0) * slice, 0, sizeof(float) * slice, st));
         }
     }
     return SHTB200_OK;
@@ -222,7 +226,7 @@ int shtb200_plan_create(shtb200_plan **plan_out, int kind, int nlat, int nlon, i
     pl->vector = is_vector(kind);
     pl->ncomp = pl->vector ? 2 : 1;
     pl->Kh = (nlat + 1) / 2;
-    pl->Kp = (int)round_up(pl->Kh, 8);
+    pl->Ka = pl->ncomp * pl->Kh;
     pl->Lh = (lmax + 1) / 2;
     pl->negate_seg1 = (kind == SHTB200_VSHT_ADJOINT || kind == SHTB200_IVSHT_ADJOINT) ? 1 : 0;
 
@@ -260,9 +264,9 @@ int shtb200_plan_create(shtb200_plan **plan_out, int kind, int nlat, int nlon, i
     pl->group_b0.assign(ngroups + 1, 0);
     std::vector<int> kb0(ngroups, 0);
     if (pl->analysis) {
-        pl->a_pitch = (long long)pl->ncomp * pl->Kp;
+        pl->a_pitch = round_up(pl->Ka, 8);
         pl->a_dx = kBK;
-        pl->a_kext = pl->vector ? 2 * pl->Kp : pl->Kh;
+        pl->a_kext = pl->Ka;
         for (int g = 0; g < ngroups; ++g) {
             pl->group_a0[g + 1] = pl->group_a0[g] + pl->group_rows[g];
             // degree slabs of the contraction's output (same layout the synthesis side reads)
@@ -271,7 +275,7 @@ int shtb200_plan_create(shtb200_plan **plan_out, int kind, int nlat, int nlon, i
         }
         pl->total_b_slabs = pl->group_b0[ngroups];
         pl->table_floats = (size_t)(pl->group_a0[ngroups] + kItemRowsMax) * pl->a_pitch;
-        const int kblocks = ceil_div(pl->vector ? 2 * pl->Kp : pl->Kh, kBK);
+        const int kblocks = ceil_div(pl->Ka, kBK);
         for (int g = 0; g < ngroups; ++g)
             for (int r0 = 0; r0 < pl->group_rows[g]; r0 += kItemRowsMax) {
                 GemmItem it{};

@@ -70,7 +70,7 @@ constexpr int kItemRowsMax = 128;  // one 128-row tensor-core tile
 // How a finished tile leaves the contraction kernel.
 enum EpilogueMode : int {
     EPI_COEFFS = 0,   // analysis: rows are degrees l = m + p + 2 r  -> complex64 out[n][l][m - m0]
-    EPI_LATROWS = 1,  // synthesis: rows are folded latitudes k'      -> float Y[group][col][k'] (row pitch ld)
+    EPI_LATROWS = 1,  // synthesis: rows are folded latitudes k'      -> float Y[group * out_rows + k'][col] (row pitch ld)
     EPI_SLABS = 2,    // analysis: rows are degrees -> float Z[(slab0[g] + r / 32) * ncols + col][r % 32], the same
                       // degree-slab layout the synthesis contraction reads its coefficients from
 };
@@ -82,6 +82,8 @@ struct GemmParams {
     long long b_pitch;    // floats per operand row
     int a_dx, b_dx;       // see above
     int a_kext, b_kext;   // valid extent of the inner (k) axis of a row (reads beyond it yield 0)
+    int b_mn;             // 1: B is column-contiguous, element (col, k) of group u at B[((u - b_unit0) * b_krows + k) * b_pitch + col]
+    int b_krows;          // b_mn: rows (contraction indices) per group
     int ncols;            // columns of the product = 2 * nfields (4 * pairs for vector kinds)
     long long b_unit0;    // operand origin (same units as GemmItem::b_y0) of the first order held in B
     const GemmItem *items;
@@ -90,8 +92,8 @@ struct GemmParams {
     float *out;           // destination
     int lmax, mmax_out;   // EPI_COEFFS: out dims (mmax_out = number of orders stored = mloc)
     int m0;               // first order stored in out (orders outside [m0, m0 + mmax_out) are skipped)
-    long long out_ld;     // EPI_LATROWS: floats per (group, col) row of Y
-    int ngroups_cols;     // EPI_LATROWS: columns per group in Y (= ncols)
+    long long out_ld;     // EPI_LATROWS: floats per row of Y[(group * out_rows + k')][col]
+    int out_rows;         // EPI_LATROWS: rows per group of Y
     const long long *slab0;  // EPI_SLABS: first slab of every group (device array, 2 * mmax + 1 entries)
     long long slab_unit0;    // EPI_SLABS: slab0 of the first order held in the output
 };
@@ -103,7 +105,7 @@ struct Plan {
     int kind = 0, engine = 0, device = 0;
     int nlat = 0, nlon = 0, lmax = 0, mmax = 0;
     int Kh = 0;   // folded latitude count, (nlat + 1) / 2
-    int Kp = 0;   // floats per row of a latitude-indexed operand (Kh rounded up to 8)
+    int Ka = 0;   // contraction length of the analysis kinds, ncomp * Kh
     int Lh = 0;   // largest number of degrees of one parity, (lmax + 1) / 2
     bool analysis = false;  // grid -> spectral
     bool vector = false;
@@ -152,9 +154,9 @@ struct Plan {
 // ------------------------------------------------------------------------------------------------
 int build_fft_plan(int nlon, FftPlanDev *out, float2 **d_tw, unsigned short **d_perm);
 
-// analysis: rows of x -> folded, order-major operand X[group][col][k'] (row pitch Kp)
+// analysis: rows of x -> folded, order-major operand X[group * Ka + k][col] (row pitch round_up(ncols, 4))
 int launch_fft_analysis(const Plan &pl, const float *x, float *X, int nfields, cudaStream_t st);
-// synthesis: Y[group][col][k'] -> rows of x
+// synthesis: Y[group * Kh + k'][col] -> rows of x
 int launch_fft_synthesis(const Plan &pl, const float *Y, float *x, int nfields, cudaStream_t st);
 // plain row transforms for the distributed stages
 int launch_rfft_modes(const float *in, float2 *out, long long nrows, int nlon, int nmodes, float scale, cudaStream_t st);

@@ -1,14 +1,15 @@
 // Longitude transforms of the SHT: shared-memory mixed-radix FFT kernels.
 //
 // Analysis (grid -> order-major operand of the Legendre contraction), per CTA:
-//   * P pairs of latitude rows (k', nlat-1-k') of one field are loaded with coalesced float4 reads
+//   * one pair of latitude rows (k', nlat-1-k') of each of eight fields is loaded with coalesced float4 reads
 //     and folded about the equator: z_j = (x_north + x_south) + i (x_north - x_south).  The even /
 //     odd combinations are what the parity-split Legendre tables contract with, and one complex
 //     transform of z yields the spectra of both real rows at once.
 //   * an in-place decimation-in-frequency FFT of length nlon runs in shared memory (radix 4, 2, 3, 5
 //     butterflies; any other prime factor <= 31 goes through a generic butterfly),
 //   * only the retained orders m < mmax are written, already transposed into the contraction's
-//     operand layout X[group = 2 m + parity][column = 2 field + re/im][k'] (k' contiguous).
+//     operand layout X[group = 2 m + parity][k'][column = 2 field + re/im] (columns contiguous; a CTA
+//     covers eight consecutive fields so that every write is a full 64-byte run).
 // Synthesis is the mirror image: gather the two parities, rebuild the Hermitian spectrum of
 // (north + i south), decimation-in-time inverse FFT, coalesced float4 row stores.
 //
@@ -309,10 +310,18 @@ __device__ void generic_butterfly(float2 *p, int R, int str, const float2 *tw, i
     }
 }
 
-// All passes of ONE transform of length n, carried by one warp (in place, __syncwarp between passes).
-// Forward: natural order in, bin k at slot perm[k] out.  Inverse: bin k at slot perm[k] in, natural order out.
-template <bool INV>
-__device__ void fft_warp(float2 *d, const FftPlanDev &fp, const float2 *tw_s, int lane) {
+// Barrier among the G warps that share one transform (named barrier `id`; plain __syncwarp when G = 1).
+template <int G>
+__device__ __forceinline__ void group_sync(int id) {
+    if (G == 1) __syncwarp();
+    else asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(32 * G) : "memory");
+}
+
+// All passes of ONE transform of length n, carried by G warps (in place, group barrier between passes).
+// `lane` is the thread's index inside the group.  Forward: natural order in, bin k at slot perm[k] out.
+// Inverse: bin k at slot perm[k] in, natural order out.
+template <bool INV, int G>
+__device__ void fft_group(float2 *d, const FftPlanDev &fp, const float2 *tw_s, int lane, int bar_id) {
     const int n = fp.n;
     for (int ss = 0; ss < fp.nstages; ++ss) {
         const int s = INV ? fp.nstages - 1 - ss : ss;
@@ -322,7 +331,7 @@ __device__ void fft_warp(float2 *d, const FftPlanDev &fp, const float2 *tw_s, in
         const int nb = n / R;  // butterflies in this pass
         const bool has_tw = Ls > 1;
         const float2 *tw = tw_s + fp.twoff[s];
-        for (int i = lane; i < nb; i += 32) {
+        for (int i = lane; i < nb; i += 32 * G) {
             const int b = i / Ls;
             const int j = i - b * Ls;
             float2 *p = d + b * L + j;
@@ -341,7 +350,7 @@ __device__ void fft_warp(float2 *d, const FftPlanDev &fp, const float2 *tw_s, in
                 default: generic_butterfly<INV>(p, R, Ls, tw + j, Ls, has_tw, fp.tw_full, n);
             }
         }
-        __syncwarp();
+        group_sync<G>(bar_id);
     }
 }
 
@@ -352,69 +361,42 @@ __device__ __forceinline__ void load_tables(const FftPlanDev &fp, float2 *tw_s, 
 }
 
 // ------------------------------------------------------------------------------------------------
-// small helpers: runs of P consecutive floats along k' (P = 2, 4 or 8; 8-byte / 16-byte aligned)
-// ------------------------------------------------------------------------------------------------
-template <int P>
-__device__ __forceinline__ void store_run(float *dst, const float *v) {
-    if (P % 4 == 0) {
-#pragma unroll
-        for (int q = 0; q < P; q += 4) *reinterpret_cast<float4 *>(dst + q) = make_float4(v[q], v[q + 1], v[q + 2], v[q + 3]);
-    } else {
-#pragma unroll
-        for (int q = 0; q < P; q += 2) *reinterpret_cast<float2 *>(dst + q) = make_float2(v[q], v[q + 1]);
-    }
-}
-template <int P>
-__device__ __forceinline__ void load_run(const float *src, float *v) {
-    if (P % 4 == 0) {
-#pragma unroll
-        for (int q = 0; q < P; q += 4) {
-            float4 a = *reinterpret_cast<const float4 *>(src + q);
-            v[q] = a.x; v[q + 1] = a.y; v[q + 2] = a.z; v[q + 3] = a.w;
-        }
-    } else {
-#pragma unroll
-        for (int q = 0; q < P; q += 2) {
-            float2 a = *reinterpret_cast<const float2 *>(src + q);
-            v[q] = a.x; v[q + 1] = a.y;
-        }
-    }
-}
-
-// ------------------------------------------------------------------------------------------------
 // analysis kernel
 // ------------------------------------------------------------------------------------------------
-// grid: (Kp / P, nfields), block: NW warps, one transform per warp.  VEC = 1: scalar fields, P = NW row pairs;
-// VEC = 2: (theta, phi) component pairs, P = NW / 2 row pairs of each component.
+// grid: (ceil(nfields / (NW / VEC)), Kh), block: NW transforms x G warps.  A CTA takes ONE pair of latitude rows
+// (k', nlat-1-k') of NW / VEC consecutive fields (VEC = 1: scalar fields; VEC = 2: (theta, phi) component pairs), so
+// that what it emits for an order m is one contiguous run of 2 NW floats along the column axis of the operand.
 //
-// Scalar operand layout   X[(2 m + p) * ncols + 2 f + ri][k'],  p = 0 even fold, p = 1 odd fold.
-// Vector operand layout   X[(2 m + p) * ncols + 4 f + c][seg * Kp + k'] with seg 0 contracting against
-// the d/dtheta table (fold parity opposite to p) and seg 1 against the m/sin(theta) table (fold parity p);
-// the four columns c carry the sign pattern of torch_harmonics/sht.py:488-493:
-//   c0 (s_re): [ Re X0 | -Im X1 ]   c1 (s_im): [ Im X0 |  Re X1 ]
-//   c2 (t_re): [-Re X1 | -Im X0 ]   c3 (t_im): [-Im X1 |  Re X0 ]
-template <int NW, int VEC>
-__global__ void __launch_bounds__(32 * NW) fft_analysis_kernel(const float *__restrict__ x, float *__restrict__ X, FftPlanDev fp, int nlat, int Kh, int Kp,
-                                                               int mmax, int ncols, const float *__restrict__ mscale, int zero_imag_edges, int vec4ok) {
+// Operand layout (column-contiguous):  X[(2 m + p) * Ka + kk][col],  row pitch ncp floats, Ka = VEC * Kh.
+//   scalar:  kk = k',  col = 2 f + (re, im);  p = 0 holds the even fold, p = 1 the odd fold.
+//   vector:  col = 4 f + c;  kk = k' contracts against the d/dtheta table and carries the fold of parity 1 - p,
+//            kk = Kh + k' contracts against the m/sin(theta) table and carries the fold of parity p; the four
+//            columns c follow the sign pattern of torch_harmonics/sht.py:488-493:
+//              c0 (s_re): [ Re X0 | -Im X1 ]   c1 (s_im): [ Im X0 |  Re X1 ]
+//              c2 (t_re): [-Re X1 | -Im X0 ]   c3 (t_im): [-Im X1 |  Re X0 ]
+template <int NW, int VEC, int G>
+__global__ void __launch_bounds__(32 * NW * G, (NW * G >= 16) ? 2 : 1) fft_analysis_kernel(const float *__restrict__ x, float *__restrict__ X, FftPlanDev fp,
+                                                                                            int nlat, int Kh, int nfields, int ncp, int mmax,
+                                                                                            const float *__restrict__ mscale, int zero_imag_edges, int vec4ok) {
     extern __shared__ float2 smem[];
     const int n = fp.n;
-    constexpr int P = NW / VEC;
+    constexpr int NF = NW / VEC;                    // fields (or component pairs) per CTA
+    constexpr int GT = 32 * G;                      // threads per transform
     float2 *data = smem;
     float2 *tw_s = data + (size_t)NW * n;
     unsigned short *perm_s = reinterpret_cast<unsigned short *>(tw_s + fp.tw_pass_total);
 
-    const int f = blockIdx.y;
-    const int k0 = blockIdx.x * P;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int kn = blockIdx.y;
+    const int f0 = blockIdx.x * NF;  // field blocks vary fastest: CTAs that complete each other's 128-byte lines run together
+    const int t = threadIdx.x / GT, lane = threadIdx.x % GT;  // transform index, index inside its group
     load_tables(fp, tw_s, perm_s);
 
-    // ---- each warp loads and folds its own pair of rows ----
+    // ---- each group loads and folds its own pair of rows ----
     {
-        const int q = warp % P, comp = warp / P;
-        const int kn = k0 + q;
-        float2 *dst = data + (size_t)warp * n;
-        if (kn >= Kh) {
-            for (int j = lane; j < n; j += 32) dst[j] = make_float2(0.f, 0.f);
+        const int f = f0 + t / VEC, comp = t % VEC;
+        float2 *dst = data + (size_t)t * n;
+        if (f >= nfields) {
+            for (int j = lane; j < n; j += GT) dst[j] = make_float2(0.f, 0.f);
         } else {
             const int ks = nlat - 1 - kn;
             const float *rn = x + ((size_t)(f * VEC + comp) * nlat + kn) * n;
@@ -423,16 +405,31 @@ __global__ void __launch_bounds__(32 * NW) fft_analysis_kernel(const float *__re
             if ((n % 4 == 0) && vec4ok) {
                 const float4 *rn4 = reinterpret_cast<const float4 *>(rn);
                 const float4 *rs4 = reinterpret_cast<const float4 *>(rs);
-                for (int j = lane; j < n / 4; j += 32) {
-                    float4 a = __ldg(rn4 + j);
-                    float4 b = self ? make_float4(0.f, 0.f, 0.f, 0.f) : __ldg(rs4 + j);
-                    float4 o = self ? make_float4(0.f, 0.f, 0.f, 0.f) : make_float4(a.x - b.x, a.y - b.y, a.z - b.z, a.w - b.w);
-                    float4 *d4 = reinterpret_cast<float4 *>(dst + 4 * j);
-                    d4[0] = make_float4(a.x + b.x, o.x, a.y + b.y, o.y);
-                    d4[1] = make_float4(a.z + b.z, o.z, a.w + b.w, o.w);
+                constexpr int U = 3;  // loads in flight per thread: 2 U float4
+                const int n4 = n / 4;
+                for (int j0 = lane; j0 < n4; j0 += GT * U) {
+                    float4 a[U], b[U];
+#pragma unroll
+                    for (int u = 0; u < U; ++u) {
+                        const int j = j0 + GT * u;
+                        if (j < n4) {
+                            a[u] = __ldg(rn4 + j);
+                            b[u] = self ? make_float4(0.f, 0.f, 0.f, 0.f) : __ldg(rs4 + j);
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < U; ++u) {
+                        const int j = j0 + GT * u;
+                        if (j < n4) {
+                            float4 o = self ? make_float4(0.f, 0.f, 0.f, 0.f) : make_float4(a[u].x - b[u].x, a[u].y - b[u].y, a[u].z - b[u].z, a[u].w - b[u].w);
+                            float4 *d4 = reinterpret_cast<float4 *>(dst + 4 * j);
+                            d4[0] = make_float4(a[u].x + b[u].x, o.x, a[u].y + b[u].y, o.y);
+                            d4[1] = make_float4(a[u].z + b[u].z, o.z, a[u].w + b[u].w, o.w);
+                        }
+                    }
                 }
             } else {
-                for (int j = lane; j < n; j += 32) {
+                for (int j = lane; j < n; j += GT) {
                     float a = __ldg(rn + j);
                     float b = self ? 0.f : __ldg(rs + j);
                     dst[j] = self ? make_float2(a, 0.f) : make_float2(a + b, a - b);
@@ -442,62 +439,60 @@ __global__ void __launch_bounds__(32 * NW) fft_analysis_kernel(const float *__re
     }
     __syncthreads();  // tables and rows in place
 
-    fft_warp<false>(data + (size_t)warp * n, fp, tw_s, lane);
+    fft_group<false, G>(data + (size_t)t * n, fp, tw_s, lane, 1 + t);
     __syncthreads();
 
-    // ---- emit the retained orders ----
+    // ---- emit the retained orders: one thread per order, 2 NW floats per (order, fold) ----
     const int nyq = n / 2;
+    const int Ka = VEC * Kh;
     for (int m = threadIdx.x; m < mmax; m += blockDim.x) {
-        float e_re[NW], e_im[NW], o_re[NW], o_im[NW];
+        float e[2 * NW], o[2 * NW];  // (re, im) of the even / odd fold of every transform
         if (m <= nyq) {
             const float sc = 0.5f * mscale[m];
             const int pm = perm_s[m];
             const int pn = perm_s[m == 0 ? 0 : n - m];
             const bool edge = zero_imag_edges && (m == 0 || (2 * m == n));
 #pragma unroll
-            for (int t = 0; t < NW; ++t) {
-                float2 zm = data[(size_t)t * n + pm];
-                float2 zn = data[(size_t)t * n + pn];
+            for (int u = 0; u < NW; ++u) {
+                float2 zm = data[(size_t)u * n + pm];
+                float2 zn = data[(size_t)u * n + pn];
                 // spectra of the two real rows packed in z = even + i odd
-                e_re[t] = sc * (zm.x + zn.x);
-                e_im[t] = edge ? 0.f : sc * (zm.y - zn.y);
-                o_re[t] = sc * (zm.y + zn.y);
-                o_im[t] = edge ? 0.f : sc * (zn.x - zm.x);
+                e[2 * u] = sc * (zm.x + zn.x);
+                e[2 * u + 1] = edge ? 0.f : sc * (zm.y - zn.y);
+                o[2 * u] = sc * (zm.y + zn.y);
+                o[2 * u + 1] = edge ? 0.f : sc * (zn.x - zm.x);
             }
         } else {
 #pragma unroll
-            for (int t = 0; t < NW; ++t) e_re[t] = e_im[t] = o_re[t] = o_im[t] = 0.f;
+            for (int u = 0; u < 2 * NW; ++u) e[u] = o[u] = 0.f;
         }
         if (VEC == 1) {
-            float *g0 = X + ((size_t)(2 * m) * ncols + 2 * f) * Kp + k0;
-            float *g1 = X + ((size_t)(2 * m + 1) * ncols + 2 * f) * Kp + k0;
-            store_run<P>(g0, e_re);
-            store_run<P>(g0 + Kp, e_im);
-            store_run<P>(g1, o_re);
-            store_run<P>(g1 + Kp, o_im);
+            float *ge = X + ((size_t)(2 * m) * Ka + kn) * ncp + 2 * f0;
+            float *go = X + ((size_t)(2 * m + 1) * Ka + kn) * ncp + 2 * f0;
+#pragma unroll
+            for (int c = 0; c < 2 * NW; c += 4) {
+                if (2 * f0 + c < ncp) {
+                    *reinterpret_cast<float4 *>(ge + c) = make_float4(e[c], e[c + 1], e[c + 2], e[c + 3]);
+                    *reinterpret_cast<float4 *>(go + c) = make_float4(o[c], o[c + 1], o[c + 2], o[c + 3]);
+                }
+            }
         } else {
-            // component 0 occupies t in [0, P), component 1 t in [P, 2P)
-            const size_t pitch = 2 * (size_t)Kp;
+            // transforms 2 q (theta component X0) and 2 q + 1 (phi component X1) of pair q
 #pragma unroll
             for (int p = 0; p < 2; ++p) {
-                float *g = X + ((size_t)(2 * m + p) * ncols + 4 * f) * pitch + k0;
-                float c0a[P], c0b[P], c1a[P], c1b[P], c2a[P], c2b[P], c3a[P], c3b[P];
-                // seg 0 (d/dtheta table) takes the fold of parity 1 - p (suffix a), seg 1 the fold of parity p (suffix b)
+                float *ga = X + ((size_t)(2 * m + p) * Ka + kn) * ncp + 4 * f0;       // d/dtheta rows: fold 1 - p
+                float *gb = X + ((size_t)(2 * m + p) * Ka + Kh + kn) * ncp + 4 * f0;  // m/sin(theta) rows: fold p
+                const float *fa = p ? e : o;
+                const float *fb = p ? o : e;
 #pragma unroll
-                for (int q = 0; q < P; ++q) {
-                    const float x0re_a = p ? e_re[q] : o_re[q], x0im_a = p ? e_im[q] : o_im[q];
-                    const float x1re_a = p ? e_re[P + q] : o_re[P + q], x1im_a = p ? e_im[P + q] : o_im[P + q];
-                    const float x0re_b = p ? o_re[q] : e_re[q], x0im_b = p ? o_im[q] : e_im[q];
-                    const float x1re_b = p ? o_re[P + q] : e_re[P + q], x1im_b = p ? o_im[P + q] : e_im[P + q];
-                    c0a[q] = x0re_a;  c0b[q] = -x1im_b;
-                    c1a[q] = x0im_a;  c1b[q] = x1re_b;
-                    c2a[q] = -x1re_a; c2b[q] = -x0im_b;
-                    c3a[q] = -x1im_a; c3b[q] = x0re_b;
+                for (int q = 0; q < NF; ++q) {
+                    if (4 * (f0 + q) < ncp) {
+                        const float x0re_a = fa[4 * q], x0im_a = fa[4 * q + 1], x1re_a = fa[4 * q + 2], x1im_a = fa[4 * q + 3];
+                        const float x0re_b = fb[4 * q], x0im_b = fb[4 * q + 1], x1re_b = fb[4 * q + 2], x1im_b = fb[4 * q + 3];
+                        *reinterpret_cast<float4 *>(ga + 4 * q) = make_float4(x0re_a, x0im_a, -x1re_a, -x1im_a);
+                        *reinterpret_cast<float4 *>(gb + 4 * q) = make_float4(-x1im_b, x1re_b, -x0im_b, x0re_b);
+                    }
                 }
-                store_run<P>(g + 0 * pitch, c0a); store_run<P>(g + 0 * pitch + Kp, c0b);
-                store_run<P>(g + 1 * pitch, c1a); store_run<P>(g + 1 * pitch + Kp, c1b);
-                store_run<P>(g + 2 * pitch, c2a); store_run<P>(g + 2 * pitch + Kp, c2b);
-                store_run<P>(g + 3 * pitch, c3a); store_run<P>(g + 3 * pitch + Kp, c3b);
             }
         }
     }
@@ -506,21 +501,25 @@ __global__ void __launch_bounds__(32 * NW) fft_analysis_kernel(const float *__re
 // ------------------------------------------------------------------------------------------------
 // synthesis kernel
 // ------------------------------------------------------------------------------------------------
-// Scalar: Y[(2 m + p) * ncols + 2 f + ri][k'] holds the even (p = 0) / odd (p = 1) latitude parts of order m.
-// Vector: Y[(2 m + p) * ncols + 4 f + c][k'] with c = (theta re, theta im, phi re, phi im).
-template <int NW, int VEC>
-__global__ void __launch_bounds__(32 * NW) fft_synthesis_kernel(const float *__restrict__ Y, float *__restrict__ x, FftPlanDev fp, int nlat, int Kh, int Kp,
-                                                                int mmax, int ncols, const float *__restrict__ mscale, int vec4ok) {
+// Y[(2 m + p) * Kh + k'][col] (row pitch ncp) holds the even (p = 0) / odd (p = 1) latitude parts of order m;
+// col = 2 f + (re, im) for scalar fields, 4 f + (theta re, theta im, phi re, phi im) for vector pairs: in both
+// cases transform u of the CTA reads columns 2 u, 2 u + 1 past the CTA's first column.
+template <int NW, int VEC, int G>
+__global__ void __launch_bounds__(32 * NW * G, (NW * G >= 16) ? 2 : 1) fft_synthesis_kernel(const float *__restrict__ Y, float *__restrict__ x, FftPlanDev fp,
+                                                                                             int nlat, int Kh, int nfields, int ncp, int mmax,
+                                                                                             const float *__restrict__ mscale, int vec4ok) {
     extern __shared__ float2 smem[];
     const int n = fp.n;
-    constexpr int P = NW / VEC;
+    constexpr int NF = NW / VEC;
+    constexpr int GT = 32 * G;
     float2 *data = smem;
     float2 *tw_s = data + (size_t)NW * n;
     unsigned short *perm_s = reinterpret_cast<unsigned short *>(tw_s + fp.tw_pass_total);
 
-    const int f = blockIdx.y;
-    const int k0 = blockIdx.x * P;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int kn = blockIdx.y;
+    const int f0 = blockIdx.x * NF;
+    const int colbase = 2 * VEC * f0;
+    const int t = threadIdx.x / GT, lane = threadIdx.x % GT;
     load_tables(fp, tw_s, perm_s);
     __syncthreads();
 
@@ -530,29 +529,34 @@ __global__ void __launch_bounds__(32 * NW) fft_synthesis_kernel(const float *__r
     {
         const int nzero = n - 2 * mtop + 1;
         for (int i = threadIdx.x; i < NW * nzero; i += blockDim.x) {
-            const int t = i / nzero, m = mtop + (i - t * nzero);
-            data[(size_t)t * n + perm_s[m]] = make_float2(0.f, 0.f);
+            const int u = i / nzero, m = mtop + (i - u * nzero);
+            data[(size_t)u * n + perm_s[m]] = make_float2(0.f, 0.f);
         }
     }
-    for (int i = threadIdx.x; i < mtop * VEC; i += blockDim.x) {
-        const int m = i % mtop, comp = i / mtop;
+    for (int m = threadIdx.x; m < mtop; m += blockDim.x) {
         const float sc = mscale[m];
-        const float *ge = Y + ((size_t)(2 * m) * ncols + (2 * VEC) * f + 2 * comp) * Kp + k0;
-        const float *go = Y + ((size_t)(2 * m + 1) * ncols + (2 * VEC) * f + 2 * comp) * Kp + k0;
-        float er[P], ei[P], orr[P], oi[P];
-        load_run<P>(ge, er);
-        load_run<P>(ge + Kp, ei);
-        load_run<P>(go, orr);
-        load_run<P>(go + Kp, oi);
+        const float *ge = Y + ((size_t)(2 * m) * Kh + kn) * ncp + colbase;
+        const float *go = Y + ((size_t)(2 * m + 1) * Kh + kn) * ncp + colbase;
+        float e[2 * NW], o[2 * NW];
+#pragma unroll
+        for (int c = 0; c < 2 * NW; c += 4) {
+            float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+            if (colbase + c < ncp) {
+                a = *reinterpret_cast<const float4 *>(ge + c);
+                b = *reinterpret_cast<const float4 *>(go + c);
+            }
+            e[c] = a.x; e[c + 1] = a.y; e[c + 2] = a.z; e[c + 3] = a.w;
+            o[c] = b.x; o[c + 1] = b.y; o[c + 2] = b.z; o[c + 3] = b.w;
+        }
         const bool edge = (m == 0) || (2 * m == n);
         const int pm = perm_s[m];
         const int pn = perm_s[m == 0 ? 0 : n - m];
 #pragma unroll
-        for (int q = 0; q < P; ++q) {
+        for (int u = 0; u < NW; ++u) {
             // north row spectrum A = even + odd, south row spectrum B = even - odd; Z = A + i B
-            float ar = sc * (er[q] + orr[q]), ai = sc * (ei[q] + oi[q]);
-            float br = sc * (er[q] - orr[q]), bi = sc * (ei[q] - oi[q]);
-            float2 *dd = data + (size_t)(comp * P + q) * n;
+            const float ar = sc * (e[2 * u] + o[2 * u]), ai = sc * (e[2 * u + 1] + o[2 * u + 1]);
+            const float br = sc * (e[2 * u] - o[2 * u]), bi = sc * (e[2 * u + 1] - o[2 * u + 1]);
+            float2 *dd = data + (size_t)u * n;
             if (edge) {
                 dd[pm] = make_float2(ar, br);  // imaginary parts of DC / Nyquist are dropped
             } else {
@@ -563,26 +567,25 @@ __global__ void __launch_bounds__(32 * NW) fft_synthesis_kernel(const float *__r
     }
     __syncthreads();
 
-    fft_warp<true>(data + (size_t)warp * n, fp, tw_s, lane);
+    fft_group<true, G>(data + (size_t)t * n, fp, tw_s, lane, 1 + t);
 
-    // ---- each warp stores its own pair of rows ----
+    // ---- each group stores its own pair of rows ----
     {
-        const int q = warp % P, comp = warp / P;
-        const int kn = k0 + q;
-        if (kn < Kh) {
+        const int f = f0 + t / VEC, comp = t % VEC;
+        if (f < nfields) {
             const int ks = nlat - 1 - kn;
-            const float2 *src = data + (size_t)warp * n;
+            const float2 *src = data + (size_t)t * n;
             float *rn = x + ((size_t)(f * VEC + comp) * nlat + kn) * n;
             float *rs = x + ((size_t)(f * VEC + comp) * nlat + ks) * n;
             if ((n % 4 == 0) && vec4ok) {
-                for (int j = lane; j < n / 4; j += 32) {
+                for (int j = lane; j < n / 4; j += GT) {
                     const float4 *s4 = reinterpret_cast<const float4 *>(src + 4 * j);
                     float4 a = s4[0], b = s4[1];
                     reinterpret_cast<float4 *>(rn)[j] = make_float4(a.x, a.z, b.x, b.z);
                     if (ks != kn) reinterpret_cast<float4 *>(rs)[j] = make_float4(a.y, a.w, b.y, b.w);
                 }
             } else {
-                for (int j = lane; j < n; j += 32) {
+                for (int j = lane; j < n; j += GT) {
                     rn[j] = src[j].x;
                     if (ks != kn) rs[j] = src[j].y;
                 }
@@ -615,7 +618,7 @@ __global__ void __launch_bounds__(32 * NW) rfft_rows_kernel(const float *__restr
         }
     }
     __syncthreads();
-    fft_warp<false>(data + (size_t)warp * n, fp, tw_s, lane);
+    fft_group<false, 1>(data + (size_t)warp * n, fp, tw_s, lane, 0);
     const int nyq = n / 2;
     {
         const long long ra = r0 + 2 * warp, rb = ra + 1;
@@ -661,7 +664,7 @@ __global__ void __launch_bounds__(32 * NW) irfft_rows_kernel(const float2 *__res
         }
     }
     __syncwarp();
-    fft_warp<true>(dd, fp, tw_s, lane);
+    fft_group<true, 1>(dd, fp, tw_s, lane, 0);
     for (int j = lane; j < n; j += 32) {
         if (ra < nrows) out[ra * n + j] = dd[j].x;
         if (rb < nrows) out[rb * n + j] = dd[j].y;
@@ -682,7 +685,9 @@ static int set_smem(K kernel, size_t bytes) {
     return SHTB200_OK;
 }
 
-// transforms (warps) per CTA: 8 when two such CTAs fit one SM, else 4, else 2
+constexpr int kGroupWarps = 2;  // warps that share one transform
+
+// transforms per CTA: 8 when two such CTAs fit one SM, else 4, else 2
 static int pick_warps(const FftPlanDev &fp, int vec) {
     for (int nw = 8; nw > 2 * vec; nw /= 2)
         if (fft_smem_bytes(nw, fp) <= 110 * 1024) return nw;
@@ -692,17 +697,16 @@ static int pick_warps(const FftPlanDev &fp, int vec) {
 int launch_fft_analysis(const Plan &pl, const float *x, float *X, int nfields, cudaStream_t st) {
     const int vec = pl.vector ? 2 : 1;
     const int NW = pick_warps(pl.fft, vec);
-    const int P = NW / vec;
-    const int ncols = (pl.vector ? 4 : 2) * nfields;
-    dim3 grid(pl.Kp / P, nfields);  // covers the row padding [Kh, Kp) too, which must hold zeros
+    const int ncp = (int)round_up((pl.vector ? 4 : 2) * nfields, 4);
+    dim3 grid(ceil_div(nfields, NW / vec), pl.Kh);
     size_t smem = fft_smem_bytes(NW, pl.fft);
     const int al = (int)(((uintptr_t)x & 15) == 0);
     int rc;
-#define LAUNCH_A(WW, VV)                                                                                                                  \
-    do {                                                                                                                                  \
-        if ((rc = set_smem(fft_analysis_kernel<WW, VV>, smem)) != 0) return rc;                                                           \
-        fft_analysis_kernel<WW, VV><<<grid, 32 * WW, smem, st>>>(x, X, pl.fft, pl.nlat, pl.Kh, pl.Kp, pl.mmax, ncols, pl.d_mscale,       \
-                                                                 pl.zero_imag_edges, al);                                                 \
+#define LAUNCH_A(WW, VV)                                                                                                                    \
+    do {                                                                                                                                    \
+        if ((rc = set_smem(fft_analysis_kernel<WW, VV, kGroupWarps>, smem)) != 0) return rc;                                                \
+        fft_analysis_kernel<WW, VV, kGroupWarps><<<grid, 32 * WW * kGroupWarps, smem, st>>>(x, X, pl.fft, pl.nlat, pl.Kh, nfields, ncp,     \
+                                                                                            pl.mmax, pl.d_mscale, pl.zero_imag_edges, al); \
     } while (0)
     if (vec == 1) {
         if (NW == 8) LAUNCH_A(8, 1);
@@ -720,16 +724,16 @@ int launch_fft_analysis(const Plan &pl, const float *x, float *X, int nfields, c
 int launch_fft_synthesis(const Plan &pl, const float *Y, float *x, int nfields, cudaStream_t st) {
     const int vec = pl.vector ? 2 : 1;
     const int NW = pick_warps(pl.fft, vec);
-    const int P = NW / vec;
-    const int ncols = (pl.vector ? 4 : 2) * nfields;
-    dim3 grid(ceil_div(pl.Kh, P), nfields);
+    const int ncp = (int)round_up((pl.vector ? 4 : 2) * nfields, 4);
+    dim3 grid(ceil_div(nfields, NW / vec), pl.Kh);
     size_t smem = fft_smem_bytes(NW, pl.fft);
     const int al = (int)(((uintptr_t)x & 15) == 0);
     int rc;
-#define LAUNCH_S(WW, VV)                                                                                                              \
-    do {                                                                                                                              \
-        if ((rc = set_smem(fft_synthesis_kernel<WW, VV>, smem)) != 0) return rc;                                                      \
-        fft_synthesis_kernel<WW, VV><<<grid, 32 * WW, smem, st>>>(Y, x, pl.fft, pl.nlat, pl.Kh, pl.Kp, pl.mmax, ncols, pl.d_mscale, al); \
+#define LAUNCH_S(WW, VV)                                                                                                                 \
+    do {                                                                                                                                 \
+        if ((rc = set_smem(fft_synthesis_kernel<WW, VV, kGroupWarps>, smem)) != 0) return rc;                                            \
+        fft_synthesis_kernel<WW, VV, kGroupWarps><<<grid, 32 * WW * kGroupWarps, smem, st>>>(Y, x, pl.fft, pl.nlat, pl.Kh, nfields, ncp, \
+                                                                                             pl.mmax, pl.d_mscale, al);                  \
     } while (0)
     if (vec == 1) {
         if (NW == 8) LAUNCH_S(8, 1);

@@ -47,7 +47,16 @@ __global__ void __launch_bounds__(256) legendre_simt_kernel(GemmParams gp) {
             const int ra = row0 + r;
             As[kk][r] = (ra < it.rows) ? load_operand(gp.A, gp.a_pitch, it.a_y0, it.a_dy, gp.a_dx, gp.a_kext, ra, k0 + kk) : 0.f;
             const int cb = col0 + r;
-            Bs[kk][r] = (cb < gp.ncols) ? load_operand(gp.B, gp.b_pitch, b_y0, b_dy, gp.b_dx, gp.b_kext, cb, k0 + kk) : 0.f;
+            float bv = 0.f;
+            if (cb < gp.ncols) {
+                if (gp.b_mn) {
+                    const int k = k0 + kk;
+                    if (k < gp.b_krows) bv = gp.B[(((long long)it.b_y0 - gp.b_unit0) * gp.b_krows + k) * gp.b_pitch + cb];
+                } else {
+                    bv = load_operand(gp.B, gp.b_pitch, b_y0, b_dy, gp.b_dx, gp.b_kext, cb, k0 + kk);
+                }
+            }
+            Bs[kk][r] = bv;
         }
         __syncthreads();
 #pragma unroll
@@ -94,7 +103,7 @@ __global__ void __launch_bounds__(256) legendre_simt_kernel(GemmParams gp) {
             for (int j = 0; j < 4; ++j) {
                 const int c = col0 + tx * 4 + j;
                 if (c >= gp.ncols) continue;
-                gp.out[((size_t)g * gp.ngroups_cols + c) * gp.out_ld + rg] = acc[i][j];
+                gp.out[((size_t)g * gp.out_rows + rg) * gp.out_ld + c] = acc[i][j];
             }
         }
     }

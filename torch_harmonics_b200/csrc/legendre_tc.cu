@@ -41,6 +41,7 @@ constexpr int NACC = 3;                // accumulator buffers in tensor memory
 constexpr int A_TILE_BYTES = TILE_M * TK * 4;                // 16 KiB
 constexpr int STAGE_BYTES = A_TILE_BYTES + BN_MAX * TK * 4;  // 36 KiB
 constexpr int B_OFF = A_TILE_BYTES;
+constexpr int B_BLK_BYTES = 32 * TK * 4;  // column-contiguous B: one 32 (k) x 32 (columns) block, 4 KiB
 constexpr int TMEM_COLS = 512;
 constexpr int NSPLIT_WARPS = 8, NEPI_WARPS = 8;
 constexpr int NTHREADS = 32 * (2 + NSPLIT_WARPS + NEPI_WARPS);  // 576
@@ -57,6 +58,7 @@ struct TcParams {
     int ntiles;      // column tiles
     int nunits;      // nitems * ntiles
     int ksteps_cap;  // row-packed operands: k-steps that cover the valid extent
+    int bblk;        // column-contiguous B: 32-column blocks per tile
     int write_hi;    // also store the TF32-truncated value back (only needed if the tensor core rounded instead of truncating)
     int *err;        // device error word
 };
@@ -123,18 +125,25 @@ legendre_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             int s = 0;
             uint32_t ph = 0;
             bool ok = true;
-            const uint32_t bytes = (uint32_t)(A_TILE_BYTES + P.bn * TK * 4);
+            const uint32_t bytes = (uint32_t)(A_TILE_BYTES + (gp.b_mn ? P.bblk * B_BLK_BYTES : P.bn * TK * 4));
             for (int u = blockIdx.x; u < P.nunits && ok; u += gridDim.x) {
                 const Unit w = get_unit(u);
                 if (w.skip) continue;
-                const long long by0 = ((long long)w.it.b_y0 - gp.b_unit0) * gp.ncols + (long long)w.ntile * P.bn;
+                const long long by0 = gp.b_mn ? ((long long)w.it.b_y0 - gp.b_unit0) * gp.b_krows
+                                              : ((long long)w.it.b_y0 - gp.b_unit0) * gp.ncols + (long long)w.ntile * P.bn;
                 for (int ks = 0; ks < w.ksteps; ++ks) {
                     if (!(ok = ptx::mbar_wait_bounded(bar_empty(s), ph ^ 1u, abort_flag, WAIT_LIMIT))) break;
                     ptx::mbar_arrive_expect_tx(bar_full(s), bytes);
                     const uint32_t dst = stage0 + s * STAGE_BYTES;
                     ptx::tma_load_2d(dst, &tmA, row_packed_a ? ks * TK : 0, w.it.a_y0 + (row_packed_a ? 0 : ks * w.it.a_dy), bar_full(s));
-                    const long long by = by0 + (row_packed_b ? 0 : (long long)ks * w.it.b_dy * gp.ncols);
-                    ptx::tma_load_2d(dst + B_OFF, &tmB, row_packed_b ? ks * TK : 0, (int)by, bar_full(s));
+                    if (gp.b_mn) {
+                        // 32 contraction rows x 32 columns per box; consecutive boxes hold consecutive column blocks
+                        for (int i = 0; i < P.bblk; ++i)
+                            ptx::tma_load_2d(dst + B_OFF + i * B_BLK_BYTES, &tmB, w.ntile * P.bn + 32 * i, (int)(by0 + (long long)ks * TK), bar_full(s));
+                    } else {
+                        const long long by = by0 + (row_packed_b ? 0 : (long long)ks * w.it.b_dy * gp.ncols);
+                        ptx::tma_load_2d(dst + B_OFF, &tmB, row_packed_b ? ks * TK : 0, (int)by, bar_full(s));
+                    }
                     if (++s == NSTAGE) { s = 0; ph ^= 1u; }
                 }
             }
@@ -145,7 +154,7 @@ legendre_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             int s = 0, c = 0, a = 0;
             uint32_t ph = 0, phc = 0, pha = 0;
             bool ok = true;
-            const uint32_t idesc = ptx::idesc_tf32_m128((uint32_t)P.bn);
+            const uint32_t idesc = ptx::idesc_tf32_m128((uint32_t)P.bn) | (gp.b_mn ? (1u << 16) : 0u);  // bit 16: B is column (MN) major
             for (int u = blockIdx.x; u < P.nunits && ok; u += gridDim.x) {
                 const Unit w = get_unit(u);
                 if (w.skip) continue;
@@ -159,13 +168,16 @@ legendre_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                     ptx::tc_fence_after();
                     const uint32_t hi = stage0 + s * STAGE_BYTES, lo = lo0 + c * STAGE_BYTES;
                     const uint64_t ah = ptx::smem_desc_sw128(hi), al = ptx::smem_desc_sw128(lo);
-                    const uint64_t bh = ptx::smem_desc_sw128(hi + B_OFF), bl = ptx::smem_desc_sw128(lo + B_OFF);
+                    const uint64_t bh = gp.b_mn ? ptx::smem_desc_sw128_mn(hi + B_OFF, B_BLK_BYTES) : ptx::smem_desc_sw128(hi + B_OFF);
+                    const uint64_t bl = gp.b_mn ? ptx::smem_desc_sw128_mn(lo + B_OFF, B_BLK_BYTES) : ptx::smem_desc_sw128(lo + B_OFF);
+                    // one MMA consumes 8 contraction indices: 32 bytes along a K-major row, one 8-row (1 KiB) group of a column-major tile
+                    const uint64_t bstep = gp.b_mn ? (uint64_t)(1024 >> 4) : (uint64_t)(32 >> 4);
 #pragma unroll
                     for (int k8 = 0; k8 < TK / 8; ++k8) {
-                        const uint64_t koff = (uint64_t)((k8 * 32) >> 4);  // 8 TF32 = 32 bytes along the swizzled row
-                        ptx::mma_tf32(d, al + koff, bh + koff, idesc, (ks | k8) ? 1u : 0u);  // small terms first
-                        ptx::mma_tf32(d, ah + koff, bl + koff, idesc, 1u);
-                        ptx::mma_tf32(d, ah + koff, bh + koff, idesc, 1u);
+                        const uint64_t koff = (uint64_t)((k8 * 32) >> 4), kb = bstep * k8;
+                        ptx::mma_tf32(d, al + koff, bh + kb, idesc, (ks | k8) ? 1u : 0u);  // small terms first
+                        ptx::mma_tf32(d, ah + koff, bl + kb, idesc, 1u);
+                        ptx::mma_tf32(d, ah + koff, bh + kb, idesc, 1u);
                     }
                     ptx::tc_commit(bar_empty(s));
                     ptx::tc_commit(bar_loempty(c));
@@ -184,7 +196,7 @@ legendre_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         int s = 0, c = 0;
         uint32_t ph = 0, phc = 0;
         bool ok = true;
-        const int na4 = A_TILE_BYTES / 16, nb4 = P.bn * TK * 4 / 16;
+        const int na4 = A_TILE_BYTES / 16, nb4 = (gp.b_mn ? P.bblk * B_BLK_BYTES : P.bn * TK * 4) / 16;
         for (int u = blockIdx.x; u < P.nunits && ok; u += gridDim.x) {
             const Unit w = get_unit(u);
             if (w.skip) continue;
@@ -261,12 +273,10 @@ legendre_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                     }
                 } else {
                     const int g = 2 * (w.it.m - gp.m0) + w.it.p;
-                    float *o = gp.out + ((size_t)g * gp.ngroups_cols) * gp.out_ld + rg;
+                    float *o = gp.out + ((size_t)g * gp.out_rows + rg) * gp.out_ld + col0 + cc;  // 16 consecutive columns: 64 bytes
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const int col = col0 + cc + j;
-                        if (col < gp.ncols) o[(size_t)col * gp.out_ld] = v[j];
-                    }
+                    for (int j = 0; j < 16; j += 4)
+                        if (col0 + cc + j < gp.out_ld) *reinterpret_cast<float4 *>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
                 }
             }
             ptx::tc_fence_before();
@@ -308,14 +318,15 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-int make_map(CUtensorMap *tm, const float *base, long long inner, long long rows, long long pitch_floats, int box_rows) {
+int make_map(CUtensorMap *tm, const float *base, long long inner, long long rows, long long pitch_floats, int box_rows, bool atom32 = false) {
+    if (inner <= 0 || rows <= 0) return fail(SHTB200_EINVAL, "empty operand");
     EncodeTiledFn fn = encode_fn();
     if (!fn) return fail(SHTB200_ECUDA, "cuTensorMapEncodeTiled not available from the driver");
     cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)rows};
     cuuint64_t strides[1] = {(cuuint64_t)pitch_floats * 4};
     cuuint32_t box[2] = {(cuuint32_t)TK, (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void *)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+    CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void *)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
                     CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(SHTB200_ECUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
     return SHTB200_OK;
@@ -345,6 +356,7 @@ int launch_gemm_tc(const Plan &pl, const GemmParams &gp, cudaStream_t st) {
     P.ntiles = ceil_div(gp.ncols, P.bn);
     P.nunits = gp.nitems * P.ntiles;
     P.ksteps_cap = ceil_div(gp.a_kext, TK);
+    P.bblk = ceil_div(P.bn, 32);
     P.err = pl.d_err;
     {
         const char *e = getenv("SHTB200_TC_WRITE_HI");
@@ -357,8 +369,8 @@ int launch_gemm_tc(const Plan &pl, const GemmParams &gp, cudaStream_t st) {
     if (analysis) {
         a_inner = gp.a_kext;
         a_rows = pl.group_a0.back() + kItemRowsMax;
-        b_inner = gp.b_kext;
-        b_rows = (long long)2 * gp.mmax_out * gp.ncols;
+        b_inner = gp.ncols;  // columns beyond it read as zeros
+        b_rows = (long long)2 * gp.mmax_out * gp.b_krows;
     } else {
         a_inner = kBK;
         a_rows = pl.group_a0.back() + kItemRowsMax;
@@ -368,7 +380,7 @@ int launch_gemm_tc(const Plan &pl, const GemmParams &gp, cudaStream_t st) {
     CUtensorMap tmA, tmB;
     int rc;
     if ((rc = make_map(&tmA, gp.A, a_inner, a_rows, gp.a_pitch, TILE_M))) return rc;
-    if ((rc = make_map(&tmB, gp.B, b_inner, b_rows, gp.b_pitch, P.bn))) return rc;
+    if ((rc = make_map(&tmB, gp.B, b_inner, b_rows, gp.b_pitch, gp.b_mn ? 32 : P.bn, gp.b_mn != 0))) return rc;
 
     const int grid = std::min(sm_count, P.nunits);
     legendre_tc_kernel<<<grid, NTHREADS, SMEM_BYTES, st>>>(tmA, tmB, P);

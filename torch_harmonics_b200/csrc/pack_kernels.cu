@@ -25,21 +25,20 @@ struct TableView {
     }
 };
 
-// rows = degrees, contraction index = folded latitude (row-packed): A[a0[g] + r][seg * Kp + k']
-__global__ void pack_table_rows_kernel(TableView tv, float *A, const long long *a0, const int *grows, int ngroups, int ncomp, int Kh, int Kp, int negate_seg1) {
+// rows = degrees, contraction index = folded latitude (row-packed): A[a0[g] + r][seg * Kh + k'], zero beyond
+__global__ void pack_table_rows_kernel(TableView tv, float *A, const long long *a0, const int *grows, int ngroups, int ncomp, int Kh, int pitch, int negate_seg1) {
     const int g = blockIdx.y;
     const int m = g >> 1, p = g & 1;
     const int rows = grows[g];
-    const int pitch = ncomp * Kp;
     const long long total = (long long)rows * pitch;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         const int r = (int)(i / pitch), c = (int)(i - (long long)r * pitch);
-        const int seg = c / Kp, k = c - seg * Kp;
+        const int seg = c / Kh, k = c - seg * Kh;
         const int l = m + p + 2 * r;
         // scalar and the m/sin(theta) table share parity p with the rows; the d/dtheta table (seg 0 of a
         // vector plan) has the opposite parity but is addressed the same way: the fold is chosen by the FFT kernel
         float v = 0.f;
-        if (k < Kh) v = tv.at(ncomp == 2 ? seg : 0, m, l, k);
+        if (seg < ncomp) v = tv.at(ncomp == 2 ? seg : 0, m, l, k);
         if (negate_seg1 && seg == 1) v = -v;
         A[(a0[g] + r) * pitch + c] = v;
     }
@@ -172,44 +171,37 @@ __global__ void zero_upper_kernel(float2 *c, long long nfl, int lmax, int mloc, 
     }
 }
 
-// Xc (field, k, mloc) complex -> X[(2 mi + p) * ncols + 2 f + ri][k'] (pitch Kp), zero in the pitch padding
-__global__ void fold_modes_kernel(const float2 *__restrict__ Xc, float *__restrict__ X, int nfields, int nlat, int Kh, int Kp, int mloc) {
-    const long long total = (long long)mloc * nfields * Kp;
-    const int ncols = 2 * nfields;
+// Xc (field, k, mloc) complex -> X[(2 mi + p) * Kh + k'][2 f + ri] (row pitch ncp)
+__global__ void fold_modes_kernel(const float2 *__restrict__ Xc, float *__restrict__ X, int nfields, int nlat, int Kh, int ncp, int mloc) {
+    const long long total = (long long)mloc * Kh * nfields;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-        const int k = (int)(i % Kp);
-        const long long t = i / Kp;
-        const int f = (int)(t % nfields);
-        const int mi = (int)(t / nfields);
-        float2 e = make_float2(0.f, 0.f), o = e;
-        if (k < Kh) {
-            const int ks = nlat - 1 - k;
-            float2 a = Xc[((size_t)f * nlat + k) * mloc + mi];
-            if (ks == k) { e = a; }
-            else {
-                float2 b = Xc[((size_t)f * nlat + ks) * mloc + mi];
-                e = make_float2(a.x + b.x, a.y + b.y);
-                o = make_float2(a.x - b.x, a.y - b.y);
-            }
+        const int f = (int)(i % nfields);
+        const long long t = i / nfields;
+        const int k = (int)(t % Kh);
+        const int mi = (int)(t / Kh);
+        const int ks = nlat - 1 - k;
+        float2 a = Xc[((size_t)f * nlat + k) * mloc + mi];
+        float2 e = a, o = make_float2(0.f, 0.f);
+        if (ks != k) {
+            float2 b = Xc[((size_t)f * nlat + ks) * mloc + mi];
+            e = make_float2(a.x + b.x, a.y + b.y);
+            o = make_float2(a.x - b.x, a.y - b.y);
         }
-        float *g0 = X + ((size_t)(2 * mi) * ncols + 2 * f) * Kp + k;
-        float *g1 = X + ((size_t)(2 * mi + 1) * ncols + 2 * f) * Kp + k;
-        g0[0] = e.x; g0[Kp] = e.y; g1[0] = o.x; g1[Kp] = o.y;
+        *reinterpret_cast<float2 *>(X + ((size_t)(2 * mi) * Kh + k) * ncp + 2 * f) = e;
+        *reinterpret_cast<float2 *>(X + ((size_t)(2 * mi + 1) * Kh + k) * ncp + 2 * f) = o;
     }
 }
 
-// Y[(2 mi + p) * ncols + 2 f + ri][k'] -> Xc (field, k, mloc) complex
-__global__ void unfold_modes_kernel(const float *__restrict__ Y, float2 *__restrict__ Xc, int nfields, int nlat, int Kh, int Kp, int mloc) {
+// Y[(2 mi + p) * Kh + k'][2 f + ri] -> Xc (field, k, mloc) complex
+__global__ void unfold_modes_kernel(const float *__restrict__ Y, float2 *__restrict__ Xc, int nfields, int nlat, int Kh, int ncp, int mloc) {
     const long long total = (long long)nfields * Kh * mloc;
-    const int ncols = 2 * nfields;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         const int mi = (int)(i % mloc);
         const long long t = i / mloc;
         const int k = (int)(t % Kh);
         const int f = (int)(t / Kh);
-        const float *g0 = Y + ((size_t)(2 * mi) * ncols + 2 * f) * Kp + k;
-        const float *g1 = Y + ((size_t)(2 * mi + 1) * ncols + 2 * f) * Kp + k;
-        float2 e = make_float2(g0[0], g0[Kp]), o = make_float2(g1[0], g1[Kp]);
+        const float2 e = *reinterpret_cast<const float2 *>(Y + ((size_t)(2 * mi) * Kh + k) * ncp + 2 * f);
+        const float2 o = *reinterpret_cast<const float2 *>(Y + ((size_t)(2 * mi + 1) * Kh + k) * ncp + 2 * f);
         const int ks = nlat - 1 - k;
         Xc[((size_t)f * nlat + k) * mloc + mi] = make_float2(e.x + o.x, e.y + o.y);
         if (ks != k) Xc[((size_t)f * nlat + ks) * mloc + mi] = make_float2(e.x - o.x, e.y - o.y);
@@ -232,7 +224,7 @@ int launch_pack_table(Plan &pl, const float *table, cudaStream_t st) {
     tv.mkl = (pl.kind == SHTB200_ISHT || pl.kind == SHTB200_ISHT_ADJOINT || pl.kind == SHTB200_IVSHT || pl.kind == SHTB200_IVSHT_ADJOINT) ? 1 : 0;
     dim3 grid(64, ngroups);
     if (pl.analysis) {
-        pack_table_rows_kernel<<<grid, 256, 0, st>>>(tv, pl.d_table, pl.d_ga0, pl.d_grows, ngroups, pl.ncomp, pl.Kh, pl.Kp, pl.negate_seg1);
+        pack_table_rows_kernel<<<grid, 256, 0, st>>>(tv, pl.d_table, pl.d_ga0, pl.d_grows, ngroups, pl.ncomp, pl.Kh, (int)pl.a_pitch, pl.negate_seg1);
     } else {
         pack_table_blocks_kernel<<<grid, 256, 0, st>>>(tv, pl.d_table, pl.d_ga0, pl.d_gkb, pl.d_gkb0, ngroups, pl.ncomp, pl.Kh, pl.lmax, pl.negate_seg1);
     }
@@ -278,9 +270,9 @@ int launch_zero_upper(const Plan &pl, float2 *c, int nfields, int m0, int mloc, 
 int launch_fold_modes(const Plan &pl, const float2 *Xc, float *X, int nfields, int m0, int mloc, cudaStream_t st) {
     (void)m0;
     if (pl.vector) return fail(SHTB200_EINVAL, "stage-wise Legendre entry point supports the scalar kinds only");
-    const long long total = (long long)mloc * nfields * pl.Kp;
+    const long long total = (long long)mloc * nfields * pl.Kh;
     if (total == 0) return SHTB200_OK;
-    fold_modes_kernel<<<grid_x_for(total), 256, 0, st>>>(Xc, X, nfields, pl.nlat, pl.Kh, pl.Kp, mloc);
+    fold_modes_kernel<<<grid_x_for(total), 256, 0, st>>>(Xc, X, nfields, pl.nlat, pl.Kh, (int)round_up(2 * nfields, 4), mloc);
     SHT_CUDA_CHECK(cudaGetLastError());
     return SHTB200_OK;
 }
@@ -290,7 +282,7 @@ int launch_unfold_modes(const Plan &pl, const float *Y, float2 *Xc, int nfields,
     if (pl.vector) return fail(SHTB200_EINVAL, "stage-wise Legendre entry point supports the scalar kinds only");
     const long long total = (long long)nfields * pl.Kh * mloc;
     if (total == 0) return SHTB200_OK;
-    unfold_modes_kernel<<<grid_x_for(total), 256, 0, st>>>(Y, Xc, nfields, pl.nlat, pl.Kh, pl.Kp, mloc);
+    unfold_modes_kernel<<<grid_x_for(total), 256, 0, st>>>(Y, Xc, nfields, pl.nlat, pl.Kh, (int)round_up(2 * nfields, 4), mloc);
     SHT_CUDA_CHECK(cudaGetLastError());
     return SHTB200_OK;
 }

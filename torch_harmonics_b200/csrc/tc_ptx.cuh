@@ -121,6 +121,19 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
     d |= (uint64_t)2 << 61;  // layout type SWIZZLE_128B
     return d;
 }
+// Column-contiguous ("MN-major") 32-bit operand: the only layout the tensor core takes for it is the 128-byte
+// swizzle with 32-byte atoms (TMA mode SWIZZLE_128B_ATOM_32B).  The tile is a sequence of blocks of 32 columns;
+// inside a block each contraction index is one 128-byte row and 4 rows form a 512-byte swizzle group.
+// Leading byte offset = distance between column blocks, stride byte offset = distance between 4-row groups.
+__device__ __forceinline__ uint64_t smem_desc_sw128_mn(uint32_t smem_addr, uint32_t block_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)((block_bytes >> 4) & 0x3FFFu) << 16;
+    d |= (uint64_t)(512u >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)1 << 61;  // layout type SWIZZLE_128B_BASE32B
+    return d;
+}
 // Instruction descriptor: fp32 accumulator, TF32 x TF32, both K-major, M = 128, N = n.
 __device__ __forceinline__ uint32_t idesc_tf32_m128(uint32_t n) { return (1u << 4) | (2u << 7) | (2u << 10) | ((n >> 3) << 17) | ((128u >> 4) << 24); }
 

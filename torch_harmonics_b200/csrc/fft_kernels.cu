@@ -423,8 +423,13 @@ __global__ void __launch_bounds__(32 * NW * G, (NW * G >= 16) ? 2 : 1) fft_analy
                         if (j < n4) {
                             float4 o = self ? make_float4(0.f, 0.f, 0.f, 0.f) : make_float4(a[u].x - b[u].x, a[u].y - b[u].y, a[u].z - b[u].z, a[u].w - b[u].w);
                             float4 *d4 = reinterpret_cast<float4 *>(dst + 4 * j);
-                            d4[0] = make_float4(a[u].x + b[u].x, o.x, a[u].y + b[u].y, o.y);
-                            d4[1] = make_float4(a[u].z + b[u].z, o.z, a[u].w + b[u].w, o.w);
+                            const float4 c0 = make_float4(a[u].x + b[u].x, o.x, a[u].y + b[u].y, o.y);
+                            const float4 c1 = make_float4(a[u].z + b[u].z, o.z, a[u].w + b[u].w, o.w);
+                            // a thread owns two adjacent 16-byte chunks; lanes 4..7 of every 8 store them in the other
+                            // order so that the 8 lanes of one shared-memory wavefront hit 8 different bank groups
+                            const int sw = (lane >> 2) & 1;
+                            d4[sw] = sw ? c1 : c0;
+                            d4[sw ^ 1] = sw ? c0 : c1;
                         }
                     }
                 }
@@ -580,7 +585,9 @@ __global__ void __launch_bounds__(32 * NW * G, (NW * G >= 16) ? 2 : 1) fft_synth
             if ((n % 4 == 0) && vec4ok) {
                 for (int j = lane; j < n / 4; j += GT) {
                     const float4 *s4 = reinterpret_cast<const float4 *>(src + 4 * j);
-                    float4 a = s4[0], b = s4[1];
+                    const int sw = (lane >> 2) & 1;  // same bank-conflict-free chunk order as on the analysis side
+                    const float4 c0 = s4[sw], c1 = s4[sw ^ 1];
+                    const float4 a = sw ? c1 : c0, b = sw ? c0 : c1;
                     reinterpret_cast<float4 *>(rn)[j] = make_float4(a.x, a.z, b.x, b.z);
                     if (ks != kn) reinterpret_cast<float4 *>(rs)[j] = make_float4(a.y, a.w, b.y, b.w);
                 }

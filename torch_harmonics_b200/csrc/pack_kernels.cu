@@ -115,48 +115,70 @@ __global__ void pack_coeffs_kernel(const float2 *__restrict__ c, float *__restri
 // Scalar fast path, both directions: tiled transpose between the coefficient array c[field][l][m] (m contiguous)
 // and the degree-slab layout S[(slab0[g] + r / 32) * ncols + 2 field + re/im][r % 32] with r = (l - m - p) / 2.
 // One CTA moves a 64 (degrees) x 32 (orders) tile of one field through shared memory so that both sides see
-// full 128- or 256-byte runs.  TO_SLABS also writes the zero padding of the last slab of every group;
-// the reverse direction also writes the exact zeros of the l < m triangle.
+// full 128- or 256-byte runs; the tile is stored with even and odd degrees apart, which makes both phases free of
+// bank conflicts.  TO_SLABS also writes the zero padding of the last slab of every group; the reverse direction
+// also writes the exact zeros of the l < m triangle.
 template <bool TO_SLABS>
 __global__ void __launch_bounds__(256) coeff_slab_transpose_kernel(float2 *__restrict__ c, float *__restrict__ S, const long long *__restrict__ slab0,
                                                                    const int *__restrict__ gkb, int ncols, int lmax, int mloc, int m0) {
-    __shared__ float tre[64][33], tim[64][33];
+    __shared__ float tre[2][32][33], tim[2][32][33];  // [degree parity][degree / 2][order]
+    __shared__ long long s_slab[64];
+    __shared__ int s_rows[64];
     const int mb0 = blockIdx.x * 32, l0 = blockIdx.y * 64, f = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const long long unit0 = slab0[2 * m0];
 
+    if (threadIdx.x < 64) {  // the 32 x 2 (order, parity) groups this tile touches
+        const int mi = mb0 + (threadIdx.x >> 1);
+        long long sl = 0;
+        int rows = 0;
+        if (mi < mloc) {
+            const int g = 2 * (m0 + mi) + (threadIdx.x & 1);
+            sl = slab0[g] - slab0[2 * m0];
+            rows = gkb[g] * kBK;
+        }
+        s_slab[threadIdx.x] = sl;
+        s_rows[threadIdx.x] = rows;
+    }
     if (TO_SLABS) {
         for (int r = warp; r < 64; r += 8) {
             const int l = l0 + r, mi = mb0 + lane;
             float2 z = make_float2(0.f, 0.f);
             if (l < lmax && mi < mloc) z = c[((size_t)f * lmax + l) * mloc + mi];
-            tre[r][lane] = z.x;
-            tim[r][lane] = z.y;
+            tre[r & 1][r >> 1][lane] = z.x;
+            tim[r & 1][r >> 1][lane] = z.y;
         }
-        __syncthreads();
     }
-    // 32 orders x 2 parities x (re, im) = 128 runs of up to 32 consecutive r
-    for (int task = warp; task < 128; task += 8) {
-        const int ml = task >> 2, p = (task >> 1) & 1, ri = task & 1;
+    __syncthreads();
+    // 32 orders x 2 parities: runs of up to 32 consecutive r, real and imaginary rows 32 floats apart
+    for (int combo = warp; combo < 64; combo += 8) {
+        const int ml = combo >> 1, p = combo & 1;
         const int mi = mb0 + ml;
         if (mi >= mloc) continue;
-        const int m = m0 + mi, g = 2 * m + p;
-        const int l = l0 + ((m + p) & 1) + 2 * lane;  // l0 is even: degrees of this parity inside the tile
-        const int r = (l - m - p) >> 1;               // arithmetic shift: negative when l < m + p
-        float(*t)[33] = ri ? tim : tre;
+        const int m = m0 + mi;
+        const int par = (m + p) & 1;        // l0 is even: degrees of this parity inside the tile are l0 + par + 2 lane
+        const int l = l0 + par + 2 * lane;
+        const int r = (l - m - p) >> 1;     // arithmetic shift: negative when l < m + p
+        const size_t at = ((size_t)(s_slab[combo] + (r >> 5)) * ncols + 2 * f) * kBK + (r & 31);
         if (TO_SLABS) {
-            if (l >= m + p && r < gkb[g] * kBK) S[((size_t)(slab0[g] - unit0 + (r >> 5)) * ncols + 2 * f + ri) * kBK + (r & 31)] = t[l - l0][ml];
+            if (l >= m + p && r < s_rows[combo]) {
+                S[at] = tre[par][lane][ml];
+                S[at + kBK] = tim[par][lane][ml];
+            }
         } else {
-            float v = 0.f;
-            if (l >= m + p && l < lmax) v = S[((size_t)(slab0[g] - unit0 + (r >> 5)) * ncols + 2 * f + ri) * kBK + (r & 31)];
-            t[l - l0][ml] = v;
+            float vr = 0.f, vi = 0.f;
+            if (l >= m + p && l < lmax) {
+                vr = S[at];
+                vi = S[at + kBK];
+            }
+            tre[par][lane][ml] = vr;
+            tim[par][lane][ml] = vi;
         }
     }
     if (!TO_SLABS) {
         __syncthreads();
         for (int r = warp; r < 64; r += 8) {
             const int l = l0 + r, mi = mb0 + lane;
-            if (l < lmax && mi < mloc) c[((size_t)f * lmax + l) * mloc + mi] = make_float2(tre[r][lane], tim[r][lane]);
+            if (l < lmax && mi < mloc) c[((size_t)f * lmax + l) * mloc + mi] = make_float2(tre[r & 1][r >> 1][lane], tim[r & 1][r >> 1][lane]);
         }
     }
 }

@@ -17,6 +17,7 @@
 // scale / transpose / real-imag split passes at torch_harmonics/sht.py:171-176 and :337-340.
 
 #include <math.h>
+#include <stdlib.h>
 
 #include <algorithm>
 #include <vector>
@@ -34,7 +35,7 @@ namespace {
 // Radices with in-register butterflies (2..5 direct, the others as products of two of those).
 const int kFastRadices[] = {16, 15, 12, 10, 9, 8, 6, 5, 4, 3, 2};
 
-// Fewest passes; among those the most balanced split (largest smallest radix).
+// Split n into fast radices (see the ranking inside).
 std::vector<int> best_split(int n, std::vector<std::vector<int>> &memo, std::vector<char> &done) {
     if (n == 1) return {};
     if (done[n]) return memo[n];
@@ -45,8 +46,13 @@ std::vector<int> best_split(int n, std::vector<std::vector<int>> &memo, std::vec
         std::vector<int> cand = best_split(n / r, memo, done);
         if (n / r != 1 && cand.empty()) continue;  // remainder not factorable with fast radices
         cand.insert(cand.begin(), r);
+        // fewest passes; then a split that contains an odd radix (it goes last, where an even radix would make the
+        // unit-stride pass and the final gather conflict on shared-memory banks); then the most balanced one
         auto mn = [](const std::vector<int> &v) { int m = 1 << 30; for (int x : v) m = std::min(m, x); return m; };
-        if (!have || cand.size() < best.size() || (cand.size() == best.size() && mn(cand) > mn(best))) { best = cand; have = true; }
+        auto odd = [](const std::vector<int> &v) { for (int x : v) if (x & 1) return 1; return 0; };
+        bool better = !have || cand.size() < best.size();
+        if (have && cand.size() == best.size()) better = odd(cand) > odd(best) || (odd(cand) == odd(best) && mn(cand) > mn(best));
+        if (better) { best = cand; have = true; }
     }
     done[n] = 1;
     memo[n] = best;
@@ -78,6 +84,23 @@ int build_fft_plan(int nlon, FftPlanDev *out, float2 **d_tw, unsigned short **d_
     std::sort(rad.begin(), rad.end(), [](int a, int b) { return a > b; });
     for (size_t i = 0; i + 1 < rad.size(); ++i)
         if (rad.back() % 2 == 0 && rad[i] % 2 == 1) { std::swap(rad[i], rad.back()); break; }
+    if (const char *ov = getenv("SHTB200_FFT_RADICES")) {  // e.g. "16,9,10": explicit pass order (tuning aid)
+        std::vector<int> r2;
+        long long prod = 1;
+        for (const char *q = ov; *q;) {
+            int v = atoi(q);
+            if (v > 1) { r2.push_back(v); prod *= v; }
+            while (*q && *q != ',') ++q;
+            if (*q == ',') ++q;
+        }
+        bool okr = prod == n;
+        for (int v : r2) {
+            bool known = false;
+            for (int f : kFastRadices) known |= (f == v);
+            okr &= known;
+        }
+        if (okr) rad = r2;
+    }
     rad.insert(rad.begin(), slow.begin(), slow.end());
     if ((int)rad.size() > kMaxFftStages) return fail(SHTB200_EINVAL, "nlon has too many factors");
 

@@ -324,9 +324,18 @@ int shtb200_plan_create(shtb200_plan **plan_out, int kind, int nlat, int nlon, i
         }
     }
     if (pl->group_a0[ngroups] + kItemRowsMax > 0x7fffffffLL) { shtb200_plan_destroy(pl); return fail(SHTB200_EINVAL, "table too large for 32-bit row indices"); }
-    std::stable_sort(pl->items.begin(), pl->items.end(), [](const GemmItem &a, const GemmItem &b) {
-        return (long long)a.kblocks * a.rows > (long long)b.kblocks * b.rows;
-    });
+    // Heaviest groups first; the row tiles of one group stay adjacent so that CTAs working on them at the same
+    // time share the group's operand through L2 instead of fetching it from HBM again later.
+    {
+        std::vector<long long> gwork(ngroups, 0);
+        for (const GemmItem &it : pl->items) gwork[2 * it.m + it.p] += (long long)it.kblocks * it.rows;
+        std::stable_sort(pl->items.begin(), pl->items.end(), [&gwork](const GemmItem &a, const GemmItem &b) {
+            const int ga = 2 * a.m + a.p, gb = 2 * b.m + b.p;
+            if (gwork[ga] != gwork[gb]) return gwork[ga] > gwork[gb];
+            if (ga != gb) return ga < gb;
+            return a.r0 < b.r0;
+        });
+    }
 
     if ((rc = upload(&pl->d_items, pl->items)) || (rc = upload(&pl->d_ga0, pl->group_a0)) || (rc = upload(&pl->d_gb0, pl->group_b0)) ||
         (rc = upload(&pl->d_grows, pl->group_rows)) || (rc = upload(&pl->d_gkb, pl->group_kblocks)) || (rc = upload(&pl->d_gkb0, kb0))) {

@@ -1,0 +1,94 @@
+"""CPU checks of the distributed host logic with two gloo ranks: split helpers, the all-to-all transposes
+(exact after gathering, forward and backward, even and uneven splits, real and complex), the process-grid
+registry.  Mirrors torch-harmonics tests/test_distributed_primitives.py:71-220."""
+
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, which):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import torch_harmonics_b200.distributed as thd
+
+    group = dist.new_group(list(range(world)))
+    if which == "azimuth":
+        thd.init(None, group)
+        tr = thd.distributed_transpose_azimuth
+        assert thd.azimuth_group_size() == world and thd.polar_group_size() == 1 and thd.azimuth_group_rank() == rank
+    else:
+        thd.init(group, None)
+        tr = thd.distributed_transpose_polar
+        assert thd.polar_group_size() == world and thd.azimuth_group_size() == 1 and thd.polar_group_rank() == rank
+    assert thd.is_initialized()
+    thd.config.debug = True  # exercises the shape-verification all-gathers too
+
+    for shape, dims, dtype in (((5, 3, 7, 9), (-3, -1), torch.float32), ((4, 6, 33, 65), (1, 2), torch.float64), ((3, 8, 5), (0, 2), torch.complex64), ((2, 2, 4), (-1, -3), torch.float32)):
+        g = torch.Generator().manual_seed(1)
+        if dtype.is_complex:
+            full = torch.complex(torch.randn(shape, generator=g), torch.randn(shape, generator=g))
+        else:
+            full = torch.randn(shape, generator=g, dtype=dtype)
+        d0, d1 = dims[0] % len(shape), dims[1] % len(shape)
+        s1 = thd.compute_split_shapes(shape[d1], world)
+        s0 = thd.compute_split_shapes(shape[d0], world)
+        local = thd.split_tensor_along_dim(full, d1, world)[rank].clone().requires_grad_(not dtype.is_complex)
+        out = tr(local, dims, s1)
+        expect = thd.split_tensor_along_dim(full, d0, world)[rank]
+        assert out.shape == expect.shape and torch.equal(out.detach(), expect), (shape, dims)
+        # the reverse transpose restores the tile, and autograd's backward is that reverse transpose
+        back = tr(out.detach(), (dims[1], dims[0]), s0)
+        assert torch.equal(back, local.detach())
+        if not dtype.is_complex:
+            out.backward(expect.clone())
+            assert torch.equal(local.grad, local.detach())
+
+    thd.config.debug = False
+    with pytest.raises(RuntimeError):
+        thd.compute_split_shapes(1, 2)
+    thd.finalize()
+    assert not thd.is_initialized() and thd.polar_group_size() == 1
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("which", ["azimuth", "polar"])
+def test_transposes_two_ranks(which):
+    mp.spawn(_worker, args=(2, _free_port(), which), nprocs=2, join=True)
+
+
+def test_split_helpers():
+    import torch_harmonics_b200.distributed as thd
+
+    assert thd.compute_split_shapes(256, 4) == [64] * 4
+    assert thd.compute_split_shapes(128, 3) == [43, 43, 42]
+    assert thd.compute_split_shapes(10, 4) == [3, 3, 2, 2]
+    assert thd.compute_split_shapes(721, 2) == [361, 360]
+    for size in (7, 33, 720):
+        for n in (1, 2, 3, 4, 7):
+            s = thd.compute_split_shapes(size, n)
+            assert sum(s) == size and max(s) - min(s) <= 1 and sorted(s, reverse=True) == s
+    x = torch.arange(2 * 3 * 4 * 5, dtype=torch.float32).reshape(2, 3, 4, 5)
+    y, lead, n = thd.flatten_and_pad_leading_dims(x, 8)
+    assert y.shape == (8, 4, 5) and lead == (2, 3) and n == 6 and torch.all(y[6:] == 0)
+    assert torch.equal(thd.unpad_and_unflatten_leading_dims(y, lead, n), x)
+    y, lead, n = thd.flatten_and_pad_leading_dims(x, 4)
+    assert y.shape == (6, 4, 5)
+    xv = torch.zeros(3, 2, 4, 5)
+    y, lead, n = thd.flatten_and_pad_leading_dims(xv, 4, num_trailing_dims=3)
+    assert y.shape == (4, 2, 4, 5) and n == 3
+    # no groups registered: transposes are the identity
+    assert torch.equal(thd.distributed_transpose_azimuth(x, (0, 1), [3]), x)

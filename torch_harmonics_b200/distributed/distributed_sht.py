@@ -1,0 +1,234 @@
+"""Spatially distributed scalar SHT modules on the shtb200 kernels.
+
+Counterparts of ``DistributedRealSHT`` / ``DistributedInverseRealSHT``
+(torch_harmonics/distributed/distributed_sht.py:51-222, :225-391): same constructor arguments, attributes
+(``comm_size_*``, ``comm_rank_*``, ``lat_shapes``, ``lon_shapes``, ``l_shapes``, ``m_shapes``, ``nlat_local``,
+``nlon_local``, ``lmax_local``, ``mmax_local``), local tensor layouts and autograd behaviour.  Latitudes and
+degrees are sharded over the polar group, longitudes and orders over the azimuth group; four all-to-all
+transposes per direction move between the layouts.  The longitude FFT and the Legendre contraction between the
+transposes run through the stage entry points of the C ABI (``shtb200_rfft_modes``, ``shtb200_irfft_modes``,
+``shtb200_legendre``).
+"""
+
+import ctypes
+import math
+
+import torch
+import torch.nn as nn
+
+from .. import _lib
+from ..legendre import _precompute_legpoly
+from ..quadrature import sht_colatitudes
+from ..sht import _default_engine, _require
+from ..truncation import truncate_sht
+from .primitives import (
+    compute_split_shapes,
+    distributed_transpose_azimuth,
+    distributed_transpose_polar,
+    flatten_and_pad_leading_dims,
+    split_tensor_along_dim,
+    unpad_and_unflatten_leading_dims,
+)
+from .utils import azimuth_group_rank, azimuth_group_size, polar_group_rank, polar_group_size
+
+
+def _stream(t):
+    return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def _edge_weights(nmodes, nlon, interior, device):
+    """Per-order factors of the FFT adjoints: 1 at m = 0 and Nyquist, ``interior`` elsewhere."""
+    w = torch.full((nmodes,), interior, dtype=torch.float32, device=device)
+    w[0] = 1.0
+    if nlon % 2 == 0 and nlon // 2 < nmodes:
+        w[nlon // 2] = 1.0
+    return w
+
+
+def _zero_edge_imag(c, nlon):
+    c = c.clone()
+    c[..., 0] = torch.complex(c[..., 0].real, torch.zeros_like(c[..., 0].real))
+    if nlon % 2 == 0 and nlon // 2 < c.shape[-1]:
+        k = nlon // 2
+        c[..., k] = torch.complex(c[..., k].real, torch.zeros_like(c[..., k].real))
+    return c
+
+
+class _RfftStage(torch.autograd.Function):
+    """(rows, nlon) float32 -> (rows, nmodes) complex64 = scale * rfft(norm="forward"), kept / zero-padded to nmodes."""
+
+    @staticmethod
+    def forward(ctx, x, nmodes, scale):
+        ctx.nlon, ctx.nmodes, ctx.scale = x.shape[-1], nmodes, scale
+        xc = x.contiguous()
+        out = torch.empty(xc.shape[:-1] + (nmodes,), dtype=torch.complex64, device=x.device)
+        rows = xc.numel() // xc.shape[-1] if xc.numel() else 0
+        with torch.cuda.device(x.device):
+            _lib.check(_lib.load().shtb200_rfft_modes(ctypes.c_void_p(xc.data_ptr()), ctypes.c_void_p(out.data_ptr()), rows, xc.shape[-1], nmodes, scale, _stream(x)), "shtb200_rfft_modes")
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        # adjoint: (scale / nlon) * unnormalised c2r of the cotangent with interior bins halved
+        w = _edge_weights(ctx.nmodes, ctx.nlon, 0.5, g.device) * (ctx.scale / ctx.nlon)
+        return _IrfftStage.apply((g * w).contiguous(), ctx.nlon), None, None
+
+
+class _IrfftStage(torch.autograd.Function):
+    """(rows, nmodes) complex64 -> (rows, nlon) float32: unnormalised c2r, imaginary parts of DC / Nyquist ignored."""
+
+    @staticmethod
+    def forward(ctx, c, nlon):
+        ctx.nlon, ctx.nmodes = nlon, c.shape[-1]
+        cc = c.contiguous()
+        out = torch.empty(cc.shape[:-1] + (nlon,), dtype=torch.float32, device=c.device)
+        rows = cc.numel() // cc.shape[-1] if cc.numel() else 0
+        with torch.cuda.device(c.device):
+            _lib.check(_lib.load().shtb200_irfft_modes(ctypes.c_void_p(cc.data_ptr()), ctypes.c_void_p(out.data_ptr()), rows, nlon, cc.shape[-1], _stream(c)), "shtb200_irfft_modes")
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        # adjoint: unnormalised r2c, interior bins doubled, imaginary parts of DC / Nyquist zeroed
+        r = _RfftStage.apply(g.contiguous(), ctx.nmodes, float(ctx.nlon))
+        w = _edge_weights(ctx.nmodes, ctx.nlon, 2.0, g.device)
+        return _zero_edge_imag(r * w, ctx.nlon), None
+
+
+class _LegendreStage(torch.autograd.Function):
+    """Contraction with the packed table for the local orders [m0, m0 + mloc): (N, nlat, mloc) <-> (N, lmax, mloc)."""
+
+    @staticmethod
+    def forward(ctx, x, owner, adjoint, out_rows):
+        ctx.owner, ctx.adjoint, ctx.in_rows = owner, adjoint, x.shape[-2]
+        xc = x.contiguous()
+        n, mloc = xc.shape[0], xc.shape[-1]
+        out = torch.empty((n, out_rows, mloc), dtype=torch.complex64, device=x.device)
+        if n == 0 or mloc == 0:
+            return out
+        plan = owner._plan(x.device, adjoint)
+        ws = torch.empty(max(plan.legendre_workspace_bytes(n, mloc), 1), dtype=torch.uint8, device=x.device)
+        with torch.cuda.device(x.device):
+            plan.legendre(xc, out, n, owner._m0, mloc, ws, torch.cuda.current_stream(x.device).cuda_stream)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        return _LegendreStage.apply(g.contiguous(), ctx.owner, not ctx.adjoint, ctx.in_rows), None, None, None
+
+
+class _DistributedBase(nn.Module):
+    def __init__(self, nlat, nlon, lmax, mmax, grid, norm, csphase):
+        super().__init__()
+        self.nlat, self.nlon, self.grid, self.norm, self.csphase = nlat, nlon, grid, norm, csphase
+        self.engine = _default_engine()
+        self._tq, self._quad_w = sht_colatitudes(nlat, grid)  # raises ValueError("Unknown quadrature mode")
+        self.comm_size_polar = polar_group_size()
+        self.comm_rank_polar = polar_group_rank()
+        self.comm_size_azimuth = azimuth_group_size()
+        self.comm_rank_azimuth = azimuth_group_rank()
+        self.lmax, self.mmax = truncate_sht(nlat, nlon, lmax, mmax, grid)
+        self.lat_shapes = compute_split_shapes(self.nlat, self.comm_size_polar)
+        self.nlat_local = self.lat_shapes[self.comm_rank_polar]
+        self.lon_shapes = compute_split_shapes(self.nlon, self.comm_size_azimuth)
+        self.nlon_local = self.lon_shapes[self.comm_rank_azimuth]
+        self.l_shapes = compute_split_shapes(self.lmax, self.comm_size_polar)
+        self.lmax_local = self.l_shapes[self.comm_rank_polar]
+        self.m_shapes = compute_split_shapes(self.mmax, self.comm_size_azimuth)
+        self.mmax_local = self.m_shapes[self.comm_rank_azimuth]
+        self._m0 = sum(self.m_shapes[: self.comm_rank_azimuth])
+        self._plans = {}
+
+    def extra_repr(self):
+        return f"nlat={self.nlat}, nlon={self.nlon},\n lmax={self.lmax}, mmax={self.mmax},\n grid={self.grid}, csphase={self.csphase}"
+
+    def _full_table(self):
+        raise NotImplementedError
+
+    def _plan(self, device, adjoint):
+        key = (device.index, adjoint, self.engine)
+        pl = self._plans.get(key)
+        if pl is None:
+            with torch.cuda.device(device):
+                t32 = self._full_table().to(device=device, dtype=torch.float32).contiguous()
+                pl = _lib.Plan(self._adj_kind if adjoint else self._kind, self.nlat, self.nlon, self.lmax, self.mmax, t32, engine=self.engine)
+                del t32
+            self._plans[key] = pl
+        return pl
+
+
+class DistributedRealSHT(_DistributedBase):
+    """Forward SHT on a local tile: ``(..., nlat_local, nlon_local)`` float32 -> ``(..., lmax_local, mmax_local)`` complex64."""
+
+    _kind, _adj_kind = _lib.SHT, _lib.SHT_ADJOINT
+
+    def __init__(self, nlat, nlon, lmax=None, mmax=None, grid="equiangular", norm="ortho", csphase=True):
+        super().__init__(nlat, nlon, lmax, mmax, grid, norm, csphase)
+        weights = self._full_table()
+        # the module keeps this rank's orders only, like the reference (distributed_sht.py:164)
+        weights = split_tensor_along_dim(weights, dim=0, num_chunks=self.comm_size_azimuth)[self.comm_rank_azimuth].contiguous()
+        self.register_buffer("weights", weights, persistent=False)
+
+    def _full_table(self):
+        pct = _precompute_legpoly(self.mmax, self.lmax, self._tq, norm=self.norm, csphase=self.csphase)
+        return (pct * self._quad_w.to(pct.device)[None, None, :]).contiguous()
+
+    def forward(self, x: torch.Tensor):
+        torch._check(x.dim() >= 3, lambda: f"Expected tensor with at least 3 dimensions but got {x.dim()} instead")
+        torch._check(x.shape[-2] == self.nlat_local, lambda: f"Expected latitudes shape[-2]=={self.nlat_local}, got {x.shape[-2]}")
+        torch._check(x.shape[-1] == self.nlon_local, lambda: f"Expected longitudes shape[-1]=={self.nlon_local}, got {x.shape[-1]}")
+        _require(x, torch.float32, "DistributedRealSHT")
+
+        x, lead_shape, lead_size = flatten_and_pad_leading_dims(x, max(self.comm_size_polar, self.comm_size_azimuth))
+        num_chans = x.shape[-3]
+        # fields get sharded over the azimuth group, longitudes become local
+        if self.comm_size_azimuth > 1:
+            x = distributed_transpose_azimuth(x, (-3, -1), self.lon_shapes)
+        x = _RfftStage.apply(x, self.mmax, 2.0 * math.pi)
+        # orders get sharded, fields local again
+        if self.comm_size_azimuth > 1:
+            x = distributed_transpose_azimuth(x, (-1, -3), compute_split_shapes(num_chans, self.comm_size_azimuth))
+        # fields get sharded over the polar group, latitudes become local
+        if self.comm_size_polar > 1:
+            x = distributed_transpose_polar(x, (-3, -2), self.lat_shapes)
+        x = _LegendreStage.apply(x, self, False, self.lmax)
+        # degrees get sharded, fields local again
+        if self.comm_size_polar > 1:
+            x = distributed_transpose_polar(x, (-2, -3), compute_split_shapes(num_chans, self.comm_size_polar))
+        return unpad_and_unflatten_leading_dims(x, lead_shape, lead_size)
+
+
+class DistributedInverseRealSHT(_DistributedBase):
+    """Inverse SHT on a local tile: ``(..., lmax_local, mmax_local)`` complex64 -> ``(..., nlat_local, nlon_local)`` float32."""
+
+    _kind, _adj_kind = _lib.ISHT, _lib.ISHT_ADJOINT
+
+    def __init__(self, nlat, nlon, lmax=None, mmax=None, grid="equiangular", norm="ortho", csphase=True):
+        super().__init__(nlat, nlon, lmax, mmax, grid, norm, csphase)
+        pct = self._full_table()
+        pct = split_tensor_along_dim(pct, dim=0, num_chunks=self.comm_size_azimuth)[self.comm_rank_azimuth].contiguous()
+        self.register_buffer("pct", pct, persistent=False)
+
+    def _full_table(self):
+        pct = _precompute_legpoly(self.mmax, self.lmax, self._tq, norm=self.norm, inverse=True, csphase=self.csphase)
+        return pct.permute(0, 2, 1).contiguous()
+
+    def forward(self, x: torch.Tensor):
+        torch._check(x.dim() >= 3, lambda: f"Expected tensor with at least 3 dimensions but got {x.dim()} instead")
+        torch._check(x.shape[-2] == self.lmax_local, lambda: f"Expected spherical harmonic degrees (lmax) shape[-2]=={self.lmax_local}, got {x.shape[-2]}")
+        torch._check(x.shape[-1] == self.mmax_local, lambda: f"Expected spherical harmonic orders (mmax) shape[-1]=={self.mmax_local}, got {x.shape[-1]}")
+        _require(x, torch.complex64, "DistributedInverseRealSHT")
+
+        x, lead_shape, lead_size = flatten_and_pad_leading_dims(x, max(self.comm_size_polar, self.comm_size_azimuth))
+        num_chans = x.shape[-3]
+        if self.comm_size_polar > 1:
+            x = distributed_transpose_polar(x, (-3, -2), self.l_shapes)
+        x = _LegendreStage.apply(x, self, False, self.nlat)
+        if self.comm_size_polar > 1:
+            x = distributed_transpose_polar(x, (-2, -3), compute_split_shapes(num_chans, self.comm_size_polar))
+        if self.comm_size_azimuth > 1:
+            x = distributed_transpose_azimuth(x, (-3, -1), self.m_shapes)
+        x = _IrfftStage.apply(x, self.nlon)
+        if self.comm_size_azimuth > 1:
+            x = distributed_transpose_azimuth(x, (-1, -3), compute_split_shapes(num_chans, self.comm_size_azimuth))
+        return unpad_and_unflatten_leading_dims(x, lead_shape, lead_size)

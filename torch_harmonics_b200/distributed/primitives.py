@@ -1,0 +1,171 @@
+"""Differentiable all-to-all transposes and the split helpers of the distributed transforms.
+
+Same functions as torch_harmonics/distributed/primitives.py:74-347 and :775-822.  A transpose trades a sharded
+axis for a shard of another one: the tensor arrives sharded along ``dims[1]`` (every rank holds a slice of it and
+all of ``dims[0]``) and leaves sharded along ``dims[0]`` with ``dims[1]`` complete.  Chunks are balanced and may be
+uneven (``compute_split_shapes``).
+
+The exchange itself is ONE ``all_to_all_single`` over NCCL on a send buffer packed peer-major by a single
+``movedim(...).contiguous()`` (the reference copies every chunk separately and uses the list form).  Backends
+without all-to-all (gloo, used by the CPU tests) go through point-to-point sends.
+"""
+
+from typing import List
+
+import torch
+import torch.distributed as dist
+
+from .utils import azimuth_group, azimuth_group_size, config, is_distributed_azimuth, is_distributed_polar, polar_group, polar_group_size
+
+
+def compute_split_shapes(size: int, num_chunks: int) -> List[int]:
+    """Balanced chunk sizes: the first ``size % num_chunks`` chunks get one extra element.
+    Raises RuntimeError when ``size < num_chunks`` (every chunk must be non-empty)."""
+    torch._check(size >= num_chunks, lambda: f"Cannot split {size} elements into {num_chunks} chunks; every chunk must be non-empty.")
+    base, rem = divmod(size, num_chunks)
+    return [base + 1] * rem + [base] * (num_chunks - rem)
+
+
+def split_tensor_along_dim(tensor, dim, num_chunks):
+    """Views of ``tensor`` cut into balanced chunks along ``dim``."""
+    torch._check(len(tensor.shape) > dim, lambda: f"Error, tensor dimension is {len(tensor.shape)} which cannot be split along {dim}")
+    torch._check(tensor.shape[dim] >= num_chunks, lambda: f"Error, cannot split dim {dim} of size {tensor.shape[dim]} into {num_chunks} chunks. Empty slices are currently not supported.")
+    return torch.split(tensor, compute_split_shapes(tensor.shape[dim], num_chunks), dim=dim)
+
+
+def flatten_and_pad_leading_dims(tensor: torch.Tensor, min_leading_size: int, num_trailing_dims: int = 2):
+    """Collapse all but the trailing dims into one leading axis and zero-pad it up to ``min_leading_size``
+    (the transposes redistribute this axis, so it must be at least as long as the larger group)."""
+    lead_shape = tensor.shape[:-num_trailing_dims]
+    tensor = tensor.reshape(-1, *tensor.shape[-num_trailing_dims:])
+    lead_size = tensor.shape[0]
+    if lead_size < min_leading_size:
+        tensor = torch.cat([tensor, tensor.new_zeros((min_leading_size - lead_size, *tensor.shape[1:]))], dim=0)
+    return tensor.contiguous(), lead_shape, lead_size
+
+
+def unpad_and_unflatten_leading_dims(tensor: torch.Tensor, lead_shape, lead_size: int, num_trailing_dims: int = 2) -> torch.Tensor:
+    """Inverse of :func:`flatten_and_pad_leading_dims`."""
+    tensor = tensor.narrow(0, 0, lead_size)
+    return tensor.reshape(*lead_shape, *tensor.shape[-num_trailing_dims:]).contiguous()
+
+
+def _verify(msg, local_value, expected, group):
+    """Debug mode: gather one integer per rank and compare with the expected per-rank list."""
+    t = torch.tensor([local_value], dtype=torch.int64)
+    if dist.get_backend(group) == "nccl":
+        t = t.cuda()
+    gathered = [torch.empty_like(t) for _ in range(dist.get_world_size(group))]
+    dist.all_gather(gathered, t, group=group)
+    got = [int(g.item()) for g in gathered]
+    for idx, (a, b) in enumerate(zip(got, expected)):
+        if a != b:
+            raise ValueError(f"{msg} shapes are not correct. Expected {b}, got {a} for index {idx}. Please check that the number of chunks is correct.")
+
+
+def _exchange(send: torch.Tensor, send_counts, recv_counts, group):
+    """Flat all-to-all with per-peer element counts."""
+    recv = send.new_empty(sum(recv_counts))
+    if dist.get_backend(group) == "nccl":
+        dist.all_to_all_single(recv, send, output_split_sizes=list(recv_counts), input_split_sizes=list(send_counts), group=group)
+        return recv
+    # point-to-point fallback
+    rank = dist.get_rank(group)
+    size = dist.get_world_size(group)
+    ranks = dist.get_process_group_ranks(group)
+    soff = [0]
+    roff = [0]
+    for a, b in zip(send_counts, recv_counts):
+        soff.append(soff[-1] + a)
+        roff.append(roff[-1] + b)
+    reqs = []
+    for peer in range(size):
+        if peer == rank:
+            recv[roff[peer]:roff[peer + 1]] = send[soff[peer]:soff[peer + 1]]
+            continue
+        reqs.append(dist.isend(send[soff[peer]:soff[peer + 1]].contiguous(), dst=ranks[peer], group=group))
+    bufs = {}
+    for peer in range(size):
+        if peer == rank:
+            continue
+        bufs[peer] = send.new_empty(recv_counts[peer])
+        reqs.append(dist.irecv(bufs[peer], src=ranks[peer], group=group))
+    for r in reqs:
+        r.wait()
+    for peer, b in bufs.items():
+        recv[roff[peer]:roff[peer + 1]] = b
+    return recv
+
+
+def _transpose(x: torch.Tensor, dim0: int, dim1: int, dim1_split_sizes, group):
+    """Scatter ``dim0``, gather ``dim1`` across ``group``; returns the redistributed contiguous tensor."""
+    size = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    if size == 1:
+        return x
+    nd = x.dim()
+    dim0 %= nd
+    dim1 %= nd
+    if config.debug:
+        _verify("_transpose: error, dim1_split_sizes", x.shape[dim1], list(dim1_split_sizes), group)
+    is_complex = x.is_complex()
+    xr = torch.view_as_real(x) if is_complex else x  # trailing (re, im) axis does not move
+    # peer-major send buffer: dim0 first
+    send = xr.movedim(dim0, 0).contiguous()
+    d0 = compute_split_shapes(x.shape[dim0], size)
+    per_row = send[0].numel() if send.shape[0] > 0 else 0
+    send_counts = [c * per_row for c in d0]
+    # what arrives from peer j: my dim0 chunk, with dim1 of length dim1_split_sizes[j]
+    rest = per_row // x.shape[dim1]
+    recv_counts = [d0[rank] * rest * s for s in dim1_split_sizes]
+    recv = _exchange(send.reshape(-1), send_counts, recv_counts, group)
+    # unpack: piece j has the send layout (dim0 first) with dim1 -> split j
+    shape_moved = list(send.shape)
+    d1_moved = dim1 + 1 if dim1 < dim0 else dim1  # position of dim1 after dim0 moved to the front
+    pieces = []
+    off = 0
+    for j, s in enumerate(dim1_split_sizes):
+        shp = list(shape_moved)
+        shp[0] = d0[rank]
+        shp[d1_moved] = s
+        n = recv_counts[j]
+        pieces.append(recv[off:off + n].view(shp))
+        off += n
+    out = torch.cat(pieces, dim=d1_moved).movedim(0, dim0).contiguous()
+    return torch.view_as_complex(out) if is_complex else out
+
+
+class _Transpose(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, dims, dim1_split_sizes, which):
+        group = azimuth_group() if which == "azimuth" else polar_group()
+        active = is_distributed_azimuth() if which == "azimuth" else is_distributed_polar()
+        ctx.which, ctx.dims, ctx.active = which, dims, active
+        x = x.contiguous()
+        if not active:
+            return x
+        gsize = azimuth_group_size() if which == "azimuth" else polar_group_size()
+        ctx.dim0_split_sizes = compute_split_shapes(x.shape[dims[0]], gsize)
+        return _transpose(x, dims[0], dims[1], dim1_split_sizes, group)
+
+    @staticmethod
+    def backward(ctx, go):
+        go = go.contiguous()
+        if not ctx.active:
+            return go, None, None, None
+        group = azimuth_group() if ctx.which == "azimuth" else polar_group()
+        gi = _transpose(go, ctx.dims[1], ctx.dims[0], ctx.dim0_split_sizes, group)
+        return gi, None, None, None
+
+
+@torch.compiler.disable()
+def distributed_transpose_azimuth(input_, dims_, shapes_):
+    """All-to-all transpose across the azimuth group: sharded along ``dims_[1]`` in, sharded along ``dims_[0]`` out.
+    ``shapes_`` lists the per-rank lengths along ``dims_[1]``."""
+    return _Transpose.apply(input_, dims_, shapes_, "azimuth")
+
+
+@torch.compiler.disable()
+def distributed_transpose_polar(input_, dims_, shapes_):
+    """Same across the polar group."""
+    return _Transpose.apply(input_, dims_, shapes_, "polar")

@@ -1,0 +1,95 @@
+"""Process-grid registry of the spatially distributed transforms.
+
+Two orthogonal process groups describe a 2-D grid over the sphere: the polar group shards latitudes / degrees,
+the azimuth group shards longitudes / orders.  Same public functions and defaults (size 1, rank 0 when a group
+is not registered) as torch_harmonics/distributed/utils.py:73-209.
+"""
+
+import os
+
+import torch.distributed as dist
+
+_POLAR_GROUP = None
+_AZIMUTH_GROUP = None
+_INITIALIZED = False
+
+
+class _DistributedConfig:
+    """Runtime switches; ``debug`` turns on the split-shape verification all-gathers
+    (env default ``TORCH_HARMONICS_DISTRIBUTED_DEBUG=1``, torch_harmonics/distributed/utils.py:43-70)."""
+
+    def __init__(self):
+        self._debug = None
+
+    @property
+    def debug(self):
+        if self._debug is None:
+            return os.getenv("TORCH_HARMONICS_DISTRIBUTED_DEBUG", "0") == "1"
+        return self._debug
+
+    @debug.setter
+    def debug(self, value):
+        self._debug = bool(value)
+
+    def __repr__(self):
+        return f"_DistributedConfig(debug={self.debug})"
+
+
+config = _DistributedConfig()
+
+
+def init(polar_process_group, azimuth_process_group):
+    """Register the polar and azimuth process groups (either may be None for an undistributed axis)."""
+    global _POLAR_GROUP, _AZIMUTH_GROUP, _INITIALIZED
+    _POLAR_GROUP = polar_process_group
+    _AZIMUTH_GROUP = azimuth_process_group
+    _INITIALIZED = True
+
+
+def finalize():
+    """Destroy the registered groups and reset the registry."""
+    global _POLAR_GROUP, _AZIMUTH_GROUP, _INITIALIZED
+    if _INITIALIZED:
+        if _POLAR_GROUP is not None:
+            dist.destroy_process_group(_POLAR_GROUP)
+            _POLAR_GROUP = None
+        if _AZIMUTH_GROUP is not None:
+            dist.destroy_process_group(_AZIMUTH_GROUP)
+            _AZIMUTH_GROUP = None
+    _INITIALIZED = False
+
+
+def is_initialized() -> bool:
+    return _INITIALIZED
+
+
+def polar_group():
+    return _POLAR_GROUP
+
+
+def azimuth_group():
+    return _AZIMUTH_GROUP
+
+
+def is_distributed_polar() -> bool:
+    return _POLAR_GROUP is not None
+
+
+def is_distributed_azimuth() -> bool:
+    return _AZIMUTH_GROUP is not None
+
+
+def polar_group_size() -> int:
+    return dist.get_world_size(group=_POLAR_GROUP) if is_distributed_polar() else 1
+
+
+def azimuth_group_size() -> int:
+    return dist.get_world_size(group=_AZIMUTH_GROUP) if is_distributed_azimuth() else 1
+
+
+def polar_group_rank() -> int:
+    return dist.get_rank(group=_POLAR_GROUP) if is_distributed_polar() else 0
+
+
+def azimuth_group_rank() -> int:
+    return dist.get_rank(group=_AZIMUTH_GROUP) if is_distributed_azimuth() else 0

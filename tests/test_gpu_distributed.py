@@ -102,12 +102,12 @@ def _dist_worker(rank, world, port, gh, gw):
         xl = _tile(x, -2, -1, gh, gw, rh, rw).requires_grad_(True)
         cl = dsht(xl)
         cl.backward(_tile(gc, -2, -1, gh, gw, rh, rw))
-        scale = float(cs.abs().max())
+        scale = float(cs.detach().abs().max())
         e1 = float((cl.detach() - _tile(cs.detach(), -2, -1, gh, gw, rh, rw)).abs().max()) / scale
         e2 = float((xl.grad - _tile(xs.grad, -2, -1, gh, gw, rh, rw)).abs().max()) / float(xs.grad.abs().max())
         c0 = cs.detach().clone().requires_grad_(True)
         ys = isht(c0)
-        gy = torch.randn_like(ys)
+        gy = torch.randn(ys.shape, device="cuda", generator=gen)  # same numbers on every rank
         ys.backward(gy)
         cloc = _tile(cs.detach(), -2, -1, gh, gw, rh, rw).requires_grad_(True)
         yl = disht(cloc)

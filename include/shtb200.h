@@ -91,6 +91,26 @@ int shtb200_execute(shtb200_plan *plan, const void *in_dev, void *out_dev, int n
  */
 int shtb200_execute_host(shtb200_plan *plan, const void *in_host, void *out_host, int nfields, void *stream);
 
+/*
+ * shtb200_execute for callers that are not allowed to allocate device memory (no counterpart in the reference).
+ * Same transform and arguments as shtb200_execute, minus the workspace: the scratch is a device array of
+ * SHTB200_STATIC_SCRATCH_BYTES built into the library, so the call itself performs no cudaMalloc / cudaFree and calls
+ * no allocating library routine.  Meant for hosts that cannot allocate at call time: code inside a stream capture,
+ * latency-bound serving loops with a fixed memory plan, plug-ins with a fixed device budget.
+ *   - fails with SHTB200_EWORKSPACE (and says how much was needed) when shtb200_workspace_bytes(plan, nfields)
+ *     exceeds SHTB200_STATIC_SCRATCH_BYTES; fails with SHTB200_EINVAL while per-kernel profiling is switched on;
+ *   - the first call on each device looks up the array's device address (cudaGetSymbolAddress); make that first call
+ *     before any stream capture begins;
+ *   - all calls on a device share the one array and it keeps whatever the previous call left in it: the transform
+ *     overwrites everything it later reads, so nothing has to be cleared between calls, but two calls that overlap
+ *     on the GPU (different streams, no dependency) race on it — serialise them;
+ *   - every GPU that loads the library holds the array until the process exits.
+ * The plan must have been created (that step allocates) before the phase in which allocation is forbidden.
+ */
+#define SHTB200_STATIC_SCRATCH_BYTES (32u * 1024u * 1024u)
+size_t shtb200_static_scratch_bytes(void);
+int shtb200_execute_static_scratch(shtb200_plan *plan, const void *in_dev, void *out_dev, int nfields, void *stream);
+
 /* Introspection used by the tests and the benchmark. */
 int shtb200_plan_info(const shtb200_plan *plan, int *nlat, int *nlon, int *lmax, int *mmax, int *kind, int *engine);
 /* Kernel launches the last shtb200_execute on this plan enqueued. */

@@ -55,7 +55,7 @@ class ClockSampler:
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             os.close(fd)
             self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100"],
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "20"],
                 stdout=open(self.path, "w"), stderr=subprocess.DEVNULL,
             )
         except Exception:
@@ -194,14 +194,16 @@ def run_ours(args):
 
     for _ in range(max(args.warmup, 3)):
         step()
+    # clocks are sampled from before the timed round-trip loop until the separately timed forward / inverse loops end
+    # (all three run the same kernels back to back; a single loop of 20 steps is shorter than one sampling period)
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
     t_step = time_steps(step, args.steps, barrier)
-    barrier()
-    clocks = sampler.stop() if rank == 0 else None
     t_fwd = time_steps(fwd, args.steps, barrier)
     t_inv = time_steps(inv, args.steps, barrier)
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
 
     # per-kernel times from events recorded between the launches (separate pass, not the timed one)
     names_f = ["fft_analysis", "legendre_analysis", "unpack_coeffs"]
@@ -353,7 +355,7 @@ def run_reference(args):
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--nfields", type=int, default=73)

@@ -162,42 +162,22 @@ legendre_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                 if (!(ok = ptx::mbar_wait_bounded(bar_accempty(a), pha ^ 1u, abort_flag, WAIT_LIMIT))) break;
                 ptx::tc_fence_after();
                 const uint32_t d = tmem_base + (uint32_t)(a * BN_MAX);
-                // One MMA consumes 8 contraction indices: 32 bytes along a K-major row, one 1 KiB (two 4-row groups) step of a
-                // column-major tile.  The full-precision product of a k-step needs only the landed stage, the two correction
-                // products also need the splitter's output; issuing the former one k-step ahead of the latter keeps the
-                // tensor pipe busy while the splitter works.
-                const uint64_t bstep = gp.b_mn ? (uint64_t)(1024 >> 4) : (uint64_t)(32 >> 4);
-                auto desc_b = [&](uint32_t addr) { return gp.b_mn ? ptx::smem_desc_sw128_mn(addr, B_BLK_BYTES) : ptx::smem_desc_sw128(addr); };
-                auto issue_main = [&](int stage, bool first) {
-                    const uint32_t hi = stage0 + stage * STAGE_BYTES;
-                    const uint64_t ah = ptx::smem_desc_sw128(hi), bh = desc_b(hi + B_OFF);
-#pragma unroll
-                    for (int k8 = 0; k8 < TK / 8; ++k8)
-                        ptx::mma_tf32(d, ah + (uint64_t)((k8 * 32) >> 4), bh + bstep * k8, idesc, (first && k8 == 0) ? 0u : 1u);
-                };
-                int sm = s;          // stage whose main product is issued next
-                uint32_t phm = ph;
-                if (!(ok = ptx::mbar_wait_bounded(bar_full(sm), phm, abort_flag, WAIT_LIMIT))) break;
-                ptx::tc_fence_after();
-                issue_main(sm, true);
-                if (++sm == NSTAGE) { sm = 0; phm ^= 1u; }
                 for (int ks = 0; ks < w.ksteps; ++ks) {
-                    if (ks + 1 < w.ksteps) {
-                        if (!(ok = ptx::mbar_wait_bounded(bar_full(sm), phm, abort_flag, WAIT_LIMIT))) break;
-                        ptx::tc_fence_after();
-                        issue_main(sm, false);
-                        if (++sm == NSTAGE) { sm = 0; phm ^= 1u; }
-                    }
+                    if (!(ok = ptx::mbar_wait_bounded(bar_full(s), ph, abort_flag, WAIT_LIMIT))) break;
                     if (!(ok = ptx::mbar_wait_bounded(bar_lofull(c), phc, abort_flag, WAIT_LIMIT))) break;
                     ptx::tc_fence_after();
                     const uint32_t hi = stage0 + s * STAGE_BYTES, lo = lo0 + c * STAGE_BYTES;
                     const uint64_t ah = ptx::smem_desc_sw128(hi), al = ptx::smem_desc_sw128(lo);
-                    const uint64_t bh = desc_b(hi + B_OFF), bl = desc_b(lo + B_OFF);
+                    const uint64_t bh = gp.b_mn ? ptx::smem_desc_sw128_mn(hi + B_OFF, B_BLK_BYTES) : ptx::smem_desc_sw128(hi + B_OFF);
+                    const uint64_t bl = gp.b_mn ? ptx::smem_desc_sw128_mn(lo + B_OFF, B_BLK_BYTES) : ptx::smem_desc_sw128(lo + B_OFF);
+                    // one MMA consumes 8 contraction indices: 32 bytes along a K-major row, one 8-row (1 KiB) group of a column-major tile
+                    const uint64_t bstep = gp.b_mn ? (uint64_t)(1024 >> 4) : (uint64_t)(32 >> 4);
 #pragma unroll
                     for (int k8 = 0; k8 < TK / 8; ++k8) {
                         const uint64_t koff = (uint64_t)((k8 * 32) >> 4), kb = bstep * k8;
-                        ptx::mma_tf32(d, al + koff, bh + kb, idesc, 1u);
+                        ptx::mma_tf32(d, al + koff, bh + kb, idesc, (ks | k8) ? 1u : 0u);  // small terms first
                         ptx::mma_tf32(d, ah + koff, bl + kb, idesc, 1u);
+                        ptx::mma_tf32(d, ah + koff, bh + kb, idesc, 1u);
                     }
                     ptx::tc_commit(bar_empty(s));
                     ptx::tc_commit(bar_loempty(c));

@@ -126,6 +126,8 @@ __global__ void __launch_bounds__(256) coeff_slab_transpose_kernel(float2 *__res
     __shared__ int s_rows[64];
     const int mb0 = blockIdx.x * 32, l0 = blockIdx.y * 64, f = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // tiles entirely above the diagonal (every l < every m) hold no coefficient: nothing to read for the slabs
+    if (TO_SLABS && l0 + 63 < m0 + mb0) return;
 
     if (threadIdx.x < 64) {  // the 32 x 2 (order, parity) groups this tile touches
         const int mi = mb0 + (threadIdx.x >> 1);

@@ -58,12 +58,12 @@ WsLayout ws_layout(const Plan &pl, int nfields, int m0, int mloc) {
     const size_t ncols = (size_t)(pl.vector ? 4 : 2) * nfields;
     const size_t ncp = (ncols + 3) / 4 * 4;  // row pitch of the column-contiguous operands
     if (pl.analysis) {
-        w.op_bytes = (size_t)2 * mloc * pl.Ka * ncp * sizeof(float);
+        w.op_bytes = (size_t)2 * mloc * round_up(pl.Ka, kBK) * ncp * sizeof(float);
         if (!pl.vector) w.y_bytes = (size_t)(pl.group_b0[2 * (m0 + mloc)] - pl.group_b0[2 * m0]) * ncols * kBK * sizeof(float);
     } else {
         const long long slabs = pl.group_b0[2 * (m0 + mloc)] - pl.group_b0[2 * m0];
         w.op_bytes = (size_t)slabs * ncols * kBK * sizeof(float);
-        w.y_bytes = (size_t)2 * mloc * pl.Kh * ncp * sizeof(float);
+        w.y_bytes = (size_t)2 * mloc * round_up(pl.Kh, kBK) * ncp * sizeof(float);
     }
     return w;
 }
@@ -85,6 +85,7 @@ GemmParams gemm_params(const Plan &pl, int nfields, int m0, int mloc, const floa
     if (pl.analysis) {
         gp.b_mn = 1;
         gp.b_krows = pl.Ka;
+        gp.b_groups = 2 * mloc;
         gp.b_pitch = round_up(gp.ncols, 4);
         gp.b_dx = kBK;
         gp.b_kext = pl.Ka;
@@ -99,7 +100,7 @@ GemmParams gemm_params(const Plan &pl, int nfields, int m0, int mloc, const floa
         gp.b_unit0 = pl.group_b0[2 * m0];
         gp.mode = EPI_LATROWS;
         gp.out_ld = round_up(gp.ncols, 4);
-        gp.out_rows = pl.Kh;
+        gp.out_groups = 2 * mloc;
     }
     return gp;
 }
@@ -126,8 +127,9 @@ int run_gemm(Plan &pl, const GemmParams &gp, cudaStream_t st) {
 int clear_empty_groups(const Plan &pl, float *Y, int ncols, int m0, int mloc, cudaStream_t st) {
     for (int g = 2 * m0; g < 2 * (m0 + mloc); ++g) {
         if (pl.group_kblocks[g] == 0) {
-            const size_t slice = (size_t)pl.Kh * round_up(ncols, 4);
-            SHT_CUDA_CHECK(cudaMemsetAsync(Y + (size_t)(g - 2 * m0) * slice, 0, sizeof(float) * slice, st));
+            const size_t ncp = round_up(ncols, 4);
+            for (int k0 = 0; k0 < pl.Kh; k0 += kBK)  // the group's rows come in 32-row blocks
+                SHT_CUDA_CHECK(cudaMemsetAsync(Y + (size_t)blocked_row(g - 2 * m0, k0, 2 * mloc) * ncp, 0, sizeof(float) * kBK * ncp, st));
         }
     }
     return SHTB200_OK;

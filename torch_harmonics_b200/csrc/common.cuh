@@ -70,7 +70,7 @@ constexpr int kItemRowsMax = 128;  // one 128-row tensor-core tile
 // How a finished tile leaves the contraction kernel.
 enum EpilogueMode : int {
     EPI_COEFFS = 0,   // analysis: rows are degrees l = m + p + 2 r  -> complex64 out[n][l][m - m0]
-    EPI_LATROWS = 1,  // synthesis: rows are folded latitudes k'      -> float Y[group * out_rows + k'][col] (row pitch ld)
+    EPI_LATROWS = 1,  // synthesis: rows are folded latitudes k'      -> float Y[blocked_row(group, k')][col] (row pitch ld)
     EPI_SLABS = 2,    // analysis: rows are degrees -> float Z[(slab0[g] + r / 32) * ncols + col][r % 32], the same
                       // degree-slab layout the synthesis contraction reads its coefficients from
 };
@@ -82,8 +82,9 @@ struct GemmParams {
     long long b_pitch;    // floats per operand row
     int a_dx, b_dx;       // see above
     int a_kext, b_kext;   // valid extent of the inner (k) axis of a row (reads beyond it yield 0)
-    int b_mn;             // 1: B is column-contiguous, element (col, k) of group u at B[((u - b_unit0) * b_krows + k) * b_pitch + col]
-    int b_krows;          // b_mn: rows (contraction indices) per group
+    int b_mn;             // 1: B is column-contiguous, element (col, k) of group u at B[blocked_row(u - b_unit0, k, b_groups) * b_pitch + col]
+    int b_krows;          // b_mn: valid contraction indices per group
+    int b_groups;         // b_mn: groups held in B
     int ncols;            // columns of the product = 2 * nfields (4 * pairs for vector kinds)
     long long b_unit0;    // operand origin (same units as GemmItem::b_y0) of the first order held in B
     const GemmItem *items;
@@ -92,8 +93,8 @@ struct GemmParams {
     float *out;           // destination
     int lmax, mmax_out;   // EPI_COEFFS: out dims (mmax_out = number of orders stored = mloc)
     int m0;               // first order stored in out (orders outside [m0, m0 + mmax_out) are skipped)
-    long long out_ld;     // EPI_LATROWS: floats per row of Y[(group * out_rows + k')][col]
-    int out_rows;         // EPI_LATROWS: rows per group of Y
+    long long out_ld;     // EPI_LATROWS: floats per row of Y
+    int out_groups;       // EPI_LATROWS: groups held in Y
     const long long *slab0;  // EPI_SLABS: first slab of every group (device array, 2 * mmax + 1 entries)
     long long slab_unit0;    // EPI_SLABS: slab0 of the first order held in the output
 };
@@ -154,9 +155,9 @@ struct Plan {
 // ------------------------------------------------------------------------------------------------
 int build_fft_plan(int nlon, FftPlanDev *out, float2 **d_tw, unsigned short **d_perm);
 
-// analysis: rows of x -> folded, order-major operand X[group * Ka + k][col] (row pitch round_up(ncols, 4))
+// analysis: rows of x -> folded, order-major operand X[blocked_row(group, k)][col] (row pitch round_up(ncols, 4))
 int launch_fft_analysis(const Plan &pl, const float *x, float *X, int nfields, cudaStream_t st);
-// synthesis: Y[group * Kh + k'][col] -> rows of x
+// synthesis: Y[blocked_row(group, k')][col] -> rows of x
 int launch_fft_synthesis(const Plan &pl, const float *Y, float *x, int nfields, cudaStream_t st);
 // plain row transforms for the distributed stages
 int launch_rfft_modes(const float *in, float2 *out, long long nrows, int nlon, int nmodes, float scale, cudaStream_t st);
@@ -173,6 +174,12 @@ int launch_unpack_coeffs(const Plan &pl, const float *Z, float2 *c, int nfields,
 int launch_zero_upper(const Plan &pl, float2 *c, int nfields, int m0, int mloc, cudaStream_t st);
 int launch_fold_modes(const Plan &pl, const float2 *Xc, float *X, int nfields, int m0, int mloc, cudaStream_t st);
 int launch_unfold_modes(const Plan &pl, const float *Y, float2 *Xc, int nfields, int m0, int mloc, cudaStream_t st);
+
+// Row of (group, k) in the column-contiguous operands X and Y: 32-row blocks of k are outermost, then the group,
+// then k inside the block.  CTAs of the FFT kernels that run at the same time work on neighbouring k for ALL groups,
+// so with this order they fill / read one contiguous region of HBM instead of 2 * mmax far-apart ones, and the
+// 32 x columns tile the contraction loads per k-step is one contiguous piece.
+__host__ __device__ inline long long blocked_row(long long group, int k, int ngroups) { return (((long long)(k >> 5) * ngroups + group) << 5) + (k & 31); }
 
 inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 inline long long round_up(long long a, long long b) { return (a + b - 1) / b * b; }

@@ -390,7 +390,7 @@ __device__ __forceinline__ void load_tables(const FftPlanDev &fp, float2 *tw_s, 
 // (k', nlat-1-k') of NW / VEC consecutive fields (VEC = 1: scalar fields; VEC = 2: (theta, phi) component pairs), so
 // that what it emits for an order m is one contiguous run of 2 NW floats along the column axis of the operand.
 //
-// Operand layout (column-contiguous):  X[(2 m + p) * Ka + kk][col],  row pitch ncp floats, Ka = VEC * Kh.
+// Operand layout (column-contiguous):  X[blocked_row(2 m + p, kk)][col],  row pitch ncp floats, kk < Ka = VEC * Kh.
 //   scalar:  kk = k',  col = 2 f + (re, im);  p = 0 holds the even fold, p = 1 the odd fold.
 //   vector:  col = 4 f + c;  kk = k' contracts against the d/dtheta table and carries the fold of parity 1 - p,
 //            kk = Kh + k' contracts against the m/sin(theta) table and carries the fold of parity p; the four
@@ -412,6 +412,19 @@ __global__ void __launch_bounds__(32 * NW * G, (NW * G >= 16) ? 2 : 1) fft_analy
     const int kn = blockIdx.y;
     const int f0 = blockIdx.x * NF;  // field blocks vary fastest: CTAs that complete each other's 128-byte lines run together
     const int t = threadIdx.x / GT, lane = threadIdx.x % GT;  // transform index, index inside its group
+    const int Ka = VEC * Kh;
+    const int ngroups = 2 * mmax;
+    if (kn >= Kh) {
+        // rows of the last 32-row block beyond the contraction length: the contraction reads them, they must be zeros
+        const int kk = Ka + (kn - Kh);
+        const int w4 = 2 * NW / 4 * 1;  // float4 per run
+        for (int i = threadIdx.x; i < ngroups * (2 * NW / 4); i += blockDim.x) {
+            const int g = i / (2 * NW / 4), c = (i - g * (2 * NW / 4)) * 4;
+            if (2 * VEC * f0 + c < ncp) *reinterpret_cast<float4 *>(X + (size_t)blocked_row(g, kk, ngroups) * ncp + 2 * VEC * f0 + c) = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        (void)w4;
+        return;
+    }
     load_tables(fp, tw_s, perm_s);
 
     // ---- each group loads and folds its own pair of rows ----
@@ -472,7 +485,6 @@ __global__ void __launch_bounds__(32 * NW * G, (NW * G >= 16) ? 2 : 1) fft_analy
 
     // ---- emit the retained orders: one thread per order, 2 NW floats per (order, fold) ----
     const int nyq = n / 2;
-    const int Ka = VEC * Kh;
     for (int m = threadIdx.x; m < mmax; m += blockDim.x) {
         float e[2 * NW], o[2 * NW];  // (re, im) of the even / odd fold of every transform
         if (m <= nyq) {
@@ -495,8 +507,8 @@ __global__ void __launch_bounds__(32 * NW * G, (NW * G >= 16) ? 2 : 1) fft_analy
             for (int u = 0; u < 2 * NW; ++u) e[u] = o[u] = 0.f;
         }
         if (VEC == 1) {
-            float *ge = X + ((size_t)(2 * m) * Ka + kn) * ncp + 2 * f0;
-            float *go = X + ((size_t)(2 * m + 1) * Ka + kn) * ncp + 2 * f0;
+            float *ge = X + (size_t)blocked_row(2 * m, kn, ngroups) * ncp + 2 * f0;
+            float *go = X + (size_t)blocked_row(2 * m + 1, kn, ngroups) * ncp + 2 * f0;
 #pragma unroll
             for (int c = 0; c < 2 * NW; c += 4) {
                 if (2 * f0 + c < ncp) {
@@ -508,8 +520,8 @@ __global__ void __launch_bounds__(32 * NW * G, (NW * G >= 16) ? 2 : 1) fft_analy
             // transforms 2 q (theta component X0) and 2 q + 1 (phi component X1) of pair q
 #pragma unroll
             for (int p = 0; p < 2; ++p) {
-                float *ga = X + ((size_t)(2 * m + p) * Ka + kn) * ncp + 4 * f0;       // d/dtheta rows: fold 1 - p
-                float *gb = X + ((size_t)(2 * m + p) * Ka + Kh + kn) * ncp + 4 * f0;  // m/sin(theta) rows: fold p
+                float *ga = X + (size_t)blocked_row(2 * m + p, kn, ngroups) * ncp + 4 * f0;       // d/dtheta rows: fold 1 - p
+                float *gb = X + (size_t)blocked_row(2 * m + p, Kh + kn, ngroups) * ncp + 4 * f0;  // m/sin(theta) rows: fold p
                 const float *fa = p ? e : o;
                 const float *fb = p ? o : e;
 #pragma unroll
@@ -529,7 +541,7 @@ __global__ void __launch_bounds__(32 * NW * G, (NW * G >= 16) ? 2 : 1) fft_analy
 // ------------------------------------------------------------------------------------------------
 // synthesis kernel
 // ------------------------------------------------------------------------------------------------
-// Y[(2 m + p) * Kh + k'][col] (row pitch ncp) holds the even (p = 0) / odd (p = 1) latitude parts of order m;
+// Y[blocked_row(2 m + p, k')][col] (row pitch ncp) holds the even (p = 0) / odd (p = 1) latitude parts of order m;
 // col = 2 f + (re, im) for scalar fields, 4 f + (theta re, theta im, phi re, phi im) for vector pairs: in both
 // cases transform u of the CTA reads columns 2 u, 2 u + 1 past the CTA's first column.
 template <int NW, int VEC, int G>
@@ -563,8 +575,8 @@ __global__ void __launch_bounds__(32 * NW * G, (NW * G >= 16) ? 2 : 1) fft_synth
     }
     for (int m = threadIdx.x; m < mtop; m += blockDim.x) {
         const float sc = mscale[m];
-        const float *ge = Y + ((size_t)(2 * m) * Kh + kn) * ncp + colbase;
-        const float *go = Y + ((size_t)(2 * m + 1) * Kh + kn) * ncp + colbase;
+        const float *ge = Y + (size_t)blocked_row(2 * m, kn, 2 * mmax) * ncp + colbase;
+        const float *go = Y + (size_t)blocked_row(2 * m + 1, kn, 2 * mmax) * ncp + colbase;
         float e[2 * NW], o[2 * NW];
 #pragma unroll
         for (int c = 0; c < 2 * NW; c += 4) {
@@ -728,7 +740,8 @@ int launch_fft_analysis(const Plan &pl, const float *x, float *X, int nfields, c
     const int vec = pl.vector ? 2 : 1;
     const int NW = pick_warps(pl.fft, vec);
     const int ncp = (int)round_up((pl.vector ? 4 : 2) * nfields, 4);
-    dim3 grid(ceil_div(nfields, NW / vec), pl.Kh);
+    // one CTA row per latitude pair plus the zero rows that pad the contraction length to a multiple of 32
+    dim3 grid(ceil_div(nfields, NW / vec), pl.Kh + (int)(round_up(pl.Ka, kBK) - pl.Ka));
     size_t smem = fft_smem_bytes(NW, pl.fft);
     const int al = (int)(((uintptr_t)x & 15) == 0);
     int rc;

@@ -51,7 +51,7 @@ __global__ void __launch_bounds__(256) legendre_simt_kernel(GemmParams gp) {
             if (cb < gp.ncols) {
                 if (gp.b_mn) {
                     const int k = k0 + kk;
-                    if (k < gp.b_krows) bv = gp.B[(((long long)it.b_y0 - gp.b_unit0) * gp.b_krows + k) * gp.b_pitch + cb];
+                    if (k < gp.b_krows) bv = gp.B[blocked_row((long long)it.b_y0 - gp.b_unit0, k, gp.b_groups) * gp.b_pitch + cb];
                 } else {
                     bv = load_operand(gp.B, gp.b_pitch, b_y0, b_dy, gp.b_dx, gp.b_kext, cb, k0 + kk);
                 }
@@ -103,7 +103,7 @@ __global__ void __launch_bounds__(256) legendre_simt_kernel(GemmParams gp) {
             for (int j = 0; j < 4; ++j) {
                 const int c = col0 + tx * 4 + j;
                 if (c >= gp.ncols) continue;
-                gp.out[((size_t)g * gp.out_rows + rg) * gp.out_ld + c] = acc[i][j];
+                gp.out[(size_t)blocked_row(g, rg, gp.out_groups) * gp.out_ld + c] = acc[i][j];
             }
         }
     }

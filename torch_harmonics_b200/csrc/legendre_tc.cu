@@ -129,7 +129,7 @@ legendre_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             for (int u = blockIdx.x; u < P.nunits && ok; u += gridDim.x) {
                 const Unit w = get_unit(u);
                 if (w.skip) continue;
-                const long long by0 = gp.b_mn ? ((long long)w.it.b_y0 - gp.b_unit0) * gp.b_krows
+                const long long by0 = gp.b_mn ? ((long long)w.it.b_y0 - gp.b_unit0) * TK  // 32-row block of this group inside a k-step
                                               : ((long long)w.it.b_y0 - gp.b_unit0) * gp.ncols + (long long)w.ntile * P.bn;
                 for (int ks = 0; ks < w.ksteps; ++ks) {
                     if (!(ok = ptx::mbar_wait_bounded(bar_empty(s), ph ^ 1u, abort_flag, WAIT_LIMIT))) break;
@@ -139,7 +139,7 @@ legendre_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                     if (gp.b_mn) {
                         // 32 contraction rows x 32 columns per box; consecutive boxes hold consecutive column blocks
                         for (int i = 0; i < P.bblk; ++i)
-                            ptx::tma_load_2d(dst + B_OFF + i * B_BLK_BYTES, &tmB, w.ntile * P.bn + 32 * i, (int)(by0 + (long long)ks * TK), bar_full(s));
+                            ptx::tma_load_2d(dst + B_OFF + i * B_BLK_BYTES, &tmB, w.ntile * P.bn + 32 * i, (int)(by0 + (long long)ks * gp.b_groups * TK), bar_full(s));
                     } else {
                         const long long by = by0 + (row_packed_b ? 0 : (long long)ks * w.it.b_dy * gp.ncols);
                         ptx::tma_load_2d(dst + B_OFF, &tmB, row_packed_b ? ks * TK : 0, (int)by, bar_full(s));
@@ -273,7 +273,7 @@ legendre_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                     }
                 } else {
                     const int g = 2 * (w.it.m - gp.m0) + w.it.p;
-                    float *o = gp.out + ((size_t)g * gp.out_rows + rg) * gp.out_ld + col0 + cc;  // 16 consecutive columns: 64 bytes
+                    float *o = gp.out + (size_t)blocked_row(g, rg, gp.out_groups) * gp.out_ld + col0 + cc;  // 16 consecutive columns: 64 bytes
 #pragma unroll
                     for (int j = 0; j < 16; j += 4)
                         if (col0 + cc + j < gp.out_ld) *reinterpret_cast<float4 *>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
@@ -370,7 +370,7 @@ int launch_gemm_tc(const Plan &pl, const GemmParams &gp, cudaStream_t st) {
         a_inner = gp.a_kext;
         a_rows = pl.group_a0.back() + kItemRowsMax;
         b_inner = gp.ncols;  // columns beyond it read as zeros
-        b_rows = (long long)2 * gp.mmax_out * gp.b_krows;
+        b_rows = (long long)gp.b_groups * round_up(gp.b_krows, TK);
     } else {
         a_inner = kBK;
         a_rows = pl.group_a0.back() + kItemRowsMax;

@@ -195,28 +195,33 @@ __global__ void zero_upper_kernel(float2 *c, long long nfl, int lmax, int mloc, 
     }
 }
 
-// Xc (field, k, mloc) complex -> X[(2 mi + p) * Kh + k'][2 f + ri] (row pitch ncp)
+// Xc (field, k, mloc) complex -> X[blocked_row(2 mi + p, k')][2 f + ri] (row pitch ncp); rows k' >= Kh of the last
+// 32-row block are written as zeros
 __global__ void fold_modes_kernel(const float2 *__restrict__ Xc, float *__restrict__ X, int nfields, int nlat, int Kh, int ncp, int mloc) {
-    const long long total = (long long)mloc * Kh * nfields;
+    const int Kr = (Kh + kBK - 1) / kBK * kBK;
+    const long long total = (long long)mloc * Kr * nfields;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         const int f = (int)(i % nfields);
         const long long t = i / nfields;
-        const int k = (int)(t % Kh);
-        const int mi = (int)(t / Kh);
-        const int ks = nlat - 1 - k;
-        float2 a = Xc[((size_t)f * nlat + k) * mloc + mi];
-        float2 e = a, o = make_float2(0.f, 0.f);
-        if (ks != k) {
-            float2 b = Xc[((size_t)f * nlat + ks) * mloc + mi];
-            e = make_float2(a.x + b.x, a.y + b.y);
-            o = make_float2(a.x - b.x, a.y - b.y);
+        const int k = (int)(t % Kr);
+        const int mi = (int)(t / Kr);
+        float2 e = make_float2(0.f, 0.f), o = e;
+        if (k < Kh) {
+            const int ks = nlat - 1 - k;
+            float2 a = Xc[((size_t)f * nlat + k) * mloc + mi];
+            e = a;
+            if (ks != k) {
+                float2 b = Xc[((size_t)f * nlat + ks) * mloc + mi];
+                e = make_float2(a.x + b.x, a.y + b.y);
+                o = make_float2(a.x - b.x, a.y - b.y);
+            }
         }
-        *reinterpret_cast<float2 *>(X + ((size_t)(2 * mi) * Kh + k) * ncp + 2 * f) = e;
-        *reinterpret_cast<float2 *>(X + ((size_t)(2 * mi + 1) * Kh + k) * ncp + 2 * f) = o;
+        *reinterpret_cast<float2 *>(X + (size_t)blocked_row(2 * mi, k, 2 * mloc) * ncp + 2 * f) = e;
+        *reinterpret_cast<float2 *>(X + (size_t)blocked_row(2 * mi + 1, k, 2 * mloc) * ncp + 2 * f) = o;
     }
 }
 
-// Y[(2 mi + p) * Kh + k'][2 f + ri] -> Xc (field, k, mloc) complex
+// Y[blocked_row(2 mi + p, k')][2 f + ri] -> Xc (field, k, mloc) complex
 __global__ void unfold_modes_kernel(const float *__restrict__ Y, float2 *__restrict__ Xc, int nfields, int nlat, int Kh, int ncp, int mloc) {
     const long long total = (long long)nfields * Kh * mloc;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
@@ -224,8 +229,8 @@ __global__ void unfold_modes_kernel(const float *__restrict__ Y, float2 *__restr
         const long long t = i / mloc;
         const int k = (int)(t % Kh);
         const int f = (int)(t / Kh);
-        const float2 e = *reinterpret_cast<const float2 *>(Y + ((size_t)(2 * mi) * Kh + k) * ncp + 2 * f);
-        const float2 o = *reinterpret_cast<const float2 *>(Y + ((size_t)(2 * mi + 1) * Kh + k) * ncp + 2 * f);
+        const float2 e = *reinterpret_cast<const float2 *>(Y + (size_t)blocked_row(2 * mi, k, 2 * mloc) * ncp + 2 * f);
+        const float2 o = *reinterpret_cast<const float2 *>(Y + (size_t)blocked_row(2 * mi + 1, k, 2 * mloc) * ncp + 2 * f);
         const int ks = nlat - 1 - k;
         Xc[((size_t)f * nlat + k) * mloc + mi] = make_float2(e.x + o.x, e.y + o.y);
         if (ks != k) Xc[((size_t)f * nlat + ks) * mloc + mi] = make_float2(e.x - o.x, e.y - o.y);
@@ -294,7 +299,7 @@ int launch_zero_upper(const Plan &pl, float2 *c, int nfields, int m0, int mloc, 
 int launch_fold_modes(const Plan &pl, const float2 *Xc, float *X, int nfields, int m0, int mloc, cudaStream_t st) {
     (void)m0;
     if (pl.vector) return fail(SHTB200_EINVAL, "stage-wise Legendre entry point supports the scalar kinds only");
-    const long long total = (long long)mloc * nfields * pl.Kh;
+    const long long total = (long long)mloc * nfields * round_up(pl.Kh, kBK);
     if (total == 0) return SHTB200_OK;
     fold_modes_kernel<<<grid_x_for(total), 256, 0, st>>>(Xc, X, nfields, pl.nlat, pl.Kh, (int)round_up(2 * nfields, 4), mloc);
     SHT_CUDA_CHECK(cudaGetLastError());

@@ -377,7 +377,12 @@ __device__ void fft_group(float2 *d, const FftPlanDev &fp, const float2 *tw_s, i
     }
 }
 
-// shared memory: [NW * n float2 data][per-pass twiddle tables][n u16 perm]
+// Transforms of a CTA lie `n + kPad` float2 apart: with a pitch that is a multiple of 128 bytes the same bin of all
+// transforms would fall on one bank group and the final gather / initial scatter (4 lanes per order, each on two
+// different transforms) would serialise.
+constexpr int kPad = 2;
+
+// shared memory: [NW * (n + kPad) float2 data][per-pass twiddle tables][n u16 perm]
 __device__ __forceinline__ void load_tables(const FftPlanDev &fp, float2 *tw_s, unsigned short *perm_s) {
     for (int i = threadIdx.x; i < fp.tw_pass_total; i += blockDim.x) tw_s[i] = fp.tw[i];
     for (int i = threadIdx.x; i < fp.n; i += blockDim.x) perm_s[i] = fp.perm[i];
@@ -405,8 +410,9 @@ __global__ void __launch_bounds__(32 * NW * G, (NW * G >= 16) ? 2 : 1) fft_analy
     const int n = fp.n;
     constexpr int NF = NW / VEC;                    // fields (or component pairs) per CTA
     constexpr int GT = 32 * G;                      // threads per transform
+    const int np = n + kPad;
     float2 *data = smem;
-    float2 *tw_s = data + (size_t)NW * n;
+    float2 *tw_s = data + (size_t)NW * np;
     unsigned short *perm_s = reinterpret_cast<unsigned short *>(tw_s + fp.tw_pass_total);
 
     const int kn = blockIdx.y;
@@ -430,7 +436,7 @@ __global__ void __launch_bounds__(32 * NW * G, (NW * G >= 16) ? 2 : 1) fft_analy
     // ---- each group loads and folds its own pair of rows ----
     {
         const int f = f0 + t / VEC, comp = t % VEC;
-        float2 *dst = data + (size_t)t * n;
+        float2 *dst = data + (size_t)t * np;
         if (f >= nfields) {
             for (int j = lane; j < n; j += GT) dst[j] = make_float2(0.f, 0.f);
         } else {
@@ -480,58 +486,54 @@ __global__ void __launch_bounds__(32 * NW * G, (NW * G >= 16) ? 2 : 1) fft_analy
     }
     __syncthreads();  // tables and rows in place
 
-    fft_group<false, G>(data + (size_t)t * n, fp, tw_s, lane, 1 + t);
+    fft_group<false, G>(data + (size_t)t * np, fp, tw_s, lane, 1 + t);
     __syncthreads();
 
-    // ---- emit the retained orders: one thread per order, 2 NW floats per (order, fold) ----
+    // ---- emit the retained orders ----
+    // NW / 2 adjacent lanes share one order: lane c of them handles transforms 2c, 2c+1, i.e. one 16-byte piece of the
+    // 2 NW floats an (order, fold) run is made of, so that a run leaves the SM as ONE contiguous request.
     const int nyq = n / 2;
-    for (int m = threadIdx.x; m < mmax; m += blockDim.x) {
-        float e[2 * NW], o[2 * NW];  // (re, im) of the even / odd fold of every transform
+    constexpr int LPM = NW / 2;  // lanes per order
+    const int c = threadIdx.x % LPM;
+    for (int m = threadIdx.x / LPM; m < mmax; m += blockDim.x / LPM) {
+        float e[4], o[4];  // (re, im) of the even / odd fold of transforms 2c, 2c+1
         if (m <= nyq) {
             const float sc = 0.5f * mscale[m];
             const int pm = perm_s[m];
             const int pn = perm_s[m == 0 ? 0 : n - m];
             const bool edge = zero_imag_edges && (m == 0 || (2 * m == n));
 #pragma unroll
-            for (int u = 0; u < NW; ++u) {
-                float2 zm = data[(size_t)u * n + pm];
-                float2 zn = data[(size_t)u * n + pn];
+            for (int h = 0; h < 2; ++h) {
+                const float2 *dd = data + (size_t)(2 * c + h) * np;
+                float2 zm = dd[pm];
+                float2 zn = dd[pn];
                 // spectra of the two real rows packed in z = even + i odd
-                e[2 * u] = sc * (zm.x + zn.x);
-                e[2 * u + 1] = edge ? 0.f : sc * (zm.y - zn.y);
-                o[2 * u] = sc * (zm.y + zn.y);
-                o[2 * u + 1] = edge ? 0.f : sc * (zn.x - zm.x);
+                e[2 * h] = sc * (zm.x + zn.x);
+                e[2 * h + 1] = edge ? 0.f : sc * (zm.y - zn.y);
+                o[2 * h] = sc * (zm.y + zn.y);
+                o[2 * h + 1] = edge ? 0.f : sc * (zn.x - zm.x);
             }
         } else {
 #pragma unroll
-            for (int u = 0; u < 2 * NW; ++u) e[u] = o[u] = 0.f;
+            for (int u = 0; u < 4; ++u) e[u] = o[u] = 0.f;
         }
         if (VEC == 1) {
-            float *ge = X + (size_t)blocked_row(2 * m, kn, ngroups) * ncp + 2 * f0;
-            float *go = X + (size_t)blocked_row(2 * m + 1, kn, ngroups) * ncp + 2 * f0;
-#pragma unroll
-            for (int c = 0; c < 2 * NW; c += 4) {
-                if (2 * f0 + c < ncp) {
-                    *reinterpret_cast<float4 *>(ge + c) = make_float4(e[c], e[c + 1], e[c + 2], e[c + 3]);
-                    *reinterpret_cast<float4 *>(go + c) = make_float4(o[c], o[c + 1], o[c + 2], o[c + 3]);
-                }
+            // columns 2 (f0 + 2c), ..: (re, im) of two consecutive fields
+            const int col = 2 * f0 + 4 * c;
+            if (col < ncp) {
+                *reinterpret_cast<float4 *>(X + (size_t)blocked_row(2 * m, kn, ngroups) * ncp + col) = make_float4(e[0], e[1], e[2], e[3]);
+                *reinterpret_cast<float4 *>(X + (size_t)blocked_row(2 * m + 1, kn, ngroups) * ncp + col) = make_float4(o[0], o[1], o[2], o[3]);
             }
         } else {
-            // transforms 2 q (theta component X0) and 2 q + 1 (phi component X1) of pair q
+            // transforms 2c (theta component X0) and 2c + 1 (phi component X1) of pair f0 + c: four columns 4 (f0 + c)..
+            const int col = 4 * (f0 + c);
+            if (col < ncp) {
 #pragma unroll
-            for (int p = 0; p < 2; ++p) {
-                float *ga = X + (size_t)blocked_row(2 * m + p, kn, ngroups) * ncp + 4 * f0;       // d/dtheta rows: fold 1 - p
-                float *gb = X + (size_t)blocked_row(2 * m + p, Kh + kn, ngroups) * ncp + 4 * f0;  // m/sin(theta) rows: fold p
-                const float *fa = p ? e : o;
-                const float *fb = p ? o : e;
-#pragma unroll
-                for (int q = 0; q < NF; ++q) {
-                    if (4 * (f0 + q) < ncp) {
-                        const float x0re_a = fa[4 * q], x0im_a = fa[4 * q + 1], x1re_a = fa[4 * q + 2], x1im_a = fa[4 * q + 3];
-                        const float x0re_b = fb[4 * q], x0im_b = fb[4 * q + 1], x1re_b = fb[4 * q + 2], x1im_b = fb[4 * q + 3];
-                        *reinterpret_cast<float4 *>(ga + 4 * q) = make_float4(x0re_a, x0im_a, -x1re_a, -x1im_a);
-                        *reinterpret_cast<float4 *>(gb + 4 * q) = make_float4(-x1im_b, x1re_b, -x0im_b, x0re_b);
-                    }
+                for (int p = 0; p < 2; ++p) {
+                    const float *fa = p ? e : o;  // d/dtheta rows take the fold of parity 1 - p
+                    const float *fb = p ? o : e;  // m/sin(theta) rows take the fold of parity p
+                    *reinterpret_cast<float4 *>(X + (size_t)blocked_row(2 * m + p, kn, ngroups) * ncp + col) = make_float4(fa[0], fa[1], -fa[2], -fa[3]);
+                    *reinterpret_cast<float4 *>(X + (size_t)blocked_row(2 * m + p, Kh + kn, ngroups) * ncp + col) = make_float4(-fb[3], fb[2], -fb[1], fb[0]);
                 }
             }
         }
@@ -552,8 +554,9 @@ __global__ void __launch_bounds__(32 * NW * G, (NW * G >= 16) ? 2 : 1) fft_synth
     const int n = fp.n;
     constexpr int NF = NW / VEC;
     constexpr int GT = 32 * G;
+    const int np = n + kPad;
     float2 *data = smem;
-    float2 *tw_s = data + (size_t)NW * n;
+    float2 *tw_s = data + (size_t)NW * np;
     unsigned short *perm_s = reinterpret_cast<unsigned short *>(tw_s + fp.tw_pass_total);
 
     const int kn = blockIdx.y;
@@ -570,51 +573,50 @@ __global__ void __launch_bounds__(32 * NW * G, (NW * G >= 16) ? 2 : 1) fft_synth
         const int nzero = n - 2 * mtop + 1;
         for (int i = threadIdx.x; i < NW * nzero; i += blockDim.x) {
             const int u = i / nzero, m = mtop + (i - u * nzero);
-            data[(size_t)u * n + perm_s[m]] = make_float2(0.f, 0.f);
+            data[(size_t)u * np + perm_s[m]] = make_float2(0.f, 0.f);
         }
     }
-    for (int m = threadIdx.x; m < mtop; m += blockDim.x) {
-        const float sc = mscale[m];
-        const float *ge = Y + (size_t)blocked_row(2 * m, kn, 2 * mmax) * ncp + colbase;
-        const float *go = Y + (size_t)blocked_row(2 * m + 1, kn, 2 * mmax) * ncp + colbase;
-        float e[2 * NW], o[2 * NW];
-#pragma unroll
-        for (int c = 0; c < 2 * NW; c += 4) {
+    // NW / 2 adjacent lanes share one order; lane c reads the 16-byte piece of both runs that holds transforms 2c, 2c+1
+    {
+        constexpr int LPM = NW / 2;
+        const int c = threadIdx.x % LPM;
+        const int col = colbase + 4 * c;
+        for (int m = threadIdx.x / LPM; m < mtop; m += blockDim.x / LPM) {
             float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
-            if (colbase + c < ncp) {
-                a = *reinterpret_cast<const float4 *>(ge + c);
-                b = *reinterpret_cast<const float4 *>(go + c);
+            if (col < ncp) {
+                a = *reinterpret_cast<const float4 *>(Y + (size_t)blocked_row(2 * m, kn, 2 * mmax) * ncp + col);
+                b = *reinterpret_cast<const float4 *>(Y + (size_t)blocked_row(2 * m + 1, kn, 2 * mmax) * ncp + col);
             }
-            e[c] = a.x; e[c + 1] = a.y; e[c + 2] = a.z; e[c + 3] = a.w;
-            o[c] = b.x; o[c + 1] = b.y; o[c + 2] = b.z; o[c + 3] = b.w;
-        }
-        const bool edge = (m == 0) || (2 * m == n);
-        const int pm = perm_s[m];
-        const int pn = perm_s[m == 0 ? 0 : n - m];
+            const float sc = mscale[m];
+            const bool edge = (m == 0) || (2 * m == n);
+            const int pm = perm_s[m];
+            const int pn = perm_s[m == 0 ? 0 : n - m];
+            const float e[4] = {a.x, a.y, a.z, a.w}, o[4] = {b.x, b.y, b.z, b.w};
 #pragma unroll
-        for (int u = 0; u < NW; ++u) {
-            // north row spectrum A = even + odd, south row spectrum B = even - odd; Z = A + i B
-            const float ar = sc * (e[2 * u] + o[2 * u]), ai = sc * (e[2 * u + 1] + o[2 * u + 1]);
-            const float br = sc * (e[2 * u] - o[2 * u]), bi = sc * (e[2 * u + 1] - o[2 * u + 1]);
-            float2 *dd = data + (size_t)u * n;
-            if (edge) {
-                dd[pm] = make_float2(ar, br);  // imaginary parts of DC / Nyquist are dropped
-            } else {
-                dd[pm] = make_float2(ar - bi, ai + br);
-                dd[pn] = make_float2(ar + bi, br - ai);
+            for (int h = 0; h < 2; ++h) {
+                // north row spectrum A = even + odd, south row spectrum B = even - odd; Z = A + i B
+                const float ar = sc * (e[2 * h] + o[2 * h]), ai = sc * (e[2 * h + 1] + o[2 * h + 1]);
+                const float br = sc * (e[2 * h] - o[2 * h]), bi = sc * (e[2 * h + 1] - o[2 * h + 1]);
+                float2 *dd = data + (size_t)(2 * c + h) * np;
+                if (edge) {
+                    dd[pm] = make_float2(ar, br);  // imaginary parts of DC / Nyquist are dropped
+                } else {
+                    dd[pm] = make_float2(ar - bi, ai + br);
+                    dd[pn] = make_float2(ar + bi, br - ai);
+                }
             }
         }
     }
     __syncthreads();
 
-    fft_group<true, G>(data + (size_t)t * n, fp, tw_s, lane, 1 + t);
+    fft_group<true, G>(data + (size_t)t * np, fp, tw_s, lane, 1 + t);
 
     // ---- each group stores its own pair of rows ----
     {
         const int f = f0 + t / VEC, comp = t % VEC;
         if (f < nfields) {
             const int ks = nlat - 1 - kn;
-            const float2 *src = data + (size_t)t * n;
+            const float2 *src = data + (size_t)t * np;
             float *rn = x + ((size_t)(f * VEC + comp) * nlat + kn) * n;
             float *rs = x + ((size_t)(f * VEC + comp) * nlat + ks) * n;
             if ((n % 4 == 0) && vec4ok) {
@@ -717,7 +719,7 @@ __global__ void __launch_bounds__(32 * NW) irfft_rows_kernel(const float2 *__res
 // launchers
 // ------------------------------------------------------------------------------------------------
 static size_t fft_smem_bytes(int nffts, const FftPlanDev &fp) {
-    return (size_t)nffts * fp.n * sizeof(float2) + (size_t)fp.tw_pass_total * sizeof(float2) + (size_t)fp.n * sizeof(unsigned short) + 16;
+    return (size_t)nffts * (fp.n + kPad) * sizeof(float2) + (size_t)fp.tw_pass_total * sizeof(float2) + (size_t)fp.n * sizeof(unsigned short) + 16;
 }
 
 template <typename K>

@@ -56,7 +56,7 @@ struct WsLayout {
 WsLayout ws_layout(const Plan &pl, int nfields, int m0, int mloc) {
     WsLayout w;
     const size_t ncols = (size_t)(pl.vector ? 4 : 2) * nfields;
-    const size_t ncp = (ncols + 3) / 4 * 4;  // row pitch of the column-contiguous operands
+    const size_t ncp = (size_t)col_pitch((long long)ncols);  // row pitch of the column-contiguous operands
     if (pl.analysis) {
         w.op_bytes = (size_t)2 * mloc * round_up(pl.Ka, kBK) * ncp * sizeof(float);
         if (!pl.vector) w.y_bytes = (size_t)(pl.group_b0[2 * (m0 + mloc)] - pl.group_b0[2 * m0]) * ncols * kBK * sizeof(float);
@@ -86,7 +86,7 @@ GemmParams gemm_params(const Plan &pl, int nfields, int m0, int mloc, const floa
         gp.b_mn = 1;
         gp.b_krows = pl.Ka;
         gp.b_groups = 2 * mloc;
-        gp.b_pitch = round_up(gp.ncols, 4);
+        gp.b_pitch = col_pitch(gp.ncols);
         gp.b_dx = kBK;
         gp.b_kext = pl.Ka;
         gp.b_unit0 = 2 * m0;
@@ -99,7 +99,7 @@ GemmParams gemm_params(const Plan &pl, int nfields, int m0, int mloc, const floa
         gp.b_kext = kBK;
         gp.b_unit0 = pl.group_b0[2 * m0];
         gp.mode = EPI_LATROWS;
-        gp.out_ld = round_up(gp.ncols, 4);
+        gp.out_ld = col_pitch(gp.ncols);
         gp.out_groups = 2 * mloc;
     }
     return gp;
@@ -127,7 +127,7 @@ int run_gemm(Plan &pl, const GemmParams &gp, cudaStream_t st) {
 int clear_empty_groups(const Plan &pl, float *Y, int ncols, int m0, int mloc, cudaStream_t st) {
     for (int g = 2 * m0; g < 2 * (m0 + mloc); ++g) {
         if (pl.group_kblocks[g] == 0) {
-            const size_t ncp = round_up(ncols, 4);
+            const size_t ncp = (size_t)col_pitch(ncols);
             for (int k0 = 0; k0 < pl.Kh; k0 += kBK)  // the group's rows come in 32-row blocks
                 SHT_CUDA_CHECK(cudaMemsetAsync(Y + (size_t)blocked_row(g - 2 * m0, k0, 2 * mloc) * ncp, 0, sizeof(float) * kBK * ncp, st));
         }

@@ -182,6 +182,9 @@ int launch_unfold_modes(const Plan &pl, const float *Y, float2 *Xc, int nfields,
 __host__ __device__ inline long long blocked_row(long long group, int k, int ngroups) { return (((long long)(k >> 5) * ngroups + group) << 5) + (k & 31); }
 
 inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+// Row pitch (floats) of the column-contiguous operands: whole 128-byte lines, so that the 64-byte runs the FFT kernels
+// write and read never straddle two lines.
+inline long long col_pitch(long long ncols) { return (ncols + 31) / 32 * 32; }
 inline long long round_up(long long a, long long b) { return (a + b - 1) / b * b; }
 
 }  // namespace shtb200

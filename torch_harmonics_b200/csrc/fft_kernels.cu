@@ -741,7 +741,7 @@ static int pick_warps(const FftPlanDev &fp, int vec) {
 int launch_fft_analysis(const Plan &pl, const float *x, float *X, int nfields, cudaStream_t st) {
     const int vec = pl.vector ? 2 : 1;
     const int NW = pick_warps(pl.fft, vec);
-    const int ncp = (int)round_up((pl.vector ? 4 : 2) * nfields, 4);
+    const int ncp = (int)col_pitch((pl.vector ? 4 : 2) * nfields);
     // one CTA row per latitude pair plus the zero rows that pad the contraction length to a multiple of 32
     dim3 grid(ceil_div(nfields, NW / vec), pl.Kh + (int)(round_up(pl.Ka, kBK) - pl.Ka));
     size_t smem = fft_smem_bytes(NW, pl.fft);
@@ -769,7 +769,7 @@ int launch_fft_analysis(const Plan &pl, const float *x, float *X, int nfields, c
 int launch_fft_synthesis(const Plan &pl, const float *Y, float *x, int nfields, cudaStream_t st) {
     const int vec = pl.vector ? 2 : 1;
     const int NW = pick_warps(pl.fft, vec);
-    const int ncp = (int)round_up((pl.vector ? 4 : 2) * nfields, 4);
+    const int ncp = (int)col_pitch((pl.vector ? 4 : 2) * nfields);
     dim3 grid(ceil_div(nfields, NW / vec), pl.Kh);
     size_t smem = fft_smem_bytes(NW, pl.fft);
     const int al = (int)(((uintptr_t)x & 15) == 0);

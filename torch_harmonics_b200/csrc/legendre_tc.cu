@@ -253,6 +253,36 @@ legendre_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                 if (col0 + cc >= gp.ncols) break;  // warp-uniform
                 float v[16];
                 ptx::tmem_ld16(trow + (uint32_t)cc, v);
+                if (gp.mode == EPI_LATROWS) {
+                    // A thread holds 16 consecutive columns (64 bytes) of its own row.  Transposing 4 x 4 blocks of 16 bytes inside
+                    // every group of 4 lanes lets the 4 lanes store one row's 64 bytes together: one request instead of four.
+#pragma unroll
+                    for (int bit = 1; bit <= 2; bit <<= 1) {
+                        const bool up = (lane & bit) != 0;
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            if (k & bit) continue;
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const float send = up ? v[4 * k + e] : v[4 * (k | bit) + e];
+                                const float got = __shfl_xor_sync(0xffffffffu, send, bit);
+                                if (up) v[4 * k + e] = got;
+                                else v[4 * (k | bit) + e] = got;
+                            }
+                        }
+                    }
+                    // now v[4 k .. 4 k + 3] = columns 4 (lane & 3) .. of the row of lane (lane & ~3) + k
+                    const int g = 2 * (w.it.m - gp.m0) + w.it.p;
+                    const int colq = col0 + cc + 4 * (lane & 3);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const int rr = (q * 32 + (lane & ~3) + k);  // row inside the tile
+                        if (rr < w.it.rows && colq < gp.out_ld)
+                            *reinterpret_cast<float4 *>(gp.out + (size_t)blocked_row(g, w.it.r0 + rr, gp.out_groups) * gp.out_ld + colq) =
+                                make_float4(v[4 * k], v[4 * k + 1], v[4 * k + 2], v[4 * k + 3]);
+                    }
+                    continue;
+                }
                 if (!rvalid) continue;
                 if (gp.mode == EPI_COEFFS) {
                     const int l = w.it.m + w.it.p + 2 * rg;
@@ -271,12 +301,6 @@ legendre_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                         const int col = col0 + cc + j;
                         if (col < gp.ncols) o[(size_t)col * kBK] = v[j];
                     }
-                } else {
-                    const int g = 2 * (w.it.m - gp.m0) + w.it.p;
-                    float *o = gp.out + (size_t)blocked_row(g, rg, gp.out_groups) * gp.out_ld + col0 + cc;  // 16 consecutive columns: 64 bytes
-#pragma unroll
-                    for (int j = 0; j < 16; j += 4)
-                        if (col0 + cc + j < gp.out_ld) *reinterpret_cast<float4 *>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
                 }
             }
             ptx::tc_fence_before();

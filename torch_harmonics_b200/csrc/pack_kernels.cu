@@ -301,7 +301,7 @@ int launch_fold_modes(const Plan &pl, const float2 *Xc, float *X, int nfields, i
     if (pl.vector) return fail(SHTB200_EINVAL, "stage-wise Legendre entry point supports the scalar kinds only");
     const long long total = (long long)mloc * nfields * round_up(pl.Kh, kBK);
     if (total == 0) return SHTB200_OK;
-    fold_modes_kernel<<<grid_x_for(total), 256, 0, st>>>(Xc, X, nfields, pl.nlat, pl.Kh, (int)round_up(2 * nfields, 4), mloc);
+    fold_modes_kernel<<<grid_x_for(total), 256, 0, st>>>(Xc, X, nfields, pl.nlat, pl.Kh, (int)col_pitch(2 * nfields), mloc);
     SHT_CUDA_CHECK(cudaGetLastError());
     return SHTB200_OK;
 }
@@ -311,7 +311,7 @@ int launch_unfold_modes(const Plan &pl, const float *Y, float2 *Xc, int nfields,
     if (pl.vector) return fail(SHTB200_EINVAL, "stage-wise Legendre entry point supports the scalar kinds only");
     const long long total = (long long)nfields * pl.Kh * mloc;
     if (total == 0) return SHTB200_OK;
-    unfold_modes_kernel<<<grid_x_for(total), 256, 0, st>>>(Y, Xc, nfields, pl.nlat, pl.Kh, (int)round_up(2 * nfields, 4), mloc);
+    unfold_modes_kernel<<<grid_x_for(total), 256, 0, st>>>(Y, Xc, nfields, pl.nlat, pl.Kh, (int)col_pitch(2 * nfields), mloc);
     SHT_CUDA_CHECK(cudaGetLastError());
     return SHTB200_OK;
 }

@@ -36,10 +36,20 @@ struct FftPlanDev {
     int radix[kMaxFftStages];     // radix of pass s (decimation in frequency order)
     int sublen[kMaxFftStages];    // length L of the sub-transforms pass s splits (L_0 = n, L_{s+1} = L_s / radix_s)
     int twoff[kMaxFftStages];     // offset of pass s's twiddle table inside tw
-    int tw_pass_total;            // entries of all per-pass tables together
+    int tw_pass_total;            // entries of all per-pass tables together (padded to an even count)
+    int tab_bytes;                // size of the blob [tw | bfly | perm | eorder] that starts at tw (a multiple of 16)
     const float2 *tw;             // per-pass tables: entry (q - 1) * L/R + j of pass s = exp(-2 pi i q j / L_s), from double
     const float2 *tw_full;        // n roots of unity exp(-2 pi i k / n) (generic prime-radix butterflies only)
     const unsigned short *perm;   // perm[k] = slot of output bin k after the in-place DIF passes
+    // Thread -> butterfly assignment of each pass, ordered so that the 16 lanes that share a shared-memory wavefront
+    // touch 16 different 8-byte bank pairs: entry i of pass s = (first leg's slot) | (twiddle index j) << 16.
+    const unsigned *bfly;
+    int bfoff[kMaxFftStages];
+    int bf_total;
+    // Order in which the retained longitudinal orders are emitted / gathered (a permutation of [0, eorder_len)), chosen
+    // so that the lanes of one wavefront read different banks of the permuted spectrum; null = natural order.
+    const unsigned short *eorder;
+    int eorder_len;
 };
 
 // ------------------------------------------------------------------------------------------------
@@ -153,7 +163,8 @@ struct Plan {
 // ------------------------------------------------------------------------------------------------
 // kernel launchers (defined in the .cu files)
 // ------------------------------------------------------------------------------------------------
-int build_fft_plan(int nlon, FftPlanDev *out, float2 **d_tw, unsigned short **d_perm);
+// mmax_emit > 0 also builds the emit order for that many retained orders (the SHT kernels); 0 leaves it out
+int build_fft_plan(int nlon, int mmax_emit, FftPlanDev *out, float2 **d_tw, unsigned short **d_perm);
 
 // analysis: rows of x -> folded, order-major operand X[blocked_row(group, k)][col] (row pitch round_up(ncols, 4))
 int launch_fft_analysis(const Plan &pl, const float *x, float *X, int nfields, cudaStream_t st);

@@ -18,14 +18,21 @@
 
 #include <math.h>
 #include <stdlib.h>
+#include <string.h>
 
 #include <algorithm>
 #include <vector>
 
 #include "common.cuh"
 #include "fft_consts.cuh"
+#include "tc_ptx.cuh"
 
 namespace shtb200 {
+
+// Transforms of a CTA lie `n + kPad` float2 apart: with a pitch that is a multiple of 128 bytes the same bin of all
+// transforms would fall on one bank group and the final gather / initial scatter (4 lanes per order, each on two
+// different transforms) would serialise.
+constexpr int kPad = 2;
 
 // ------------------------------------------------------------------------------------------------
 // host: factorisation, twiddles, output permutation
@@ -59,9 +66,96 @@ std::vector<int> best_split(int n, std::vector<std::vector<int>> &memo, std::vec
     return best;
 }
 
+// Shared memory serves a 64-bit access of a warp as two wavefronts of 16 lanes; a wavefront costs one extra cycle for
+// every further distinct address that falls on an already used 8-byte bank pair (index mod 16 in float2 units).
+// Order the butterflies of a pass (first-leg slot `off`, twiddle index j) so that each run of 16 consecutive
+// threads touches 16 different bank pairs, for the data and for the twiddle table alike.  All legs of a butterfly
+// are shifted by the same amount, so one check covers them all.
+std::vector<unsigned> order_butterflies(int n, int L, int R) {
+    const int Ls = L / R, nb = n / R;
+    std::vector<std::vector<unsigned>> bucket(16);
+    for (int b = 0; b < n / L; ++b)
+        for (int j = 0; j < Ls; ++j) bucket[(b * L + j) % 16].push_back((unsigned)(b * L + j) | ((unsigned)j << 16));
+    std::vector<unsigned> out;
+    out.reserve(nb);
+    while ((int)out.size() < nb) {
+        int cls[16];
+        for (int c = 0; c < 16; ++c) cls[c] = c;
+        std::stable_sort(cls, cls + 16, [&](int a, int b) { return bucket[a].size() > bucket[b].size(); });
+        int jslot[16];
+        for (int c = 0; c < 16; ++c) jslot[c] = -1;
+        int taken = 0;
+        for (int ci = 0; ci < 16 && taken < 16; ++ci) {
+            std::vector<unsigned> &bk = bucket[cls[ci]];
+            for (size_t i = 0; i < bk.size(); ++i) {
+                const int j = (int)(bk[i] >> 16);
+                if (jslot[j % 16] >= 0 && jslot[j % 16] != j) continue;  // another twiddle on the same bank pair
+                jslot[j % 16] = j;
+                out.push_back(bk[i]);
+                bk.erase(bk.begin() + (long)i);
+                ++taken;
+                break;
+            }
+        }
+        // nothing conflict-free left for this run: fill it from the fullest classes
+        while (taken < 16 && (int)out.size() < nb) {
+            int best = -1;
+            for (int c = 0; c < 16; ++c)
+                if (!bucket[c].empty() && (best < 0 || bucket[c].size() > bucket[best].size())) best = c;
+            if (best < 0) break;
+            out.push_back(bucket[best].front());
+            bucket[best].erase(bucket[best].begin());
+            ++taken;
+        }
+    }
+    return out;
+}
+
+// Order of the retained orders m < mmax for the emit / gather loops.  `lanes` adjacent lanes share an order, lane c
+// of them touching transforms 2c and 2c+1 (which lie `np` float2 apart); a wavefront holds 16 / lanes orders.
+// Both spectrum slots an order reads (bin m and bin n - m) must avoid the bank pairs of the other orders of the run.
+std::vector<unsigned short> order_emit(int n, int mmax, int np, int lanes, const std::vector<unsigned short> &perm) {
+    const int per = 16 / lanes;
+    auto mask = [&](int m, int which) {
+        const int k = which == 0 ? (m < n ? m : 0) : ((n - m % n) % n);
+        unsigned mk = 0;
+        for (int c = 0; c < lanes; ++c) mk |= 1u << ((2 * c * np + perm[k]) % 16);
+        return mk;
+    };
+    std::vector<unsigned short> out;
+    out.reserve(mmax);
+    size_t first = 0;
+    std::vector<char> used(mmax, 0);
+    while ((int)out.size() < mmax) {
+        while (used[first]) ++first;
+        int cnt = 1;
+        unsigned u0 = mask((int)first, 0), u1 = mask((int)first, 1);
+        used[first] = 1;
+        out.push_back((unsigned short)first);
+        // look a bounded distance ahead so that neighbouring orders (neighbouring rows of the operand) stay together
+        for (size_t i = first + 1; i < (size_t)mmax && i < first + 256 && cnt < per; ++i) {
+            if (used[i]) continue;
+            const unsigned s0 = mask((int)i, 0), s1 = mask((int)i, 1);
+            if ((s0 & u0) || (s1 & u1)) continue;
+            u0 |= s0;
+            u1 |= s1;
+            used[i] = 1;
+            out.push_back((unsigned short)i);
+            ++cnt;
+        }
+        for (size_t i = first + 1; i < (size_t)mmax && cnt < per; ++i) {
+            if (used[i]) continue;
+            used[i] = 1;
+            out.push_back((unsigned short)i);
+            ++cnt;
+        }
+    }
+    return out;
+}
+
 }  // namespace
 
-int build_fft_plan(int nlon, FftPlanDev *out, float2 **d_tw, unsigned short **d_perm) {
+int build_fft_plan(int nlon, int mmax_emit, FftPlanDev *out, float2 **d_tw, unsigned short **d_perm) {
     if (nlon < 2 || nlon > 65535) return fail(SHTB200_EINVAL, "nlon must be in [2, 65535]");
     // strip prime factors 7..31 (generic butterflies), split the rest into fast radices
     std::vector<int> slow;
@@ -123,12 +217,8 @@ int build_fft_plan(int nlon, FftPlanDev *out, float2 **d_tw, unsigned short **d_
                 }
         L = Ls;
     }
+    if (tw.size() & 1) tw.push_back(make_float2(0.f, 0.f));  // keeps what follows the pass tables 16-byte aligned
     fp.tw_pass_total = (int)tw.size();
-    // the generic (prime radix > 5) butterflies also need the roots of unity of order n
-    for (int k = 0; k < nlon; ++k) {
-        double a = -2.0 * M_PI * (double)k / (double)nlon;
-        tw.push_back(make_float2((float)cos(a), (float)sin(a)));
-    }
     // output bin k = q1 + R1 (q2 + R2 (...)) ends at slot q1 n/R1 + q2 n/(R1 R2) + ...
     std::vector<unsigned short> perm(nlon);
     for (int k = 0; k < nlon; ++k) {
@@ -140,13 +230,64 @@ int build_fft_plan(int nlon, FftPlanDev *out, float2 **d_tw, unsigned short **d_
         }
         perm[k] = (unsigned short)pos;
     }
-    SHT_CUDA_CHECK(cudaMalloc(d_tw, sizeof(float2) * tw.size()));
-    SHT_CUDA_CHECK(cudaMalloc(d_perm, sizeof(unsigned short) * nlon));
-    SHT_CUDA_CHECK(cudaMemcpy(*d_tw, tw.data(), sizeof(float2) * tw.size(), cudaMemcpyHostToDevice));
-    SHT_CUDA_CHECK(cudaMemcpy(*d_perm, perm.data(), sizeof(unsigned short) * nlon, cudaMemcpyHostToDevice));
-    fp.tw = *d_tw;
-    fp.tw_full = *d_tw + fp.tw_pass_total;
-    fp.perm = *d_perm;
+    // thread -> butterfly tables of all passes, and the emit order; they share one allocation with perm:
+    // [bfly u32 x bf_total][perm u16 x n][eorder u16 x mmax_emit]
+    std::vector<unsigned> bfly;
+    L = nlon;
+    for (int s = 0; s < fp.nstages; ++s) {
+        fp.bfoff[s] = (int)bfly.size();
+        std::vector<unsigned> o = order_butterflies(nlon, L, rad[s]);
+        {  // every butterfly of the pass exactly once
+            std::vector<unsigned> chk(o);
+            std::sort(chk.begin(), chk.end(), [](unsigned a, unsigned b) { return (a & 0xffffu) < (b & 0xffffu); });
+            const int Ls = L / rad[s];
+            bool okp = (int)chk.size() == nlon / rad[s];
+            for (size_t i = 0; okp && i < chk.size(); ++i) okp = (int)(chk[i] & 0xffffu) == (int)(i / Ls) * L + (int)(i % Ls) && (int)(chk[i] >> 16) == (int)(i % Ls);
+            if (!okp) return fail(SHTB200_EINVAL, "butterfly order is not a permutation");
+        }
+        bfly.insert(bfly.end(), o.begin(), o.end());
+        L /= rad[s];
+    }
+    fp.bf_total = (int)bfly.size();
+    std::vector<unsigned short> eorder;
+    if (mmax_emit > 0) eorder = order_emit(nlon, mmax_emit, nlon + kPad, 4, perm);
+    {
+        std::vector<unsigned short> chk(eorder);
+        std::sort(chk.begin(), chk.end());
+        for (size_t i = 0; i < chk.size(); ++i)
+            if (chk[i] != i) return fail(SHTB200_EINVAL, "emit order is not a permutation");
+    }
+    fp.eorder_len = (int)eorder.size();
+    // One device allocation: the tables the kernels keep in shared memory as one 16-byte granular blob
+    //   [pass twiddles float2 x tw_pass_total][bfly u32 x bf_total][perm u16 x n][eorder u16 x eorder_len][pad]
+    // followed by the n roots of unity the generic prime-radix butterflies read from global memory.
+    const size_t o_bf = sizeof(float2) * tw.size();
+    const size_t o_perm = o_bf + sizeof(unsigned) * bfly.size();
+    const size_t o_eo = o_perm + sizeof(unsigned short) * perm.size();
+    const size_t tab_bytes = (o_eo + sizeof(unsigned short) * eorder.size() + 15) / 16 * 16;
+    std::vector<unsigned char> tab(tab_bytes + sizeof(float2) * nlon, 0);
+    memcpy(tab.data(), tw.data(), sizeof(float2) * tw.size());
+    memcpy(tab.data() + o_bf, bfly.data(), sizeof(unsigned) * bfly.size());
+    memcpy(tab.data() + o_perm, perm.data(), sizeof(unsigned short) * perm.size());
+    if (!eorder.empty()) memcpy(tab.data() + o_eo, eorder.data(), sizeof(unsigned short) * eorder.size());
+    {
+        float2 *roots = reinterpret_cast<float2 *>(tab.data() + tab_bytes);
+        for (int k = 0; k < nlon; ++k) {
+            double a = -2.0 * M_PI * (double)k / (double)nlon;
+            roots[k] = make_float2((float)cos(a), (float)sin(a));
+        }
+    }
+    unsigned char *d_blob = nullptr;
+    SHT_CUDA_CHECK(cudaMalloc(&d_blob, tab.size()));
+    SHT_CUDA_CHECK(cudaMemcpy(d_blob, tab.data(), tab.size(), cudaMemcpyHostToDevice));
+    *d_tw = reinterpret_cast<float2 *>(d_blob);
+    *d_perm = nullptr;
+    fp.tab_bytes = (int)tab_bytes;
+    fp.tw = reinterpret_cast<const float2 *>(d_blob);
+    fp.tw_full = reinterpret_cast<const float2 *>(d_blob + tab_bytes);
+    fp.bfly = reinterpret_cast<const unsigned *>(d_blob + o_bf);
+    fp.perm = reinterpret_cast<const unsigned short *>(d_blob + o_perm);
+    fp.eorder = eorder.empty() ? nullptr : reinterpret_cast<const unsigned short *>(d_blob + o_eo);
     *out = fp;
     return SHTB200_OK;
 }
@@ -354,10 +495,11 @@ __device__ void fft_group(float2 *d, const FftPlanDev &fp, const float2 *tw_s, i
         const int nb = n / R;  // butterflies in this pass
         const bool has_tw = Ls > 1;
         const float2 *tw = tw_s + fp.twoff[s];
+        const unsigned *bt = reinterpret_cast<const unsigned *>(tw_s + fp.tw_pass_total) + fp.bfoff[s];
         for (int i = lane; i < nb; i += 32 * G) {
-            const int b = i / Ls;
-            const int j = i - b * Ls;
-            float2 *p = d + b * L + j;
+            const unsigned e = bt[i];
+            const int j = (int)(e >> 16);
+            float2 *p = d + (e & 0xffffu);
             switch (R) {
                 case 16: butterfly<16, INV>(p, Ls, tw + j, Ls, has_tw); break;
                 case 15: butterfly<15, INV>(p, Ls, tw + j, Ls, has_tw); break;
@@ -377,15 +519,45 @@ __device__ void fft_group(float2 *d, const FftPlanDev &fp, const float2 *tw_s, i
     }
 }
 
-// Transforms of a CTA lie `n + kPad` float2 apart: with a pitch that is a multiple of 128 bytes the same bin of all
-// transforms would fall on one bank group and the final gather / initial scatter (4 lanes per order, each on two
-// different transforms) would serialise.
-constexpr int kPad = 2;
 
-// shared memory: [NW * (n + kPad) float2 data][per-pass twiddle tables][n u16 perm]
-__device__ __forceinline__ void load_tables(const FftPlanDev &fp, float2 *tw_s, unsigned short *perm_s) {
-    for (int i = threadIdx.x; i < fp.tw_pass_total; i += blockDim.x) tw_s[i] = fp.tw[i];
-    for (int i = threadIdx.x; i < fp.n; i += blockDim.x) perm_s[i] = fp.perm[i];
+// shared memory: [NW * (n + kPad) float2 data, rounded up to 16 bytes][table blob: pass twiddles | thread -> butterfly
+// tables u32 | n u16 perm | u16 emit order][8-byte mbarrier]
+__device__ __forceinline__ size_t data_bytes(int nw, int n) { return ((size_t)nw * (n + kPad) * sizeof(float2) + 15) / 16 * 16; }
+
+// plain copy of the blob by all threads of the CTA (callers synchronise afterwards)
+__device__ __forceinline__ void load_tables(const FftPlanDev &fp, float2 *tw_s) {
+    const uint4 *src = reinterpret_cast<const uint4 *>(fp.tw);
+    uint4 *dst = reinterpret_cast<uint4 *>(tw_s);
+    for (int i = threadIdx.x; i < fp.tab_bytes / 16; i += blockDim.x) dst[i] = __ldg(src + i);
+}
+
+// The same copy as ONE asynchronous bulk transfer issued by thread 0, so that it runs under the row loads instead of
+// in front of them.  tables_begin() is called by every thread before the CTA's first barrier, tables_wait() by every
+// thread at a point all threads reach: it is a CTA-wide barrier and returns false (for all threads alike) when the
+// copy did not land within about a second, in which case the kernel reports through *err and leaves.
+__device__ __forceinline__ void tables_begin(const FftPlanDev &fp, float2 *tw_s, uint32_t bar) {
+    if (threadIdx.x == 0) {
+        ptx::mbar_init(bar, 1);
+        ptx::fence_barrier_init();
+        ptx::mbar_arrive_expect_tx(bar, (uint32_t)fp.tab_bytes);
+        ptx::bulk_load(ptx::smem_u32(tw_s), fp.tw, (uint32_t)fp.tab_bytes, bar);
+    }
+}
+__device__ __forceinline__ bool tables_wait(uint32_t bar, int *err) {
+    __syncthreads();  // the barrier's initialisation is visible to every thread that polls it
+    bool ok = ptx::mbar_try_wait(bar, 0) != 0;
+    if (!ok) {
+        const long long t0 = clock64();
+        for (uint32_t it = 1; !ok; ++it) {
+            ok = ptx::mbar_try_wait(bar, 0) != 0;
+            if (!ok && (it & 63u) == 0u && clock64() - t0 > 2000000000ll) break;
+        }
+    }
+    if (__syncthreads_or(ok ? 0 : 1)) {
+        if (threadIdx.x == 0 && err) atomicExch(err, 0x0F7F0001);
+        return false;
+    }
+    return true;
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -405,15 +577,15 @@ __device__ __forceinline__ void load_tables(const FftPlanDev &fp, float2 *tw_s, 
 template <int NW, int VEC, int G>
 __global__ void __launch_bounds__(32 * NW * G, (NW * G >= 16) ? 2 : 1) fft_analysis_kernel(const float *__restrict__ x, float *__restrict__ X, FftPlanDev fp,
                                                                                             int nlat, int Kh, int nfields, int ncp, int mmax,
-                                                                                            const float *__restrict__ mscale, int zero_imag_edges, int vec4ok) {
+                                                                                            const float *__restrict__ mscale, int zero_imag_edges, int vec4ok, int *err) {
     extern __shared__ float2 smem[];
     const int n = fp.n;
     constexpr int NF = NW / VEC;                    // fields (or component pairs) per CTA
     constexpr int GT = 32 * G;                      // threads per transform
     const int np = n + kPad;
     float2 *data = smem;
-    float2 *tw_s = data + (size_t)NW * np;
-    unsigned short *perm_s = reinterpret_cast<unsigned short *>(tw_s + fp.tw_pass_total);
+    float2 *tw_s = reinterpret_cast<float2 *>(reinterpret_cast<unsigned char *>(smem) + data_bytes(NW, n));
+    const unsigned short *perm_s = reinterpret_cast<const unsigned short *>(reinterpret_cast<const unsigned *>(tw_s + fp.tw_pass_total) + fp.bf_total);
 
     const int kn = blockIdx.y;
     const int f0 = blockIdx.x * NF;  // field blocks vary fastest: CTAs that complete each other's 128-byte lines run together
@@ -431,7 +603,8 @@ __global__ void __launch_bounds__(32 * NW * G, (NW * G >= 16) ? 2 : 1) fft_analy
         (void)w4;
         return;
     }
-    load_tables(fp, tw_s, perm_s);
+    const uint32_t tab_bar = ptx::smem_u32(reinterpret_cast<unsigned char *>(tw_s) + fp.tab_bytes);
+    tables_begin(fp, tw_s, tab_bar);
 
     // ---- each group loads and folds its own pair of rows ----
     {
@@ -484,7 +657,7 @@ __global__ void __launch_bounds__(32 * NW * G, (NW * G >= 16) ? 2 : 1) fft_analy
             }
         }
     }
-    __syncthreads();  // tables and rows in place
+    if (!tables_wait(tab_bar, err)) return;  // (CTA-wide barrier: rows in place as well)
 
     fft_group<false, G>(data + (size_t)t * np, fp, tw_s, lane, 1 + t);
     __syncthreads();
@@ -495,7 +668,9 @@ __global__ void __launch_bounds__(32 * NW * G, (NW * G >= 16) ? 2 : 1) fft_analy
     const int nyq = n / 2;
     constexpr int LPM = NW / 2;  // lanes per order
     const int c = threadIdx.x % LPM;
-    for (int m = threadIdx.x / LPM; m < mmax; m += blockDim.x / LPM) {
+    const unsigned short *eo_s = (fp.eorder && fp.eorder_len == mmax) ? perm_s + n : nullptr;
+    for (int i = threadIdx.x / LPM; i < mmax; i += blockDim.x / LPM) {
+        const int m = eo_s ? eo_s[i] : i;
         float e[4], o[4];  // (re, im) of the even / odd fold of transforms 2c, 2c+1
         if (m <= nyq) {
             const float sc = 0.5f * mscale[m];
@@ -549,22 +724,23 @@ __global__ void __launch_bounds__(32 * NW * G, (NW * G >= 16) ? 2 : 1) fft_analy
 template <int NW, int VEC, int G>
 __global__ void __launch_bounds__(32 * NW * G, (NW * G >= 16) ? 2 : 1) fft_synthesis_kernel(const float *__restrict__ Y, float *__restrict__ x, FftPlanDev fp,
                                                                                              int nlat, int Kh, int nfields, int ncp, int mmax,
-                                                                                             const float *__restrict__ mscale, int vec4ok) {
+                                                                                             const float *__restrict__ mscale, int vec4ok, int *err) {
     extern __shared__ float2 smem[];
     const int n = fp.n;
     constexpr int NF = NW / VEC;
     constexpr int GT = 32 * G;
     const int np = n + kPad;
     float2 *data = smem;
-    float2 *tw_s = data + (size_t)NW * np;
-    unsigned short *perm_s = reinterpret_cast<unsigned short *>(tw_s + fp.tw_pass_total);
+    float2 *tw_s = reinterpret_cast<float2 *>(reinterpret_cast<unsigned char *>(smem) + data_bytes(NW, n));
+    const unsigned short *perm_s = reinterpret_cast<const unsigned short *>(reinterpret_cast<const unsigned *>(tw_s + fp.tw_pass_total) + fp.bf_total);
 
     const int kn = blockIdx.y;
     const int f0 = blockIdx.x * NF;
     const int colbase = 2 * VEC * f0;
     const int t = threadIdx.x / GT, lane = threadIdx.x % GT;
-    load_tables(fp, tw_s, perm_s);
-    __syncthreads();
+    const uint32_t tab_bar = ptx::smem_u32(reinterpret_cast<unsigned char *>(tw_s) + fp.tab_bytes);
+    tables_begin(fp, tw_s, tab_bar);
+    if (!tables_wait(tab_bar, err)) return;
 
     const int nyq = n / 2;
     const int mtop = min(mmax, nyq + 1);
@@ -581,7 +757,10 @@ __global__ void __launch_bounds__(32 * NW * G, (NW * G >= 16) ? 2 : 1) fft_synth
         constexpr int LPM = NW / 2;
         const int c = threadIdx.x % LPM;
         const int col = colbase + 4 * c;
-        for (int m = threadIdx.x / LPM; m < mtop; m += blockDim.x / LPM) {
+        const unsigned short *eo_s = (fp.eorder && fp.eorder_len == mmax) ? perm_s + n : nullptr;
+        for (int i = threadIdx.x / LPM; i < mmax; i += blockDim.x / LPM) {
+            const int m = eo_s ? eo_s[i] : i;
+            if (m >= mtop) continue;
             float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
             if (col < ncp) {
                 a = *reinterpret_cast<const float4 *>(Y + (size_t)blocked_row(2 * m, kn, 2 * mmax) * ncp + col);
@@ -648,9 +827,9 @@ __global__ void __launch_bounds__(32 * NW) rfft_rows_kernel(const float *__restr
     const int n = fp.n;
     float2 *data = smem;
     float2 *tw_s = data + (size_t)NW * n;
-    unsigned short *perm_s = reinterpret_cast<unsigned short *>(tw_s + fp.tw_pass_total);
+    const unsigned short *perm_s = reinterpret_cast<const unsigned short *>(reinterpret_cast<const unsigned *>(tw_s + fp.tw_pass_total) + fp.bf_total);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    load_tables(fp, tw_s, perm_s);
+    load_tables(fp, tw_s);
     const long long r0 = (long long)blockIdx.x * (2 * NW);
     {
         const long long ra = r0 + 2 * warp, rb = ra + 1;
@@ -687,9 +866,9 @@ __global__ void __launch_bounds__(32 * NW) irfft_rows_kernel(const float2 *__res
     const int n = fp.n;
     float2 *data = smem;
     float2 *tw_s = data + (size_t)NW * n;
-    unsigned short *perm_s = reinterpret_cast<unsigned short *>(tw_s + fp.tw_pass_total);
+    const unsigned short *perm_s = reinterpret_cast<const unsigned short *>(reinterpret_cast<const unsigned *>(tw_s + fp.tw_pass_total) + fp.bf_total);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    load_tables(fp, tw_s, perm_s);
+    load_tables(fp, tw_s);
     float2 *dd = data + (size_t)warp * n;
     for (int j = lane; j < n; j += 32) dd[j] = make_float2(0.f, 0.f);
     __syncthreads();
@@ -719,7 +898,7 @@ __global__ void __launch_bounds__(32 * NW) irfft_rows_kernel(const float2 *__res
 // launchers
 // ------------------------------------------------------------------------------------------------
 static size_t fft_smem_bytes(int nffts, const FftPlanDev &fp) {
-    return (size_t)nffts * (fp.n + kPad) * sizeof(float2) + (size_t)fp.tw_pass_total * sizeof(float2) + (size_t)fp.n * sizeof(unsigned short) + 16;
+    return ((size_t)nffts * (fp.n + kPad) * sizeof(float2) + 15) / 16 * 16 + (size_t)fp.tab_bytes + 16;
 }
 
 template <typename K>
@@ -751,7 +930,7 @@ int launch_fft_analysis(const Plan &pl, const float *x, float *X, int nfields, c
     do {                                                                                                                                    \
         if ((rc = set_smem(fft_analysis_kernel<WW, VV, kGroupWarps>, smem)) != 0) return rc;                                                \
         fft_analysis_kernel<WW, VV, kGroupWarps><<<grid, 32 * WW * kGroupWarps, smem, st>>>(x, X, pl.fft, pl.nlat, pl.Kh, nfields, ncp,     \
-                                                                                            pl.mmax, pl.d_mscale, pl.zero_imag_edges, al); \
+                                                                                            pl.mmax, pl.d_mscale, pl.zero_imag_edges, al, pl.d_err); \
     } while (0)
     if (vec == 1) {
         if (NW == 8) LAUNCH_A(8, 1);
@@ -778,7 +957,7 @@ int launch_fft_synthesis(const Plan &pl, const float *Y, float *x, int nfields, 
     do {                                                                                                                                 \
         if ((rc = set_smem(fft_synthesis_kernel<WW, VV, kGroupWarps>, smem)) != 0) return rc;                                            \
         fft_synthesis_kernel<WW, VV, kGroupWarps><<<grid, 32 * WW * kGroupWarps, smem, st>>>(Y, x, pl.fft, pl.nlat, pl.Kh, nfields, ncp, \
-                                                                                             pl.mmax, pl.d_mscale, al);                  \
+                                                                                             pl.mmax, pl.d_mscale, al, pl.d_err);       \
     } while (0)
     if (vec == 1) {
         if (NW == 8) LAUNCH_S(8, 1);
@@ -809,7 +988,7 @@ static int cached_fft(int nlon, FftPlanDev *fp) {
         if (c.n == nlon && c.device == dev) { *fp = c.fp; return SHTB200_OK; }
     for (auto &c : g_cache)
         if (c.n == 0) {
-            int rc = build_fft_plan(nlon, &c.fp, &c.tw, &c.perm);
+            int rc = build_fft_plan(nlon, 0, &c.fp, &c.tw, &c.perm);
             if (rc) return rc;
             c.n = nlon;
             c.device = dev;

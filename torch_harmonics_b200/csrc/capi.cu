@@ -232,7 +232,7 @@ int shtb200_plan_create(shtb200_plan **plan_out, int kind, int nlat, int nlon, i
     pl->Lh = (lmax + 1) / 2;
     pl->negate_seg1 = (kind == SHTB200_VSHT_ADJOINT || kind == SHTB200_IVSHT_ADJOINT) ? 1 : 0;
 
-    int rc = build_fft_plan(nlon, mmax, &pl->fft, &pl->d_tw, &pl->d_perm);
+    int rc = build_fft_plan(nlon, mmax, pl->analysis ? kFftSplit : kFftPacked, &pl->fft, &pl->d_tw, &pl->d_perm);
     if (rc) { shtb200_plan_destroy(pl); return rc; }
 
     // per-order scale applied inside the FFT kernels

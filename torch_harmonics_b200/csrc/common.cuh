@@ -37,6 +37,11 @@ struct FftPlanDev {
     int sublen[kMaxFftStages];    // length L of the sub-transforms pass s splits (L_0 = n, L_{s+1} = L_s / radix_s)
     int twoff[kMaxFftStages];     // offset of pass s's twiddle table inside tw
     int tw_pass_total;            // entries of all per-pass tables together (padded to an even count)
+    // Geometry of one transform in shared memory.  Split layout (analysis kernel; re array | im array of floats): the
+    // imaginary parts start `io` floats after the real parts, transforms lie `ts` floats apart (ts = 4 mod 32 spreads
+    // the transforms of a CTA over the banks), np = 0.  Interleaved layout (synthesis and stage kernels): transforms lie
+    // `np` float2 apart, io = ts = 0.
+    int io, ts, np;
     int tab_bytes;                // size of the blob [tw | bfly | perm | eorder] that starts at tw (a multiple of 16)
     const float2 *tw;             // per-pass tables: entry (q - 1) * L/R + j of pass s = exp(-2 pi i q j / L_s), from double
     const float2 *tw_full;        // n roots of unity exp(-2 pi i k / n) (generic prime-radix butterflies only)
@@ -164,7 +169,8 @@ struct Plan {
 // kernel launchers (defined in the .cu files)
 // ------------------------------------------------------------------------------------------------
 // mmax_emit > 0 also builds the emit order for that many retained orders (the SHT kernels); 0 leaves it out
-int build_fft_plan(int nlon, int mmax_emit, FftPlanDev *out, float2 **d_tw, unsigned short **d_perm);
+enum { kFftRows = 0, kFftSplit = 1, kFftPacked = 2 };  // shared-memory layout the tables are built for (see FftPlanDev)
+int build_fft_plan(int nlon, int mmax_emit, int layout, FftPlanDev *out, float2 **d_tw, unsigned short **d_perm);
 
 // analysis: rows of x -> folded, order-major operand X[blocked_row(group, k)][col] (row pitch round_up(ncols, 4))
 int launch_fft_analysis(const Plan &pl, const float *x, float *X, int nfields, cudaStream_t st);

@@ -1,17 +1,19 @@
 // Longitude transforms of the SHT: shared-memory mixed-radix FFT kernels.
 //
 // Analysis (grid -> order-major operand of the Legendre contraction), per CTA:
-//   * one pair of latitude rows (k', nlat-1-k') of each of eight fields is loaded with coalesced float4 reads
-//     and folded about the equator: z_j = (x_north + x_south) + i (x_north - x_south).  The even /
-//     odd combinations are what the parity-split Legendre tables contract with, and one complex
-//     transform of z yields the spectra of both real rows at once.
-//   * an in-place decimation-in-frequency FFT of length nlon runs in shared memory (radix 4, 2, 3, 5
-//     butterflies; any other prime factor <= 31 goes through a generic butterfly),
-//   * only the retained orders m < mmax are written, already transposed into the contraction's
-//     operand layout X[group = 2 m + parity][k'][column = 2 field + re/im] (columns contiguous; a CTA
-//     covers eight consecutive fields so that every write is a full 64-byte run).
-// Synthesis is the mirror image: gather the two parities, rebuild the Hermitian spectrum of
-// (north + i south), decimation-in-time inverse FFT, coalesced float4 row stores.
+//   * one pair of latitude rows (k', nlat-1-k') of each of eight fields arrives as bulk asynchronous copies
+//     (cp.async.bulk, one per row) straight into the real array / imaginary array of a split-complex transform
+//     buffer: z_j = x_north + i x_south.  One complex transform of z yields the spectra of both real rows at once;
+//     no thread touches the rows on their way in, and the tables come with them on the same mbarrier.
+//   * an in-place decimation-in-frequency FFT of length nlon runs in shared memory, two warps per transform
+//     (in-register butterflies of radix 2..16; any other prime factor <= 31 goes through a generic butterfly);
+//     a host-built table assigns butterflies to threads so that every pass is free of bank conflicts,
+//   * the retained orders m < mmax are separated into the two rows' spectra, folded about the equator (even = north
+//     + south, odd = north - south: what the parity-split Legendre tables contract with) and written, already
+//     transposed, into the contraction's operand layout X[blocked_row(2 m + parity, k')][column = 2 field + re/im]
+//     (columns contiguous; a CTA covers eight consecutive fields so that every write is a full 64-byte run).
+// Synthesis is the mirror image on interleaved (re, im) buffers: gather the two parities, rebuild the Hermitian
+// spectrum of (north + i south), decimation-in-time inverse FFT, coalesced float4 row stores.
 //
 // Replaces torch_harmonics/fft.py:52-68 (rfft wrapper), :71-96 (irfft wrapper) and the
 // scale / transpose / real-imag split passes at torch_harmonics/sht.py:171-176 and :337-340.
@@ -29,10 +31,6 @@
 
 namespace shtb200 {
 
-// Transforms of a CTA lie `n + kPad` float2 apart: with a pitch that is a multiple of 128 bytes the same bin of all
-// transforms would fall on one bank group and the final gather / initial scatter (4 lanes per order, each on two
-// different transforms) would serialise.
-constexpr int kPad = 2;
 
 // ------------------------------------------------------------------------------------------------
 // host: factorisation, twiddles, output permutation
@@ -66,60 +64,75 @@ std::vector<int> best_split(int n, std::vector<std::vector<int>> &memo, std::vec
     return best;
 }
 
-// Shared memory serves a 64-bit access of a warp as two wavefronts of 16 lanes; a wavefront costs one extra cycle for
-// every further distinct address that falls on an already used 8-byte bank pair (index mod 16 in float2 units).
-// Order the butterflies of a pass (first-leg slot `off`, twiddle index j) so that each run of 16 consecutive
-// threads touches 16 different bank pairs, for the data and for the twiddle table alike.  All legs of a butterfly
-// are shifted by the same amount, so one check covers them all.
-std::vector<unsigned> order_butterflies(int n, int L, int R) {
+// Shared memory serves a warp's 32-bit accesses in one wavefront when the 32 lanes touch 32 different banks (word index
+// mod 32), and a 64-bit access as two wavefronts of 16 lanes that must touch 16 different bank pairs (index mod 16 in
+// 8-byte units); every further distinct address on a used bank costs one more wavefront.
+// Order the butterflies of a pass (first-leg slot `off`, twiddle index j) so that each run of `width` consecutive
+// threads is conflict-free on the data (width 32: split re / im arrays of floats; width 16: interleaved float2) and
+// each half-warp on the float2 twiddle table.  All legs of a butterfly are shifted by the same amount, so one check
+// covers them all.
+std::vector<unsigned> order_butterflies(int n, int L, int R, int width) {
     const int Ls = L / R, nb = n / R;
-    std::vector<std::vector<unsigned>> bucket(16);
+    std::vector<std::vector<unsigned>> bucket(width);
     for (int b = 0; b < n / L; ++b)
-        for (int j = 0; j < Ls; ++j) bucket[(b * L + j) % 16].push_back((unsigned)(b * L + j) | ((unsigned)j << 16));
+        for (int j = 0; j < Ls; ++j) bucket[(b * L + j) % width].push_back((unsigned)(b * L + j) | ((unsigned)j << 16));
     std::vector<unsigned> out;
     out.reserve(nb);
+    std::vector<int> cls(width);
     while ((int)out.size() < nb) {
-        int cls[16];
-        for (int c = 0; c < 16; ++c) cls[c] = c;
-        std::stable_sort(cls, cls + 16, [&](int a, int b) { return bucket[a].size() > bucket[b].size(); });
-        int jslot[16];
-        for (int c = 0; c < 16; ++c) jslot[c] = -1;
+        for (int c = 0; c < width; ++c) cls[c] = c;
+        std::stable_sort(cls.begin(), cls.end(), [&](int a, int b) { return bucket[a].size() > bucket[b].size(); });
+        // the run is filled as `width / 16` half-warps, each with its own twiddle bank pairs
+        const int halves = width / 16;
+        std::vector<std::vector<unsigned>> half(halves);
+        std::vector<std::vector<int>> jslot(halves, std::vector<int>(16, -1));
         int taken = 0;
-        for (int ci = 0; ci < 16 && taken < 16; ++ci) {
+        for (int ci = 0; ci < width && taken < width; ++ci) {
             std::vector<unsigned> &bk = bucket[cls[ci]];
-            for (size_t i = 0; i < bk.size(); ++i) {
+            bool placed = false;
+            for (size_t i = 0; i < bk.size() && !placed; ++i) {
                 const int j = (int)(bk[i] >> 16);
-                if (jslot[j % 16] >= 0 && jslot[j % 16] != j) continue;  // another twiddle on the same bank pair
-                jslot[j % 16] = j;
-                out.push_back(bk[i]);
-                bk.erase(bk.begin() + (long)i);
-                ++taken;
-                break;
+                for (int h = 0; h < halves && !placed; ++h) {
+                    if ((int)half[h].size() >= 16) continue;
+                    if (jslot[h][j % 16] >= 0 && jslot[h][j % 16] != j) continue;  // another twiddle on the same bank pair
+                    jslot[h][j % 16] = j;
+                    half[h].push_back(bk[i]);
+                    bk.erase(bk.begin() + (long)i);
+                    placed = true;
+                    ++taken;
+                }
             }
         }
         // nothing conflict-free left for this run: fill it from the fullest classes
-        while (taken < 16 && (int)out.size() < nb) {
+        while (taken < width && (int)out.size() + taken < nb) {
             int best = -1;
-            for (int c = 0; c < 16; ++c)
+            for (int c = 0; c < width; ++c)
                 if (!bucket[c].empty() && (best < 0 || bucket[c].size() > bucket[best].size())) best = c;
             if (best < 0) break;
-            out.push_back(bucket[best].front());
+            for (int h = 0; h < halves; ++h)
+                if ((int)half[h].size() < 16) { half[h].push_back(bucket[best].front()); break; }
             bucket[best].erase(bucket[best].begin());
             ++taken;
         }
+        // full half-warps first, so that only the very last one of the pass may be ragged
+        for (int h = 0; h < halves; ++h)
+            if ((int)half[h].size() == 16) out.insert(out.end(), half[h].begin(), half[h].end());
+        for (int h = 0; h < halves; ++h)
+            if ((int)half[h].size() != 16) out.insert(out.end(), half[h].begin(), half[h].end());
     }
     return out;
 }
 
-// Order of the retained orders m < mmax for the emit / gather loops.  `lanes` adjacent lanes share an order, lane c
-// of them touching transforms 2c and 2c+1 (which lie `np` float2 apart); a wavefront holds 16 / lanes orders.
-// Both spectrum slots an order reads (bin m and bin n - m) must avoid the bank pairs of the other orders of the run.
-std::vector<unsigned short> order_emit(int n, int mmax, int np, int lanes, const std::vector<unsigned short> &perm) {
-    const int per = 16 / lanes;
+// Order of the retained orders m < mmax for the emit / gather loops of the SHT kernels.  `lanes` adjacent lanes share
+// an order, lane c of them touching transforms 2c and 2c+1, which lie `stride` units apart (floats in the split
+// layout, where a wavefront is the 32 lanes of a warp; float2 in the interleaved layout, where it is 16 lanes).
+// Both spectrum slots an order touches (bin m and bin n - m) must avoid the banks of the other orders of the wavefront.
+std::vector<unsigned short> order_emit(int n, int mmax, int stride, int lanes, int width, const std::vector<unsigned short> &perm) {
+    const int per = width / lanes;
     auto mask = [&](int m, int which) {
         const int k = which == 0 ? (m < n ? m : 0) : ((n - m % n) % n);
         unsigned mk = 0;
-        for (int c = 0; c < lanes; ++c) mk |= 1u << ((2 * c * np + perm[k]) % 16);
+        for (int c = 0; c < lanes; ++c) mk |= 1u << ((2 * c * stride + perm[k]) % width);
         return mk;
     };
     std::vector<unsigned short> out;
@@ -133,7 +146,7 @@ std::vector<unsigned short> order_emit(int n, int mmax, int np, int lanes, const
         used[first] = 1;
         out.push_back((unsigned short)first);
         // look a bounded distance ahead so that neighbouring orders (neighbouring rows of the operand) stay together
-        for (size_t i = first + 1; i < (size_t)mmax && i < first + 256 && cnt < per; ++i) {
+        for (size_t i = first + 1; i < (size_t)mmax && i < first + 512 && cnt < per; ++i) {
             if (used[i]) continue;
             const unsigned s0 = mask((int)i, 0), s1 = mask((int)i, 1);
             if ((s0 & u0) || (s1 & u1)) continue;
@@ -155,7 +168,7 @@ std::vector<unsigned short> order_emit(int n, int mmax, int np, int lanes, const
 
 }  // namespace
 
-int build_fft_plan(int nlon, int mmax_emit, FftPlanDev *out, float2 **d_tw, unsigned short **d_perm) {
+int build_fft_plan(int nlon, int mmax_emit, int layout, FftPlanDev *out, float2 **d_tw, unsigned short **d_perm) {
     if (nlon < 2 || nlon > 65535) return fail(SHTB200_EINVAL, "nlon must be in [2, 65535]");
     // strip prime factors 7..31 (generic butterflies), split the rest into fast radices
     std::vector<int> slow;
@@ -236,7 +249,7 @@ int build_fft_plan(int nlon, int mmax_emit, FftPlanDev *out, float2 **d_tw, unsi
     L = nlon;
     for (int s = 0; s < fp.nstages; ++s) {
         fp.bfoff[s] = (int)bfly.size();
-        std::vector<unsigned> o = order_butterflies(nlon, L, rad[s]);
+        std::vector<unsigned> o = order_butterflies(nlon, L, rad[s], layout == kFftSplit ? 32 : 16);
         {  // every butterfly of the pass exactly once
             std::vector<unsigned> chk(o);
             std::sort(chk.begin(), chk.end(), [](unsigned a, unsigned b) { return (a & 0xffffu) < (b & 0xffffu); });
@@ -250,7 +263,18 @@ int build_fft_plan(int nlon, int mmax_emit, FftPlanDev *out, float2 **d_tw, unsi
     }
     fp.bf_total = (int)bfly.size();
     std::vector<unsigned short> eorder;
-    if (mmax_emit > 0) eorder = order_emit(nlon, mmax_emit, nlon + kPad, 4, perm);
+    if (layout == kFftSplit) {
+        fp.io = (nlon + 3) / 4 * 4;
+        fp.ts = 2 * fp.io;
+        fp.ts += ((4 - fp.ts % 32) + 32) % 32;
+        if (mmax_emit > 0) eorder = order_emit(nlon, mmax_emit, fp.ts, 4, 32, perm);
+    } else if (layout == kFftPacked) {
+        // with a pitch that is a multiple of 128 bytes the same bin of all transforms would fall on one bank pair
+        fp.np = nlon + 2;
+        if (mmax_emit > 0) eorder = order_emit(nlon, mmax_emit, fp.np, 4, 16, perm);
+    } else {
+        fp.np = nlon;
+    }
     {
         std::vector<unsigned short> chk(eorder);
         std::sort(chk.begin(), chk.end());
@@ -413,46 +437,63 @@ template <bool INV> struct Dft<12, INV> : DftComposite<3, 4, INV> {};
 template <bool INV> struct Dft<15, INV> : DftComposite<3, 5, INV> {};
 template <bool INV> struct Dft<16, INV> : DftComposite<4, 4, INV> {};
 
+// Two views of a transform in shared memory: interleaved (re, im) pairs, or the real parts and the imaginary parts
+// as two separate arrays.  The SHT kernels use the second: a pair of latitude rows copied from global memory as it is
+// IS north + i south in that form, so the rows move between global and shared memory as bulk copies.
+struct CxPacked {
+    float2 *p;
+    __device__ __forceinline__ float2 ld(int i) const { return p[i]; }
+    __device__ __forceinline__ void st(int i, float2 v) const { p[i] = v; }
+};
+struct CxSplit {
+    float *re, *im;
+    __device__ __forceinline__ float2 ld(int i) const { return make_float2(re[i], im[i]); }
+    __device__ __forceinline__ void st(int i, float2 v) const {
+        re[i] = v.x;
+        im[i] = v.y;
+    }
+};
+
 // One butterfly of a pass.  Forward (decimation in frequency): transform, then the pass twiddles w_L^{q j};
 // inverse (decimation in time): conjugate twiddles first, then the conjugate transform.  `tw` points at the
-// table entry of (q = 1, this j); consecutive q are `twstr` entries apart.
-template <int R, bool INV>
-__device__ __forceinline__ void butterfly(float2 *p, int str, const float2 *tw, int twstr, bool has_tw) {
+// table entry of (q = 1, this j); consecutive q are `twstr` entries apart.  Legs at d[base + r * str].
+template <int R, bool INV, class D>
+__device__ __forceinline__ void butterfly(const D &d, int base, int str, const float2 *tw, int twstr, bool has_tw) {
     float2 v[R];
     if (!INV) {
 #pragma unroll
-        for (int r = 0; r < R; ++r) v[r] = p[r * str];
+        for (int r = 0; r < R; ++r) v[r] = d.ld(base + r * str);
         Dft<R, false>::run(v);
-        p[0] = v[0];
+        d.st(base, v[0]);
         if (has_tw) {
 #pragma unroll
-            for (int q = 1; q < R; ++q) p[q * str] = cmul(v[q], tw[(q - 1) * twstr]);
+            for (int q = 1; q < R; ++q) d.st(base + q * str, cmul(v[q], tw[(q - 1) * twstr]));
         } else {
 #pragma unroll
-            for (int q = 1; q < R; ++q) p[q * str] = v[q];
+            for (int q = 1; q < R; ++q) d.st(base + q * str, v[q]);
         }
     } else {
-        v[0] = p[0];
+        v[0] = d.ld(base);
         if (has_tw) {
 #pragma unroll
-            for (int r = 1; r < R; ++r) v[r] = cmulc(p[r * str], tw[(r - 1) * twstr]);
+            for (int r = 1; r < R; ++r) v[r] = cmulc(d.ld(base + r * str), tw[(r - 1) * twstr]);
         } else {
 #pragma unroll
-            for (int r = 1; r < R; ++r) v[r] = p[r * str];
+            for (int r = 1; r < R; ++r) v[r] = d.ld(base + r * str);
         }
         Dft<R, true>::run(v);
 #pragma unroll
-        for (int q = 0; q < R; ++q) p[q * str] = v[q];
+        for (int q = 0; q < R; ++q) d.st(base + q * str, v[q]);
     }
 }
 
 // Prime radix above 5: plain O(R^2) transform with the order-n roots of unity read from global memory.
-template <bool INV>
-__device__ void generic_butterfly(float2 *p, int R, int str, const float2 *tw, int twstr, bool has_tw, const float2 *__restrict__ roots, int n) {
+template <bool INV, class D>
+__device__ void generic_butterfly(const D &d, int base, int R, int str, const float2 *tw, int twstr, bool has_tw, const float2 *__restrict__ roots, int n) {
     float2 v[31], y[31];
     const int step = n / R;
     for (int r = 0; r < R; ++r) {
-        float2 z = p[r * str];
+        float2 z = d.ld(base + r * str);
         if (INV && has_tw && r) z = cmulc(z, tw[(r - 1) * twstr]);
         v[r] = z;
     }
@@ -470,7 +511,7 @@ __device__ void generic_butterfly(float2 *p, int R, int str, const float2 *tw, i
     for (int q = 0; q < R; ++q) {
         float2 z = y[q];
         if (!INV && has_tw && q) z = cmul(z, tw[(q - 1) * twstr]);
-        p[q * str] = z;
+        d.st(base + q * str, z);
     }
 }
 
@@ -484,8 +525,8 @@ __device__ __forceinline__ void group_sync(int id) {
 // All passes of ONE transform of length n, carried by G warps (in place, group barrier between passes).
 // `lane` is the thread's index inside the group.  Forward: natural order in, bin k at slot perm[k] out.
 // Inverse: bin k at slot perm[k] in, natural order out.
-template <bool INV, int G>
-__device__ void fft_group(float2 *d, const FftPlanDev &fp, const float2 *tw_s, int lane, int bar_id) {
+template <bool INV, int G, class D>
+__device__ void fft_group(const D &d, const FftPlanDev &fp, const float2 *tw_s, int lane, int bar_id) {
     const int n = fp.n;
     for (int ss = 0; ss < fp.nstages; ++ss) {
         const int s = INV ? fp.nstages - 1 - ss : ss;
@@ -499,31 +540,28 @@ __device__ void fft_group(float2 *d, const FftPlanDev &fp, const float2 *tw_s, i
         for (int i = lane; i < nb; i += 32 * G) {
             const unsigned e = bt[i];
             const int j = (int)(e >> 16);
-            float2 *p = d + (e & 0xffffu);
+            const int b = (int)(e & 0xffffu);
             switch (R) {
-                case 16: butterfly<16, INV>(p, Ls, tw + j, Ls, has_tw); break;
-                case 15: butterfly<15, INV>(p, Ls, tw + j, Ls, has_tw); break;
-                case 12: butterfly<12, INV>(p, Ls, tw + j, Ls, has_tw); break;
-                case 10: butterfly<10, INV>(p, Ls, tw + j, Ls, has_tw); break;
-                case 9: butterfly<9, INV>(p, Ls, tw + j, Ls, has_tw); break;
-                case 8: butterfly<8, INV>(p, Ls, tw + j, Ls, has_tw); break;
-                case 6: butterfly<6, INV>(p, Ls, tw + j, Ls, has_tw); break;
-                case 5: butterfly<5, INV>(p, Ls, tw + j, Ls, has_tw); break;
-                case 4: butterfly<4, INV>(p, Ls, tw + j, Ls, has_tw); break;
-                case 3: butterfly<3, INV>(p, Ls, tw + j, Ls, has_tw); break;
-                case 2: butterfly<2, INV>(p, Ls, tw + j, Ls, has_tw); break;
-                default: generic_butterfly<INV>(p, R, Ls, tw + j, Ls, has_tw, fp.tw_full, n);
+                case 16: butterfly<16, INV>(d, b, Ls, tw + j, Ls, has_tw); break;
+                case 15: butterfly<15, INV>(d, b, Ls, tw + j, Ls, has_tw); break;
+                case 12: butterfly<12, INV>(d, b, Ls, tw + j, Ls, has_tw); break;
+                case 10: butterfly<10, INV>(d, b, Ls, tw + j, Ls, has_tw); break;
+                case 9: butterfly<9, INV>(d, b, Ls, tw + j, Ls, has_tw); break;
+                case 8: butterfly<8, INV>(d, b, Ls, tw + j, Ls, has_tw); break;
+                case 6: butterfly<6, INV>(d, b, Ls, tw + j, Ls, has_tw); break;
+                case 5: butterfly<5, INV>(d, b, Ls, tw + j, Ls, has_tw); break;
+                case 4: butterfly<4, INV>(d, b, Ls, tw + j, Ls, has_tw); break;
+                case 3: butterfly<3, INV>(d, b, Ls, tw + j, Ls, has_tw); break;
+                case 2: butterfly<2, INV>(d, b, Ls, tw + j, Ls, has_tw); break;
+                default: generic_butterfly<INV>(d, b, R, Ls, tw + j, Ls, has_tw, fp.tw_full, n);
             }
         }
         group_sync<G>(bar_id);
     }
 }
 
-
-// shared memory: [NW * (n + kPad) float2 data, rounded up to 16 bytes][table blob: pass twiddles | thread -> butterfly
-// tables u32 | n u16 perm | u16 emit order][8-byte mbarrier]
-__device__ __forceinline__ size_t data_bytes(int nw, int n) { return ((size_t)nw * (n + kPad) * sizeof(float2) + 15) / 16 * 16; }
-
+// shared memory of the SHT kernels: [NW transforms x ts floats (re array | im array)][table blob: pass twiddles |
+// thread -> butterfly tables u32 | n u16 perm | u16 emit order][8-byte mbarrier]; the stage kernels keep NW x n float2.
 // plain copy of the blob by all threads of the CTA (callers synchronise afterwards)
 __device__ __forceinline__ void load_tables(const FftPlanDev &fp, float2 *tw_s) {
     const uint4 *src = reinterpret_cast<const uint4 *>(fp.tw);
@@ -577,14 +615,14 @@ __device__ __forceinline__ bool tables_wait(uint32_t bar, int *err) {
 template <int NW, int VEC, int G>
 __global__ void __launch_bounds__(32 * NW * G, (NW * G >= 16) ? 2 : 1) fft_analysis_kernel(const float *__restrict__ x, float *__restrict__ X, FftPlanDev fp,
                                                                                             int nlat, int Kh, int nfields, int ncp, int mmax,
-                                                                                            const float *__restrict__ mscale, int zero_imag_edges, int vec4ok, int *err) {
-    extern __shared__ float2 smem[];
+                                                                                            const float *__restrict__ mscale, int zero_imag_edges, int bulk_rows, int *err) {
+    extern __shared__ __align__(16) float smem_f[];
     const int n = fp.n;
     constexpr int NF = NW / VEC;                    // fields (or component pairs) per CTA
     constexpr int GT = 32 * G;                      // threads per transform
-    const int np = n + kPad;
-    float2 *data = smem;
-    float2 *tw_s = reinterpret_cast<float2 *>(reinterpret_cast<unsigned char *>(smem) + data_bytes(NW, n));
+    const int TS = fp.ts, IO = fp.io;
+    float *data = smem_f;
+    float2 *tw_s = reinterpret_cast<float2 *>(smem_f + (size_t)NW * TS);
     const unsigned short *perm_s = reinterpret_cast<const unsigned short *>(reinterpret_cast<const unsigned *>(tw_s + fp.tw_pass_total) + fp.bf_total);
 
     const int kn = blockIdx.y;
@@ -595,71 +633,52 @@ __global__ void __launch_bounds__(32 * NW * G, (NW * G >= 16) ? 2 : 1) fft_analy
     if (kn >= Kh) {
         // rows of the last 32-row block beyond the contraction length: the contraction reads them, they must be zeros
         const int kk = Ka + (kn - Kh);
-        const int w4 = 2 * NW / 4 * 1;  // float4 per run
         for (int i = threadIdx.x; i < ngroups * (2 * NW / 4); i += blockDim.x) {
             const int g = i / (2 * NW / 4), c = (i - g * (2 * NW / 4)) * 4;
             if (2 * VEC * f0 + c < ncp) *reinterpret_cast<float4 *>(X + (size_t)blocked_row(g, kk, ngroups) * ncp + 2 * VEC * f0 + c) = make_float4(0.f, 0.f, 0.f, 0.f);
         }
-        (void)w4;
         return;
     }
-    const uint32_t tab_bar = ptx::smem_u32(reinterpret_cast<unsigned char *>(tw_s) + fp.tab_bytes);
-    tables_begin(fp, tw_s, tab_bar);
+    const int ks = nlat - 1 - kn;
+    const bool self = (ks == kn);  // odd nlat: the equator row is its own mirror image
 
-    // ---- each group loads and folds its own pair of rows ----
+    // ---- tables and rows arrive as bulk copies: row kn of a field is the real array of its transform, row ks the
+    // imaginary array (z = north + i south; the fold into even / odd parts happens when the spectrum is emitted) ----
+    const uint32_t tab_bar = ptx::smem_u32(reinterpret_cast<unsigned char *>(tw_s) + fp.tab_bytes);
+    const int nvalid = min(NW, (nfields - f0) * VEC);  // transforms of this CTA that carry a field
+    if (threadIdx.x == 0) {
+        ptx::mbar_init(tab_bar, 1);
+        ptx::fence_barrier_init();
+        const uint32_t row_bytes = (uint32_t)n * 4u;
+        ptx::mbar_arrive_expect_tx(tab_bar, (uint32_t)fp.tab_bytes + (bulk_rows ? 2u * row_bytes * (uint32_t)nvalid : 0u));
+        ptx::bulk_load(ptx::smem_u32(tw_s), fp.tw, (uint32_t)fp.tab_bytes, tab_bar);
+        if (bulk_rows) {
+            for (int u = 0; u < nvalid; ++u) {
+                const size_t row0 = (size_t)((f0 + u / VEC) * VEC + u % VEC) * nlat;
+                ptx::bulk_load(ptx::smem_u32(data + (size_t)u * TS), x + (row0 + kn) * n, row_bytes, tab_bar);
+                ptx::bulk_load(ptx::smem_u32(data + (size_t)u * TS + IO), x + (row0 + ks) * n, row_bytes, tab_bar);
+            }
+        }
+    }
     {
-        const int f = f0 + t / VEC, comp = t % VEC;
-        float2 *dst = data + (size_t)t * np;
-        if (f >= nfields) {
-            for (int j = lane; j < n; j += GT) dst[j] = make_float2(0.f, 0.f);
-        } else {
-            const int ks = nlat - 1 - kn;
-            const float *rn = x + ((size_t)(f * VEC + comp) * nlat + kn) * n;
-            const float *rs = x + ((size_t)(f * VEC + comp) * nlat + ks) * n;
-            const bool self = (ks == kn);
-            if ((n % 4 == 0) && vec4ok) {
-                const float4 *rn4 = reinterpret_cast<const float4 *>(rn);
-                const float4 *rs4 = reinterpret_cast<const float4 *>(rs);
-                constexpr int U = 3;  // loads in flight per thread: 2 U float4
-                const int n4 = n / 4;
-                for (int j0 = lane; j0 < n4; j0 += GT * U) {
-                    float4 a[U], b[U];
-#pragma unroll
-                    for (int u = 0; u < U; ++u) {
-                        const int j = j0 + GT * u;
-                        if (j < n4) {
-                            a[u] = __ldg(rn4 + j);
-                            b[u] = self ? make_float4(0.f, 0.f, 0.f, 0.f) : __ldg(rs4 + j);
-                        }
-                    }
-#pragma unroll
-                    for (int u = 0; u < U; ++u) {
-                        const int j = j0 + GT * u;
-                        if (j < n4) {
-                            float4 o = self ? make_float4(0.f, 0.f, 0.f, 0.f) : make_float4(a[u].x - b[u].x, a[u].y - b[u].y, a[u].z - b[u].z, a[u].w - b[u].w);
-                            float4 *d4 = reinterpret_cast<float4 *>(dst + 4 * j);
-                            const float4 c0 = make_float4(a[u].x + b[u].x, o.x, a[u].y + b[u].y, o.y);
-                            const float4 c1 = make_float4(a[u].z + b[u].z, o.z, a[u].w + b[u].w, o.w);
-                            // a thread owns two adjacent 16-byte chunks; lanes 4..7 of every 8 store them in the other
-                            // order so that the 8 lanes of one shared-memory wavefront hit 8 different bank groups
-                            const int sw = (lane >> 2) & 1;
-                            d4[sw] = sw ? c1 : c0;
-                            d4[sw ^ 1] = sw ? c0 : c1;
-                        }
-                    }
-                }
-            } else {
-                for (int j = lane; j < n; j += GT) {
-                    float a = __ldg(rn + j);
-                    float b = self ? 0.f : __ldg(rs + j);
-                    dst[j] = self ? make_float2(a, 0.f) : make_float2(a + b, a - b);
-                }
+        float *re = data + (size_t)t * TS, *im = re + IO;
+        if (t >= nvalid) {
+            for (int j = lane; j < n; j += GT) re[j] = im[j] = 0.f;
+        } else if (!bulk_rows) {  // row starts not 16-byte aligned: plain loads
+            const size_t row0 = (size_t)((f0 + t / VEC) * VEC + t % VEC) * nlat;
+            const float *rn = x + (row0 + kn) * n, *rs = x + (row0 + ks) * n;
+            for (int j = lane; j < n; j += GT) {
+                re[j] = __ldg(rn + j);
+                im[j] = __ldg(rs + j);
             }
         }
     }
     if (!tables_wait(tab_bar, err)) return;  // (CTA-wide barrier: rows in place as well)
 
-    fft_group<false, G>(data + (size_t)t * np, fp, tw_s, lane, 1 + t);
+    {
+        float *re = data + (size_t)t * TS;
+        fft_group<false, G>(CxSplit{re, re + IO}, fp, tw_s, lane, 1 + t);
+    }
     __syncthreads();
 
     // ---- emit the retained orders ----
@@ -673,20 +692,21 @@ __global__ void __launch_bounds__(32 * NW * G, (NW * G >= 16) ? 2 : 1) fft_analy
         const int m = eo_s ? eo_s[i] : i;
         float e[4], o[4];  // (re, im) of the even / odd fold of transforms 2c, 2c+1
         if (m <= nyq) {
-            const float sc = 0.5f * mscale[m];
+            // spectra of the two real rows packed in z = north + i south: A = (z_m + conj z_{n-m}) / 2,
+            // B = (z_m - conj z_{n-m}) / (2 i); even fold = A + B, odd fold = A - B (the equator row counts once)
+            const float sc = (self ? 0.25f : 0.5f) * mscale[m];
             const int pm = perm_s[m];
             const int pn = perm_s[m == 0 ? 0 : n - m];
             const bool edge = zero_imag_edges && (m == 0 || (2 * m == n));
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
-                const float2 *dd = data + (size_t)(2 * c + h) * np;
-                float2 zm = dd[pm];
-                float2 zn = dd[pn];
-                // spectra of the two real rows packed in z = even + i odd
-                e[2 * h] = sc * (zm.x + zn.x);
-                e[2 * h + 1] = edge ? 0.f : sc * (zm.y - zn.y);
-                o[2 * h] = sc * (zm.y + zn.y);
-                o[2 * h + 1] = edge ? 0.f : sc * (zn.x - zm.x);
+                const float *dre = data + (size_t)(2 * c + h) * TS, *dim = dre + IO;
+                const float zmx = dre[pm], zmy = dim[pm], znx = dre[pn], zny = dim[pn];
+                const float ar = zmx + znx, ai = zmy - zny, br = zmy + zny, bi = znx - zmx;
+                e[2 * h] = sc * (ar + br);
+                e[2 * h + 1] = edge ? 0.f : sc * (ai + bi);
+                o[2 * h] = sc * (ar - br);
+                o[2 * h + 1] = edge ? 0.f : sc * (ai - bi);
             }
         } else {
 #pragma unroll
@@ -729,9 +749,9 @@ __global__ void __launch_bounds__(32 * NW * G, (NW * G >= 16) ? 2 : 1) fft_synth
     const int n = fp.n;
     constexpr int NF = NW / VEC;
     constexpr int GT = 32 * G;
-    const int np = n + kPad;
+    const int np = fp.np;
     float2 *data = smem;
-    float2 *tw_s = reinterpret_cast<float2 *>(reinterpret_cast<unsigned char *>(smem) + data_bytes(NW, n));
+    float2 *tw_s = data + (size_t)NW * np;
     const unsigned short *perm_s = reinterpret_cast<const unsigned short *>(reinterpret_cast<const unsigned *>(tw_s + fp.tw_pass_total) + fp.bf_total);
 
     const int kn = blockIdx.y;
@@ -788,7 +808,7 @@ __global__ void __launch_bounds__(32 * NW * G, (NW * G >= 16) ? 2 : 1) fft_synth
     }
     __syncthreads();
 
-    fft_group<true, G>(data + (size_t)t * np, fp, tw_s, lane, 1 + t);
+    fft_group<true, G>(CxPacked{data + (size_t)t * np}, fp, tw_s, lane, 1 + t);
 
     // ---- each group stores its own pair of rows ----
     {
@@ -841,7 +861,7 @@ __global__ void __launch_bounds__(32 * NW) rfft_rows_kernel(const float *__restr
         }
     }
     __syncthreads();
-    fft_group<false, 1>(data + (size_t)warp * n, fp, tw_s, lane, 0);
+    fft_group<false, 1>(CxPacked{data + (size_t)warp * n}, fp, tw_s, lane, 0);
     const int nyq = n / 2;
     {
         const long long ra = r0 + 2 * warp, rb = ra + 1;
@@ -887,7 +907,7 @@ __global__ void __launch_bounds__(32 * NW) irfft_rows_kernel(const float2 *__res
         }
     }
     __syncwarp();
-    fft_group<true, 1>(dd, fp, tw_s, lane, 0);
+    fft_group<true, 1>(CxPacked{dd}, fp, tw_s, lane, 0);
     for (int j = lane; j < n; j += 32) {
         if (ra < nrows) out[ra * n + j] = dd[j].x;
         if (rb < nrows) out[rb * n + j] = dd[j].y;
@@ -898,7 +918,8 @@ __global__ void __launch_bounds__(32 * NW) irfft_rows_kernel(const float2 *__res
 // launchers
 // ------------------------------------------------------------------------------------------------
 static size_t fft_smem_bytes(int nffts, const FftPlanDev &fp) {
-    return ((size_t)nffts * (fp.n + kPad) * sizeof(float2) + 15) / 16 * 16 + (size_t)fp.tab_bytes + 16;
+    const size_t data = fp.ts ? (size_t)nffts * fp.ts * sizeof(float) : (size_t)nffts * fp.np * sizeof(float2);
+    return data + (size_t)fp.tab_bytes + 16;
 }
 
 template <typename K>
@@ -924,7 +945,7 @@ int launch_fft_analysis(const Plan &pl, const float *x, float *X, int nfields, c
     // one CTA row per latitude pair plus the zero rows that pad the contraction length to a multiple of 32
     dim3 grid(ceil_div(nfields, NW / vec), pl.Kh + (int)(round_up(pl.Ka, kBK) - pl.Ka));
     size_t smem = fft_smem_bytes(NW, pl.fft);
-    const int al = (int)(((uintptr_t)x & 15) == 0);
+    const int al = (int)((((uintptr_t)x & 15) == 0) && (pl.fft.n % 4 == 0));
     int rc;
 #define LAUNCH_A(WW, VV)                                                                                                                    \
     do {                                                                                                                                    \
@@ -951,7 +972,7 @@ int launch_fft_synthesis(const Plan &pl, const float *Y, float *x, int nfields, 
     const int ncp = (int)col_pitch((pl.vector ? 4 : 2) * nfields);
     dim3 grid(ceil_div(nfields, NW / vec), pl.Kh);
     size_t smem = fft_smem_bytes(NW, pl.fft);
-    const int al = (int)(((uintptr_t)x & 15) == 0);
+    const int al = (int)((((uintptr_t)x & 15) == 0) && (pl.fft.n % 4 == 0));
     int rc;
 #define LAUNCH_S(WW, VV)                                                                                                                 \
     do {                                                                                                                                 \
@@ -988,7 +1009,7 @@ static int cached_fft(int nlon, FftPlanDev *fp) {
         if (c.n == nlon && c.device == dev) { *fp = c.fp; return SHTB200_OK; }
     for (auto &c : g_cache)
         if (c.n == 0) {
-            int rc = build_fft_plan(nlon, 0, &c.fp, &c.tw, &c.perm);
+            int rc = build_fft_plan(nlon, 0, kFftRows, &c.fp, &c.tw, &c.perm);
             if (rc) return rc;
             c.n = nlon;
             c.device = dev;

@@ -261,6 +261,14 @@ int shtb200_plan_create(shtb200_plan **plan_out, int kind, int nlat, int nlon, i
             int cnt = lmax - m - p;
             pl->group_rows[2 * m + p] = cnt > 0 ? (cnt + 1) / 2 : 0;
         }
+    // Polar extent of every group, in whole 32-row blocks.  The cut-off is far below what fp32 keeps next to the
+    // largest entry of the same degree, so the result is the one the full contraction would give.
+    pl->group_krow0.assign(ngroups, 0);
+    if (kind == SHTB200_SHT || kind == SHTB200_ISHT) {
+        std::vector<int> first;
+        if ((rc = launch_polar_extent(*pl, table_dev, 1e-14f, &first))) { shtb200_plan_destroy(pl); return rc; }
+        for (int g = 0; g < ngroups; ++g) pl->group_krow0[g] = std::min(first[g], std::max(pl->Kh - 1, 0)) / kBK * kBK;
+    }
     pl->group_a0.assign(ngroups + 1, 0);
     pl->group_kblocks.assign(ngroups, 0);
     pl->group_b0.assign(ngroups + 1, 0);
@@ -285,7 +293,8 @@ int shtb200_plan_create(shtb200_plan **plan_out, int kind, int nlat, int nlon, i
                 it.a_dy = 0;
                 it.b_y0 = g;
                 it.b_dy = 0;
-                it.kblocks = kblocks;
+                it.kfirst = pl->group_krow0[g] / kBK;
+                it.kblocks = kblocks - it.kfirst;
                 it.rows = std::min(kItemRowsMax, pl->group_rows[g] - r0);
                 it.m = g >> 1;
                 it.p = g & 1;
@@ -310,7 +319,7 @@ int shtb200_plan_create(shtb200_plan **plan_out, int kind, int nlat, int nlon, i
         pl->table_floats = (size_t)(pl->group_a0[ngroups] + kItemRowsMax) * kBK;
         for (int g = 0; g < ngroups; ++g) {
             if (pl->group_kblocks[g] == 0) continue;
-            for (int r0 = 0; r0 < pl->Kh; r0 += kItemRowsMax) {
+            for (int r0 = pl->group_krow0[g]; r0 < pl->Kh; r0 += kItemRowsMax) {
                 GemmItem it{};
                 it.a_y0 = (int)(pl->group_a0[g] + r0);
                 it.a_dy = pl->Kh;
@@ -340,7 +349,8 @@ int shtb200_plan_create(shtb200_plan **plan_out, int kind, int nlat, int nlon, i
     }
 
     if ((rc = upload(&pl->d_items, pl->items)) || (rc = upload(&pl->d_ga0, pl->group_a0)) || (rc = upload(&pl->d_gb0, pl->group_b0)) ||
-        (rc = upload(&pl->d_grows, pl->group_rows)) || (rc = upload(&pl->d_gkb, pl->group_kblocks)) || (rc = upload(&pl->d_gkb0, kb0))) {
+        (rc = upload(&pl->d_grows, pl->group_rows)) || (rc = upload(&pl->d_gkb, pl->group_kblocks)) || (rc = upload(&pl->d_gkb0, kb0)) ||
+        (rc = upload(&pl->d_krow0, pl->group_krow0))) {
         shtb200_plan_destroy(pl);
         return rc;
     }
@@ -372,6 +382,7 @@ int shtb200_plan_destroy(shtb200_plan *pl) {
     cudaFree(pl->stage_in);
     cudaFree(pl->stage_out);
     cudaFree(pl->stage_ws);
+    cudaFree(pl->d_krow0);
     cudaFree(pl->d_err);
     for (auto &e : pl->ev)
         if (e) cudaEventDestroy(e);

@@ -78,7 +78,7 @@ struct GemmItem {
     int m;         // spherical harmonic order
     int p;         // parity of l - m handled by this group (0 / 1)
     int r0;        // index of the item's first row inside its group
-    int pad;
+    int kfirst;    // contraction slices skipped at the front of this group: slice i of the item is slice kfirst + i of the operands
 };
 constexpr int kItemRowsMax = 128;  // one 128-row tensor-core tile
 
@@ -157,6 +157,11 @@ struct Plan {
     size_t stage_in_bytes = 0, stage_out_bytes = 0, stage_ws_bytes = 0;
 
     int last_launches = 0;
+    // First folded latitude row (a multiple of 32) of each group that the contraction touches: towards the pole the
+    // associated Legendre functions of high order vanish faster than fp32 can represent next to the row's largest value
+    // (see launch_polar_extent), so analysis never reads the operand rows above it and synthesis never writes them.
+    std::vector<int> group_krow0;
+    int *d_krow0 = nullptr;
     int *d_err = nullptr;             // device error word raised by kernels whose bounded waits ran out
 
     // optional per-kernel timing (cudaEvents recorded between the launches of one execute call)
@@ -186,11 +191,14 @@ bool gemm_tc_supported(const Plan &pl, const GemmParams &gp);
 
 // table / operand packing
 int launch_pack_table(Plan &pl, const float *table, cudaStream_t st);
+// first_row[2 m + p] = first folded latitude k' at which any degree l = m + p + 2 r of the dense table reaches `rel` times
+// that degree's largest magnitude over all latitudes (Kh if none does)
+int launch_polar_extent(const Plan &pl, const float *table, float rel, std::vector<int> *first_row);
 int launch_pack_coeffs(const Plan &pl, const float2 *c, float *Ct, int nfields, int m0, int mloc, cudaStream_t st);
 int launch_unpack_coeffs(const Plan &pl, const float *Z, float2 *c, int nfields, int m0, int mloc, cudaStream_t st);
 int launch_zero_upper(const Plan &pl, float2 *c, int nfields, int m0, int mloc, cudaStream_t st);
 int launch_fold_modes(const Plan &pl, const float2 *Xc, float *X, int nfields, int m0, int mloc, cudaStream_t st);
-int launch_unfold_modes(const Plan &pl, const float *Y, float2 *Xc, int nfields, int m0, int mloc, cudaStream_t st);
+int launch_unfold_modes(const Plan &pl, const float *Y, float2 *Xc, int nfields, int m0, int mloc, cudaStream_t st);  // honours group_krow0
 
 // Row of (group, k) in the column-contiguous operands X and Y: 32-row blocks of k are outermost, then the group,
 // then k inside the block.  CTAs of the FFT kernels that run at the same time work on neighbouring k for ALL groups,

@@ -615,7 +615,7 @@ __device__ __forceinline__ bool tables_wait(uint32_t bar, int *err) {
 template <int NW, int VEC, int G>
 __global__ void __launch_bounds__(32 * NW * G, (NW * G >= 16) ? 2 : 1) fft_analysis_kernel(const float *__restrict__ x, float *__restrict__ X, FftPlanDev fp,
                                                                                             int nlat, int Kh, int nfields, int ncp, int mmax,
-                                                                                            const float *__restrict__ mscale, int zero_imag_edges, int bulk_rows, int *err) {
+                                                                                            const float *__restrict__ mscale, const int *__restrict__ krow0, int zero_imag_edges, int bulk_rows, int *err) {
     extern __shared__ __align__(16) float smem_f[];
     const int n = fp.n;
     constexpr int NF = NW / VEC;                    // fields (or component pairs) per CTA
@@ -716,8 +716,9 @@ __global__ void __launch_bounds__(32 * NW * G, (NW * G >= 16) ? 2 : 1) fft_analy
             // columns 2 (f0 + 2c), ..: (re, im) of two consecutive fields
             const int col = 2 * f0 + 4 * c;
             if (col < ncp) {
-                *reinterpret_cast<float4 *>(X + (size_t)blocked_row(2 * m, kn, ngroups) * ncp + col) = make_float4(e[0], e[1], e[2], e[3]);
-                *reinterpret_cast<float4 *>(X + (size_t)blocked_row(2 * m + 1, kn, ngroups) * ncp + col) = make_float4(o[0], o[1], o[2], o[3]);
+                // (the contraction does not read rows above the group's polar extent)
+                if (kn >= krow0[2 * m]) *reinterpret_cast<float4 *>(X + (size_t)blocked_row(2 * m, kn, ngroups) * ncp + col) = make_float4(e[0], e[1], e[2], e[3]);
+                if (kn >= krow0[2 * m + 1]) *reinterpret_cast<float4 *>(X + (size_t)blocked_row(2 * m + 1, kn, ngroups) * ncp + col) = make_float4(o[0], o[1], o[2], o[3]);
             }
         } else {
             // transforms 2c (theta component X0) and 2c + 1 (phi component X1) of pair f0 + c: four columns 4 (f0 + c)..
@@ -744,7 +745,7 @@ __global__ void __launch_bounds__(32 * NW * G, (NW * G >= 16) ? 2 : 1) fft_analy
 template <int NW, int VEC, int G>
 __global__ void __launch_bounds__(32 * NW * G, (NW * G >= 16) ? 2 : 1) fft_synthesis_kernel(const float *__restrict__ Y, float *__restrict__ x, FftPlanDev fp,
                                                                                              int nlat, int Kh, int nfields, int ncp, int mmax,
-                                                                                             const float *__restrict__ mscale, int vec4ok, int *err) {
+                                                                                             const float *__restrict__ mscale, const int *__restrict__ krow0, int vec4ok, int *err) {
     extern __shared__ float2 smem[];
     const int n = fp.n;
     constexpr int NF = NW / VEC;
@@ -783,8 +784,9 @@ __global__ void __launch_bounds__(32 * NW * G, (NW * G >= 16) ? 2 : 1) fft_synth
             if (m >= mtop) continue;
             float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
             if (col < ncp) {
-                a = *reinterpret_cast<const float4 *>(Y + (size_t)blocked_row(2 * m, kn, 2 * mmax) * ncp + col);
-                b = *reinterpret_cast<const float4 *>(Y + (size_t)blocked_row(2 * m + 1, kn, 2 * mmax) * ncp + col);
+                // (the contraction does not produce rows above the group's polar extent: they are zeros)
+                if (kn >= krow0[2 * m]) a = *reinterpret_cast<const float4 *>(Y + (size_t)blocked_row(2 * m, kn, 2 * mmax) * ncp + col);
+                if (kn >= krow0[2 * m + 1]) b = *reinterpret_cast<const float4 *>(Y + (size_t)blocked_row(2 * m + 1, kn, 2 * mmax) * ncp + col);
             }
             const float sc = mscale[m];
             const bool edge = (m == 0) || (2 * m == n);
@@ -951,7 +953,7 @@ int launch_fft_analysis(const Plan &pl, const float *x, float *X, int nfields, c
     do {                                                                                                                                    \
         if ((rc = set_smem(fft_analysis_kernel<WW, VV, kGroupWarps>, smem)) != 0) return rc;                                                \
         fft_analysis_kernel<WW, VV, kGroupWarps><<<grid, 32 * WW * kGroupWarps, smem, st>>>(x, X, pl.fft, pl.nlat, pl.Kh, nfields, ncp,     \
-                                                                                            pl.mmax, pl.d_mscale, pl.zero_imag_edges, al, pl.d_err); \
+                                                                                            pl.mmax, pl.d_mscale, pl.d_krow0, pl.zero_imag_edges, al, pl.d_err); \
     } while (0)
     if (vec == 1) {
         if (NW == 8) LAUNCH_A(8, 1);
@@ -978,7 +980,7 @@ int launch_fft_synthesis(const Plan &pl, const float *Y, float *x, int nfields, 
     do {                                                                                                                                 \
         if ((rc = set_smem(fft_synthesis_kernel<WW, VV, kGroupWarps>, smem)) != 0) return rc;                                            \
         fft_synthesis_kernel<WW, VV, kGroupWarps><<<grid, 32 * WW * kGroupWarps, smem, st>>>(Y, x, pl.fft, pl.nlat, pl.Kh, nfields, ncp, \
-                                                                                             pl.mmax, pl.d_mscale, al, pl.d_err);       \
+                                                                                             pl.mmax, pl.d_mscale, pl.d_krow0, al, pl.d_err); \
     } while (0)
     if (vec == 1) {
         if (NW == 8) LAUNCH_S(8, 1);

@@ -40,7 +40,8 @@ __global__ void __launch_bounds__(256) legendre_simt_kernel(GemmParams gp) {
     const int K = it.kblocks * kBK;
     const long long b_y0 = ((long long)it.b_y0 - gp.b_unit0) * gp.ncols;
     const int b_dy = it.b_dy * gp.ncols;
-    for (int k0 = 0; k0 < K; k0 += TK) {
+    const int kbase = it.kfirst * kBK;  // slices skipped at the front of the group
+    for (int k0 = kbase; k0 < kbase + K; k0 += TK) {
         // 64 x 16 elements per operand, 256 threads: 4 each; consecutive threads walk k (contiguous in memory)
         for (int e = threadIdx.x; e < TM * TK; e += 256) {
             const int kk = e % TK, r = e / TK;

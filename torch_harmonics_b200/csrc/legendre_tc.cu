@@ -114,7 +114,7 @@ legendre_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         w.it = gp.items[u / P.ntiles];
         w.ntile = u % P.ntiles;
         w.ksteps = w.it.kblocks;
-        if (row_packed_a && w.ksteps > P.ksteps_cap) w.ksteps = P.ksteps_cap;
+        if (row_packed_a && w.ksteps > P.ksteps_cap - w.it.kfirst) w.ksteps = P.ksteps_cap - w.it.kfirst;
         w.skip = (w.it.m < gp.m0) || (w.it.m >= gp.m0 + gp.mmax_out);
         return w;
     };
@@ -131,7 +131,8 @@ legendre_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                 if (w.skip) continue;
                 const long long by0 = gp.b_mn ? ((long long)w.it.b_y0 - gp.b_unit0) * TK  // 32-row block of this group inside a k-step
                                               : ((long long)w.it.b_y0 - gp.b_unit0) * gp.ncols + (long long)w.ntile * P.bn;
-                for (int ks = 0; ks < w.ksteps; ++ks) {
+                for (int ki = 0; ki < w.ksteps; ++ki) {
+                    const int ks = ki + w.it.kfirst;  // slice of the operands
                     if (!(ok = ptx::mbar_wait_bounded(bar_empty(s), ph ^ 1u, abort_flag, WAIT_LIMIT))) break;
                     ptx::mbar_arrive_expect_tx(bar_full(s), bytes);
                     const uint32_t dst = stage0 + s * STAGE_BYTES;

@@ -9,6 +9,8 @@
 //                     dense table, torch_harmonics/legendre.py:77-78).
 //  * fold / unfold  : distributed stages: plain complex (field, k, m) <-> folded order-major operand.
 
+#include <string>
+
 #include "common.cuh"
 
 namespace shtb200 {
@@ -24,6 +26,29 @@ struct TableView {
         return mkl ? t[base + ((size_t)m * nlat + k) * lmax + l] : t[base + ((size_t)m * lmax + l) * nlat + k];
     }
 };
+
+// One CTA per order m, one warp per degree l at a time: the degree's largest magnitude over the northern latitudes, then
+// the first latitude that reaches rel times it; the minimum over the degrees of each parity is the group's answer.
+__global__ void polar_extent_kernel(TableView tv, int Kh, float rel, int *first_row) {
+    const int m = blockIdx.x;
+    __shared__ int s_first[2];
+    if (threadIdx.x < 2) s_first[threadIdx.x] = Kh;
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    for (int l = m + warp; l < tv.lmax; l += nwarps) {
+        float mx = 0.f;
+        for (int k = lane; k < Kh; k += 32) mx = fmaxf(mx, fabsf(tv.at(0, m, l, k)));
+        for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        int first = Kh;
+        if (mx > 0.f)
+            for (int k = lane; k < Kh && first == Kh; k += 32)
+                if (fabsf(tv.at(0, m, l, k)) >= rel * mx) first = k;
+        for (int o = 16; o; o >>= 1) first = min(first, __shfl_xor_sync(0xffffffffu, first, o));
+        if (lane == 0) atomicMin(&s_first[(l - m) & 1], first);
+    }
+    __syncthreads();
+    if (threadIdx.x < 2) first_row[2 * m + threadIdx.x] = s_first[threadIdx.x];
+}
 
 // rows = degrees, contraction index = folded latitude (row-packed): A[a0[g] + r][seg * Kh + k'], zero beyond
 __global__ void pack_table_rows_kernel(TableView tv, float *A, const long long *a0, const int *grows, int ngroups, int ncomp, int Kh, int pitch, int negate_seg1) {
@@ -222,15 +247,17 @@ __global__ void fold_modes_kernel(const float2 *__restrict__ Xc, float *__restri
 }
 
 // Y[blocked_row(2 mi + p, k')][2 f + ri] -> Xc (field, k, mloc) complex
-__global__ void unfold_modes_kernel(const float *__restrict__ Y, float2 *__restrict__ Xc, int nfields, int nlat, int Kh, int ncp, int mloc) {
+// (rows above krow0[2 (m0 + mi) + p] were not produced by the contraction: they count as zeros)
+__global__ void unfold_modes_kernel(const float *__restrict__ Y, float2 *__restrict__ Xc, int nfields, int nlat, int Kh, int ncp, int mloc, const int *__restrict__ krow0, int m0) {
     const long long total = (long long)nfields * Kh * mloc;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         const int mi = (int)(i % mloc);
         const long long t = i / mloc;
         const int k = (int)(t % Kh);
         const int f = (int)(t / Kh);
-        const float2 e = *reinterpret_cast<const float2 *>(Y + (size_t)blocked_row(2 * mi, k, 2 * mloc) * ncp + 2 * f);
-        const float2 o = *reinterpret_cast<const float2 *>(Y + (size_t)blocked_row(2 * mi + 1, k, 2 * mloc) * ncp + 2 * f);
+        float2 e = make_float2(0.f, 0.f), o = e;
+        if (k >= krow0[2 * (m0 + mi)]) e = *reinterpret_cast<const float2 *>(Y + (size_t)blocked_row(2 * mi, k, 2 * mloc) * ncp + 2 * f);
+        if (k >= krow0[2 * (m0 + mi) + 1]) o = *reinterpret_cast<const float2 *>(Y + (size_t)blocked_row(2 * mi + 1, k, 2 * mloc) * ncp + 2 * f);
         const int ks = nlat - 1 - k;
         Xc[((size_t)f * nlat + k) * mloc + mi] = make_float2(e.x + o.x, e.y + o.y);
         if (ks != k) Xc[((size_t)f * nlat + ks) * mloc + mi] = make_float2(e.x - o.x, e.y - o.y);
@@ -259,6 +286,22 @@ int launch_pack_table(Plan &pl, const float *table, cudaStream_t st) {
     }
     SHT_CUDA_CHECK(cudaGetLastError());
     SHT_CUDA_CHECK(cudaStreamSynchronize(st));
+    return SHTB200_OK;
+}
+
+int launch_polar_extent(const Plan &pl, const float *table, float rel, std::vector<int> *first_row) {
+    const int ngroups = 2 * pl.mmax;
+    first_row->assign(ngroups, 0);
+    if (pl.mmax == 0) return SHTB200_OK;
+    TableView tv{table, pl.mmax, pl.lmax, pl.nlat, 0};
+    tv.mkl = (pl.kind == SHTB200_ISHT || pl.kind == SHTB200_ISHT_ADJOINT || pl.kind == SHTB200_IVSHT || pl.kind == SHTB200_IVSHT_ADJOINT) ? 1 : 0;
+    int *d = nullptr;
+    SHT_CUDA_CHECK(cudaMalloc(&d, sizeof(int) * ngroups));
+    polar_extent_kernel<<<pl.mmax, 256>>>(tv, pl.Kh, rel, d);
+    cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) e = cudaMemcpy(first_row->data(), d, sizeof(int) * ngroups, cudaMemcpyDeviceToHost);
+    cudaFree(d);
+    if (e != cudaSuccess) return fail(SHTB200_ECUDA, std::string("polar extent: ") + cudaGetErrorString(e));
     return SHTB200_OK;
 }
 
@@ -307,11 +350,10 @@ int launch_fold_modes(const Plan &pl, const float2 *Xc, float *X, int nfields, i
 }
 
 int launch_unfold_modes(const Plan &pl, const float *Y, float2 *Xc, int nfields, int m0, int mloc, cudaStream_t st) {
-    (void)m0;
     if (pl.vector) return fail(SHTB200_EINVAL, "stage-wise Legendre entry point supports the scalar kinds only");
     const long long total = (long long)nfields * pl.Kh * mloc;
     if (total == 0) return SHTB200_OK;
-    unfold_modes_kernel<<<grid_x_for(total), 256, 0, st>>>(Y, Xc, nfields, pl.nlat, pl.Kh, (int)col_pitch(2 * nfields), mloc);
+    unfold_modes_kernel<<<grid_x_for(total), 256, 0, st>>>(Y, Xc, nfields, pl.nlat, pl.Kh, (int)col_pitch(2 * nfields), mloc, pl.d_krow0, m0);
     SHT_CUDA_CHECK(cudaGetLastError());
     return SHTB200_OK;
 }

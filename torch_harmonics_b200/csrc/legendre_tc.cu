@@ -7,13 +7,16 @@
 //
 //   warp 0      TMA producer: cp.async.bulk.tensor loads of one 128 x 32 A tile and one B tile per k-step into a
 //               4-deep ring of 128-byte-swizzled shared-memory stages (full/empty mbarriers).
-//   warps 2-9   splitter: for each landed stage compute lo = x - tf32_trunc(x) for A and B into one of two "lo"
-//               slots (same swizzled layout, so the pass is a straight elementwise sweep).
+//   warps 2-5   A splitter, one warp per tensor-memory lane quarter: a thread reads its row of the landed A tile and
+//               stores it twice into a 3-deep ring in TENSOR MEMORY, as it is and as lo = x - tf32_trunc(x)
+//               (tcgen05.st), so the table never occupies shared-memory bandwidth again: the MMAs take A from there.
+//   warps 6-9   B splitter: lo = x - tf32_trunc(x) of the B tile into one of three shared-memory "lo" slots (same
+//               swizzled layout, so the pass is a straight elementwise sweep).
 //   warp 1      MMA issuer: per k-step three tcgen05.mma chains (A_lo B, A B_lo, A B; the tensor core reads
-//               fp32 words as TF32 by dropping the low mantissa bits), fp32 accumulation in one of three
-//               tensor-memory accumulators; tcgen05.commit releases stages, lo slots and accumulators.
+//               fp32 words as TF32 by dropping the low mantissa bits), fp32 accumulation in one of two
+//               tensor-memory accumulators; tcgen05.commit releases stages, lo slots, A slots and accumulators.
 //   warps 10-17 epilogue: tcgen05.ld of a finished accumulator while the next units are being multiplied,
-//               direct stores to the coefficient array (analysis) or the latitude-row operand of the
+//               stores to the degree-slab array / coefficient array (analysis) or the latitude-row operand of the
 //               synthesis FFT.
 //
 // Every mbarrier wait is bounded: when one runs out the CTA raises a device error word and unwinds.
@@ -36,20 +39,23 @@ constexpr int TK = kBK;                // floats per k-step: one 128-byte swizzl
 constexpr int TILE_M = 128;
 constexpr int BN_MAX = 160;
 constexpr int NSTAGE = 4;              // TMA ring
-constexpr int NLO = 2;                 // slots for the low-order parts
-constexpr int NACC = 3;                // accumulator buffers in tensor memory
+constexpr int NLO = 3;                 // shared-memory slots for the low-order part of B
+constexpr int NACC = 2;                // accumulator buffers in tensor memory
+constexpr int NATM = 3;                // A slots in tensor memory (raw + lo: 2 x 32 columns each)
 constexpr int A_TILE_BYTES = TILE_M * TK * 4;                // 16 KiB
-constexpr int STAGE_BYTES = A_TILE_BYTES + BN_MAX * TK * 4;  // 36 KiB
+constexpr int B_TILE_BYTES = BN_MAX * TK * 4;                // 20 KiB
+constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;     // 36 KiB
 constexpr int B_OFF = A_TILE_BYTES;
 constexpr int B_BLK_BYTES = 32 * TK * 4;  // column-contiguous B: one 32 (k) x 32 (columns) block, 4 KiB
 constexpr int TMEM_COLS = 512;
-constexpr int NSPLIT_WARPS = 8, NEPI_WARPS = 8;
+constexpr int A_TM_COL0 = NACC * BN_MAX;  // first tensor-memory column of the A ring
+constexpr int NSPLIT_A = 4, NSPLIT_B = 4, NSPLIT_WARPS = NSPLIT_A + NSPLIT_B, NEPI_WARPS = 8;
 constexpr int NTHREADS = 32 * (2 + NSPLIT_WARPS + NEPI_WARPS);  // 576
 constexpr long long WAIT_LIMIT = 4000000000LL;                  // ~2 s of SM clock
 
-constexpr int NBARS = 2 * NSTAGE + 2 * NLO + 2 * NACC;
-constexpr int SMEM_BYTES = (NSTAGE + NLO) * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
-static_assert(NACC * BN_MAX <= TMEM_COLS, "accumulators must fit tensor memory");
+constexpr int NBARS = 2 * NSTAGE + 2 * NLO + 2 * NACC + 2 * NATM;
+constexpr int SMEM_BYTES = NSTAGE * STAGE_BYTES + NLO * B_TILE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+static_assert(NACC * BN_MAX + NATM * 2 * TK <= TMEM_COLS, "accumulators and the A ring must fit tensor memory");
 static_assert(kItemRowsMax == TILE_M, "one work item = one 128-row tensor-core tile");
 
 struct TcParams {
@@ -73,7 +79,7 @@ legendre_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     uint8_t *base_ptr = smem_raw + (base - ptx::smem_u32(smem_raw));
     const uint32_t stage0 = base;
     const uint32_t lo0 = base + NSTAGE * STAGE_BYTES;
-    const uint32_t bar0 = base + (NSTAGE + NLO) * STAGE_BYTES;
+    const uint32_t bar0 = lo0 + NLO * B_TILE_BYTES;
     // barrier slots (8 bytes each)
     auto bar_full = [&](int s) { return bar0 + 8u * s; };
     auto bar_empty = [&](int s) { return bar0 + 8u * (NSTAGE + s); };
@@ -81,7 +87,9 @@ legendre_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     auto bar_loempty = [&](int c) { return bar0 + 8u * (2 * NSTAGE + NLO + c); };
     auto bar_accfull = [&](int a) { return bar0 + 8u * (2 * NSTAGE + 2 * NLO + a); };
     auto bar_accempty = [&](int a) { return bar0 + 8u * (2 * NSTAGE + 2 * NLO + NACC + a); };
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(base_ptr + (NSTAGE + NLO) * STAGE_BYTES + 8 * NBARS);
+    auto bar_afull = [&](int t) { return bar0 + 8u * (2 * NSTAGE + 2 * NLO + 2 * NACC + t); };
+    auto bar_aempty = [&](int t) { return bar0 + 8u * (2 * NSTAGE + 2 * NLO + 2 * NACC + NATM + t); };
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(base_ptr + NSTAGE * STAGE_BYTES + NLO * B_TILE_BYTES + 8 * NBARS);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -89,7 +97,8 @@ legendre_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < NSTAGE; ++s) { ptx::mbar_init(bar_full(s), 1); ptx::mbar_init(bar_empty(s), 1); }
-        for (int c = 0; c < NLO; ++c) { ptx::mbar_init(bar_lofull(c), 32 * NSPLIT_WARPS); ptx::mbar_init(bar_loempty(c), 1); }
+        for (int c = 0; c < NLO; ++c) { ptx::mbar_init(bar_lofull(c), 32 * NSPLIT_B); ptx::mbar_init(bar_loempty(c), 1); }
+        for (int t = 0; t < NATM; ++t) { ptx::mbar_init(bar_afull(t), 32 * NSPLIT_A); ptx::mbar_init(bar_aempty(t), 1); }
         for (int a = 0; a < NACC; ++a) { ptx::mbar_init(bar_accfull(a), 1); ptx::mbar_init(bar_accempty(a), 32 * NEPI_WARPS); }
         *abort_flag = 0;
         ptx::fence_barrier_init();
@@ -152,8 +161,8 @@ legendre_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     } else if (warp == 1) {
         // =========================== MMA issuer ===========================
         if (lane == 0) {
-            int s = 0, c = 0, a = 0;
-            uint32_t ph = 0, phc = 0, pha = 0;
+            int s = 0, c = 0, a = 0, t = 0;
+            uint32_t ph = 0, phc = 0, pha = 0, pht = 0;
             bool ok = true;
             const uint32_t idesc = ptx::idesc_tf32_m128((uint32_t)P.bn) | (gp.b_mn ? (1u << 16) : 0u);  // bit 16: B is column (MN) major
             for (int u = blockIdx.x; u < P.nunits && ok; u += gridDim.x) {
@@ -166,59 +175,97 @@ legendre_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                 for (int ks = 0; ks < w.ksteps; ++ks) {
                     if (!(ok = ptx::mbar_wait_bounded(bar_full(s), ph, abort_flag, WAIT_LIMIT))) break;
                     if (!(ok = ptx::mbar_wait_bounded(bar_lofull(c), phc, abort_flag, WAIT_LIMIT))) break;
+                    if (!(ok = ptx::mbar_wait_bounded(bar_afull(t), pht, abort_flag, WAIT_LIMIT))) break;
                     ptx::tc_fence_after();
-                    const uint32_t hi = stage0 + s * STAGE_BYTES, lo = lo0 + c * STAGE_BYTES;
-                    const uint64_t ah = ptx::smem_desc_sw128(hi), al = ptx::smem_desc_sw128(lo);
+                    const uint32_t hi = stage0 + s * STAGE_BYTES, lo = lo0 + c * B_TILE_BYTES;
+                    const uint32_t ah = tmem_base + (uint32_t)(A_TM_COL0 + t * 2 * TK), al = ah + TK;  // A as it is / its low part
                     const uint64_t bh = gp.b_mn ? ptx::smem_desc_sw128_mn(hi + B_OFF, B_BLK_BYTES) : ptx::smem_desc_sw128(hi + B_OFF);
-                    const uint64_t bl = gp.b_mn ? ptx::smem_desc_sw128_mn(lo + B_OFF, B_BLK_BYTES) : ptx::smem_desc_sw128(lo + B_OFF);
-                    // one MMA consumes 8 contraction indices: 32 bytes along a K-major row, one 8-row (1 KiB) group of a column-major tile
+                    const uint64_t bl = gp.b_mn ? ptx::smem_desc_sw128_mn(lo, B_BLK_BYTES) : ptx::smem_desc_sw128(lo);
+                    // one MMA consumes 8 contraction indices: 8 columns of A in tensor memory; of B 32 bytes along a K-major row or
+                    // one 8-row (1 KiB) group of a column-major tile
                     const uint64_t bstep = gp.b_mn ? (uint64_t)(1024 >> 4) : (uint64_t)(32 >> 4);
 #pragma unroll
                     for (int k8 = 0; k8 < TK / 8; ++k8) {
-                        const uint64_t koff = (uint64_t)((k8 * 32) >> 4), kb = bstep * k8;
-                        ptx::mma_tf32(d, al + koff, bh + kb, idesc, (ks | k8) ? 1u : 0u);  // small terms first
-                        ptx::mma_tf32(d, ah + koff, bl + kb, idesc, 1u);
-                        ptx::mma_tf32(d, ah + koff, bh + kb, idesc, 1u);
+                        const uint32_t koff = (uint32_t)(k8 * 8);
+                        const uint64_t kb = bstep * k8;
+                        ptx::mma_tf32_ta(d, al + koff, bh + kb, idesc, (ks | k8) ? 1u : 0u);  // small terms first
+                        ptx::mma_tf32_ta(d, ah + koff, bl + kb, idesc, 1u);
+                        ptx::mma_tf32_ta(d, ah + koff, bh + kb, idesc, 1u);
                     }
                     ptx::tc_commit(bar_empty(s));
                     ptx::tc_commit(bar_loempty(c));
+                    ptx::tc_commit(bar_aempty(t));
                     if (++s == NSTAGE) { s = 0; ph ^= 1u; }
                     if (++c == NLO) { c = 0; phc ^= 1u; }
+                    if (++t == NATM) { t = 0; pht ^= 1u; }
                 }
                 if (!ok) break;
                 ptx::tc_commit(bar_accfull(a));
                 if (++a == NACC) { a = 0; pha ^= 1u; }
             }
         }
+    } else if (warp < 2 + NSPLIT_A) {
+        // =========================== A splitter: shared memory -> tensor memory ===========================
+        const int q = warp & 3;              // tensor-memory lane quarter this warp may write
+        const int row = q * 32 + lane;       // row of the A tile = lane of tensor memory
+        int s = 0, t = 0;
+        uint32_t ph = 0, pht = 0;
+        bool ok = true;
+        for (int u = blockIdx.x; u < P.nunits && ok; u += gridDim.x) {
+            const Unit w = get_unit(u);
+            if (w.skip) continue;
+            for (int ks = 0; ks < w.ksteps; ++ks) {
+                if (!(ok = ptx::mbar_wait_bounded(bar_full(s), ph, abort_flag, WAIT_LIMIT))) break;
+                if (!(ok = ptx::mbar_wait_bounded(bar_aempty(t), pht ^ 1u, abort_flag, WAIT_LIMIT))) break;
+                ptx::tc_fence_after();
+                // row `row` of the 128-byte-swizzled tile: 16-byte chunk j sits at position j ^ (row & 7)
+                const uint8_t *arow = base_ptr + s * STAGE_BYTES + row * 128;
+                float v[TK];
+#pragma unroll
+                for (int j = 0; j < TK / 4; ++j) {
+                    const float4 x = *reinterpret_cast<const float4 *>(arow + ((j ^ (row & 7)) << 4));
+                    v[4 * j] = x.x, v[4 * j + 1] = x.y, v[4 * j + 2] = x.z, v[4 * j + 3] = x.w;
+                }
+                const uint32_t ta = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(A_TM_COL0 + t * 2 * TK);
+                ptx::tmem_st32(ta, v);
+#pragma unroll
+                for (int j = 0; j < TK; ++j) v[j] = tf32_lo(v[j]);
+                ptx::tmem_st32(ta + TK, v);
+                ptx::tmem_st_wait();
+                ptx::tc_fence_before();
+                ptx::mbar_arrive(bar_afull(t));
+                if (++s == NSTAGE) { s = 0; ph ^= 1u; }
+                if (++t == NATM) { t = 0; pht ^= 1u; }
+            }
+        }
     } else if (warp < 2 + NSPLIT_WARPS) {
-        // =========================== splitter ===========================
-        const int tid = threadIdx.x - 64;
-        constexpr int NT = 32 * NSPLIT_WARPS;
+        // =========================== B splitter ===========================
+        const int tid = threadIdx.x - 32 * (2 + NSPLIT_A);
+        constexpr int NT = 32 * NSPLIT_B;
         int s = 0, c = 0;
         uint32_t ph = 0, phc = 0;
         bool ok = true;
-        const int na4 = A_TILE_BYTES / 16, nb4 = (gp.b_mn ? P.bblk * B_BLK_BYTES : P.bn * TK * 4) / 16;
+        const int nb4 = (gp.b_mn ? P.bblk * B_BLK_BYTES : P.bn * TK * 4) / 16;
         for (int u = blockIdx.x; u < P.nunits && ok; u += gridDim.x) {
             const Unit w = get_unit(u);
             if (w.skip) continue;
             for (int ks = 0; ks < w.ksteps; ++ks) {
                 if (!(ok = ptx::mbar_wait_bounded(bar_full(s), ph, abort_flag, WAIT_LIMIT))) break;
                 if (!(ok = ptx::mbar_wait_bounded(bar_loempty(c), phc ^ 1u, abort_flag, WAIT_LIMIT))) break;
-                float4 *src = reinterpret_cast<float4 *>(base_ptr + s * STAGE_BYTES);
-                float4 *dst = reinterpret_cast<float4 *>(base_ptr + (NSTAGE + c) * STAGE_BYTES);
-                // the B tile follows the A tile directly; all loads of a thread are issued before the first store
-                constexpr int PER = (STAGE_BYTES / 16 + NT - 1) / NT;
-                const int n4 = na4 + nb4;
+                float4 *src = reinterpret_cast<float4 *>(base_ptr + s * STAGE_BYTES + B_OFF);
+                float4 *dst = reinterpret_cast<float4 *>(base_ptr + NSTAGE * STAGE_BYTES + c * B_TILE_BYTES);
+                // all loads of a thread are issued before the first store
+                constexpr int PER = (B_TILE_BYTES / 16 + NT - 1) / NT;
                 float4 v[PER];
 #pragma unroll
                 for (int j = 0; j < PER; ++j) {
                     const int i = tid + j * NT;
-                    if (i < n4) v[j] = src[i];
+                    if (i < nb4) v[j] = src[i];
                 }
 #pragma unroll
                 for (int j = 0; j < PER; ++j) {
                     const int i = tid + j * NT;
-                    if (i < n4) {
+                    if (i < nb4) {
                         dst[i] = make_float4(tf32_lo(v[j].x), tf32_lo(v[j].y), tf32_lo(v[j].z), tf32_lo(v[j].w));
                         if (P.write_hi) src[i] = make_float4(tf32_hi(v[j].x), tf32_hi(v[j].y), tf32_hi(v[j].z), tf32_hi(v[j].w));
                     }

@@ -39,7 +39,7 @@ constexpr int TK = kBK;                // floats per k-step: one 128-byte swizzl
 constexpr int TILE_M = 128;
 constexpr int BN_MAX = 160;
 constexpr int NSTAGE = 4;              // TMA ring
-constexpr int NLO = 3;                 // shared-memory slots for the low-order part of B
+constexpr int NLO = 4;                 // shared-memory slots for the low-order part of B
 constexpr int NACC = 2;                // accumulator buffers in tensor memory
 constexpr int NATM = 3;                // A slots in tensor memory (raw + lo: 2 x 32 columns each)
 constexpr int A_TILE_BYTES = TILE_M * TK * 4;                // 16 KiB

@@ -9,6 +9,7 @@
 //                     dense table, torch_harmonics/legendre.py:77-78).
 //  * fold / unfold  : distributed stages: plain complex (field, k, m) <-> folded order-major operand.
 
+#include <algorithm>
 #include <string>
 
 #include "common.cuh"
@@ -137,75 +138,117 @@ __global__ void pack_coeffs_kernel(const float2 *__restrict__ c, float *__restri
     }
 }
 
-// Scalar fast path, both directions: tiled transpose between the coefficient array c[field][l][m] (m contiguous)
-// and the degree-slab layout S[(slab0[g] + r / 32) * ncols + 2 field + re/im][r % 32] with r = (l - m - p) / 2.
-// One CTA moves a 64 (degrees) x 32 (orders) tile of one field through shared memory so that both sides see
-// full 128- or 256-byte runs; the tile is stored with even and odd degrees apart, which makes both phases free of
-// bank conflicts.  TO_SLABS also writes the zero padding of the last slab of every group; the reverse direction
-// also writes the exact zeros of the l < m triangle.
+// Scalar fast path, both directions: tiled transpose between the coefficient array c[field][l][mi] (order index mi
+// contiguous, order m = m0 + mi) and the degree-slab layout S[(slab0[g] + r / 32) * ncols + 2 field + re/im][r % 32] with
+// g = 2 m + p and r = (l - m - p) / 2.
+//
+// A CTA takes 32 orders x ONE slab index sb (32 consecutive r of both parities of each order) of one field.  On the
+// slab side that is, per (order, parity), two adjacent 128-byte rows (re, im) moved as float4 per thread; in the
+// coefficient array it is the band 64 sb <= l - m < 64 sb + 64, i.e. 95 rows l of which every one is touched as one
+// contiguous run of up to 32 complex values (8-byte accesses, a warp per row).  The tile passes through shared memory
+// as T[l - lbase][mi ^ swz(l - lbase)] (float2); the column swizzle makes the strided scalar accesses of the slab side
+// hit 32 different banks.
+//
+// TO_SLABS = false additionally writes the exact zeros of the l < m triangle: the part next to the diagonal from the
+// sb = 0 tiles, the full 32-order row segments above it from extra tiles (blockIdx.y >= nsb).
+// TO_SLABS = true writes the zero padding of the last slab of every group (degrees l >= lmax read as zero).
+constexpr int kTileRows = 96;
+__device__ __forceinline__ int tile_swz(int ll) { return 2 * ((ll >> 3) & 7) + (ll & 1); }
+
 template <bool TO_SLABS>
 __global__ void __launch_bounds__(256) coeff_slab_transpose_kernel(float2 *__restrict__ c, float *__restrict__ S, const long long *__restrict__ slab0,
-                                                                   const int *__restrict__ gkb, int ncols, int lmax, int mloc, int m0) {
-    __shared__ float tre[2][32][33], tim[2][32][33];  // [degree parity][degree / 2][order]
-    __shared__ long long s_slab[64];
-    __shared__ int s_rows[64];
-    const int mb0 = blockIdx.x * 32, l0 = blockIdx.y * 64, f = blockIdx.z;
+                                                                   const int *__restrict__ gkb, int ncols, int lmax, int mloc, int m0, int nsb) {
+    __shared__ float2 T[kTileRows][32];
+    const int mb0 = blockIdx.x * 32, f = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // tiles entirely above the diagonal (every l < every m) hold no coefficient: nothing to read for the slabs
-    if (TO_SLABS && l0 + 63 < m0 + mb0) return;
+    const int mi_l = mb0 + lane;  // order index of this lane on the coefficient side
 
-    if (threadIdx.x < 64) {  // the 32 x 2 (order, parity) groups this tile touches
-        const int mi = mb0 + (threadIdx.x >> 1);
-        long long sl = 0;
-        int rows = 0;
-        if (mi < mloc) {
-            const int g = 2 * (m0 + mi) + (threadIdx.x & 1);
-            sl = slab0[g] - slab0[2 * m0];
-            rows = gkb[g] * kBK;
-        }
-        s_slab[threadIdx.x] = sl;
-        s_rows[threadIdx.x] = rows;
+    if ((int)blockIdx.y >= nsb) {
+        // rows entirely above the diagonal for all 32 orders: l < m0 + mb0
+        if (TO_SLABS) return;
+        const int t = blockIdx.y - nsb;
+        const int hi = m0 + mb0 - 64 * t, lo = max(hi - 64, 0);
+        for (int l = lo + warp; l < min(hi, lmax); l += 8)
+            if (mi_l < mloc) c[((size_t)f * lmax + l) * mloc + mi_l] = make_float2(0.f, 0.f);
+        return;
     }
+    const int sb = blockIdx.y;
+    // the first order of the tile has the longest groups: nothing to do beyond them (except the zeros next to the diagonal)
+    if (sb > 0 && sb >= gkb[2 * (m0 + mb0)]) return;
+    const int lbase = m0 + mb0 + 64 * sb;  // degree of tile row 0
+
     if (TO_SLABS) {
-        for (int r = warp; r < 64; r += 8) {
-            const int l = l0 + r, mi = mb0 + lane;
-            float2 z = make_float2(0.f, 0.f);
-            if (l < lmax && mi < mloc) z = c[((size_t)f * lmax + l) * mloc + mi];
-            tre[r & 1][r >> 1][lane] = z.x;
-            tim[r & 1][r >> 1][lane] = z.y;
+        // all twelve loads of a thread are in flight before the first store
+        float2 v[kTileRows / 8];
+#pragma unroll
+        for (int it = 0; it < kTileRows / 8; ++it) {
+            const int ll = warp + 8 * it;
+            const int l = lbase + ll, d = ll - lane;  // d = l - m - 64 sb
+            v[it] = make_float2(0.f, 0.f);
+            if (d >= 0 && d < 64 && l < lmax && mi_l < mloc) v[it] = __ldg(c + ((size_t)f * lmax + l) * mloc + mi_l);
         }
+#pragma unroll
+        for (int it = 0; it < kTileRows / 8; ++it) {
+            const int ll = warp + 8 * it;
+            T[ll][lane ^ tile_swz(ll)] = v[it];
+        }
+        __syncthreads();
     }
-    __syncthreads();
-    // 32 orders x 2 parities: runs of up to 32 consecutive r, real and imaginary rows 32 floats apart
-    for (int combo = warp; combo < 64; combo += 8) {
-        const int ml = combo >> 1, p = combo & 1;
-        const int mi = mb0 + ml;
-        if (mi >= mloc) continue;
-        const int m = m0 + mi;
-        const int par = (m + p) & 1;        // l0 is even: degrees of this parity inside the tile are l0 + par + 2 lane
-        const int l = l0 + par + 2 * lane;
-        const int r = (l - m - p) >> 1;     // arithmetic shift: negative when l < m + p
-        const size_t at = ((size_t)(s_slab[combo] + (r >> 5)) * ncols + 2 * f) * kBK + (r & 31);
-        if (TO_SLABS) {
-            if (l >= m + p && r < s_rows[combo]) {
-                S[at] = tre[par][lane][ml];
-                S[at + kBK] = tim[par][lane][ml];
+    // slab side: a warp moves both parities of one order per step: lane = (parity, re/im, quad of r)
+    {
+        const int q = lane & 7, ri = (lane >> 3) & 1, p = lane >> 4;
+        float4 x[4];
+        float *srow[4];
+        bool have[4];
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+            const int ml = warp + 8 * it, mi = mb0 + ml;
+            have[it] = false;
+            srow[it] = S;
+            if (mi < mloc) {
+                const int g = 2 * (m0 + mi) + p;
+                have[it] = sb < gkb[g];
+                srow[it] = S + ((size_t)(slab0[g] - slab0[2 * m0] + sb) * ncols + 2 * f + ri) * kBK + 4 * q;
             }
-        } else {
-            float vr = 0.f, vi = 0.f;
-            if (l >= m + p && l < lmax) {
-                vr = S[at];
-                vi = S[at + kBK];
+        }
+        if (!TO_SLABS) {
+#pragma unroll
+            for (int it = 0; it < 4; ++it) {
+                x[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (have[it]) x[it] = __ldg(reinterpret_cast<const float4 *>(srow[it]));
             }
-            tre[par][lane][ml] = vr;
-            tim[par][lane][ml] = vi;
+        }
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+            const int ml = warp + 8 * it;
+            const int ll0 = ml + p + 8 * q;  // tile row of the first of this thread's four degrees (rows ll0, +2, +4, +6)
+            if (TO_SLABS) {
+                if (have[it]) {
+                    float v[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int ll = ll0 + 2 * i;
+                        v[i] = reinterpret_cast<const float *>(&T[ll][ml ^ tile_swz(ll)])[ri];
+                    }
+                    *reinterpret_cast<float4 *>(srow[it]) = make_float4(v[0], v[1], v[2], v[3]);
+                }
+            } else if (mb0 + ml < mloc) {
+                const float v[4] = {x[it].x, x[it].y, x[it].z, x[it].w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int ll = ll0 + 2 * i;
+                    reinterpret_cast<float *>(&T[ll][ml ^ tile_swz(ll)])[ri] = v[i];
+                }
+            }
         }
     }
     if (!TO_SLABS) {
         __syncthreads();
-        for (int r = warp; r < 64; r += 8) {
-            const int l = l0 + r, mi = mb0 + lane;
-            if (l < lmax && mi < mloc) c[((size_t)f * lmax + l) * mloc + mi] = make_float2(tre[r & 1][r >> 1][lane], tim[r & 1][r >> 1][lane]);
+        for (int ll = warp; ll < kTileRows; ll += 8) {
+            const int l = lbase + ll, d = ll - lane;
+            if (l >= lmax || mi_l >= mloc) continue;
+            if (d >= 0 && d < 64) c[((size_t)f * lmax + l) * mloc + mi_l] = T[ll][lane ^ tile_swz(ll)];
+            else if (d < 0 && sb == 0) c[((size_t)f * lmax + l) * mloc + mi_l] = make_float2(0.f, 0.f);  // l < m
         }
     }
 }
@@ -309,8 +352,9 @@ int launch_pack_coeffs(const Plan &pl, const float2 *c, float *Ct, int nfields, 
     const int ncols = (pl.vector ? 4 : 2) * nfields;
     if (mloc == 0 || ncols == 0) return SHTB200_OK;
     if (!pl.vector && nfields <= 65535) {
-        dim3 grid(ceil_div(mloc, 32), ceil_div(pl.lmax + 64, 64), nfields);
-        coeff_slab_transpose_kernel<true><<<grid, 256, 0, st>>>(const_cast<float2 *>(c), Ct, pl.d_gb0, pl.d_gkb, ncols, pl.lmax, mloc, m0);
+        const int nsb = ceil_div(pl.Lh, kBK);  // slabs of the longest group
+        dim3 grid(ceil_div(mloc, 32), nsb, nfields);
+        coeff_slab_transpose_kernel<true><<<grid, 256, 0, st>>>(const_cast<float2 *>(c), Ct, pl.d_gb0, pl.d_gkb, ncols, pl.lmax, mloc, m0, nsb);
         SHT_CUDA_CHECK(cudaGetLastError());
         return SHTB200_OK;
     }
@@ -325,8 +369,11 @@ int launch_unpack_coeffs(const Plan &pl, const float *Z, float2 *c, int nfields,
     if (pl.vector) return fail(SHTB200_EINVAL, "slab output is implemented for the scalar kinds only");
     if (mloc == 0 || nfields == 0) return SHTB200_OK;
     if (nfields > 65535) return fail(SHTB200_EINVAL, "too many fields in one call (limit 65535)");
-    dim3 grid(ceil_div(mloc, 32), ceil_div(pl.lmax, 64), nfields);
-    coeff_slab_transpose_kernel<false><<<grid, 256, 0, st>>>(c, const_cast<float *>(Z), pl.d_gb0, pl.d_gkb, 2 * nfields, pl.lmax, mloc, m0);
+    const int nsb = ceil_div(pl.Lh, kBK);
+    // extra tile rows for the degrees above the diagonal of the last order block: l < m0 + 32 (blocks - 1)
+    const int nzero = ceil_div(std::min(m0 + 32 * (ceil_div(mloc, 32) - 1), pl.lmax), 64);
+    dim3 grid(ceil_div(mloc, 32), nsb + nzero, nfields);
+    coeff_slab_transpose_kernel<false><<<grid, 256, 0, st>>>(c, const_cast<float *>(Z), pl.d_gb0, pl.d_gkb, 2 * nfields, pl.lmax, mloc, m0, nsb);
     SHT_CUDA_CHECK(cudaGetLastError());
     return SHTB200_OK;
 }

@@ -142,6 +142,8 @@ size_t shtb200_plan_table_bytes(const shtb200_plan *plan);
  *   shtb200_legendre   : the plan's contraction alone.  Analysis kinds: complex64 [nfields, nlat, mloc]
  *                        (m fastest) -> complex64 [nfields, lmax, mloc]; synthesis kinds the reverse.  `m0` is
  *                        the first global order held locally and `mloc` the number of local orders.
+ *                        Vector kinds (distributed_sht.py:497-555, 651-711): nfields counts (theta, phi) pairs and both
+ *                        tensors carry the component axis, [nfields, 2, nlat, mloc] <-> [nfields, 2, lmax, mloc].
  */
 int shtb200_rfft_modes(const float *in_dev, void *out_dev, long long nrows, int nlon, int nmodes, float scale, void *stream);
 int shtb200_irfft_modes(const void *in_dev, float *out_dev, long long nrows, int nlon, int nmodes, void *stream);

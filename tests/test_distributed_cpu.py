@@ -37,7 +37,8 @@ def _worker(rank, world, port, which):
     assert thd.is_initialized()
     thd.config.debug = True  # exercises the shape-verification all-gathers too
 
-    for shape, dims, dtype in (((5, 3, 7, 9), (-3, -1), torch.float32), ((4, 6, 33, 65), (1, 2), torch.float64), ((3, 8, 5), (0, 2), torch.complex64), ((2, 2, 4), (-1, -3), torch.float32)):
+    for shape, dims, dtype in (((5, 3, 7, 9), (-3, -1), torch.float32), ((4, 6, 33, 65), (1, 2), torch.float64), ((3, 8, 5), (0, 2), torch.complex64), ((2, 2, 4), (-1, -3), torch.float32),
+                               ((3, 4, 2, 5, 6), (-4, -1), torch.float32), ((3, 4, 2, 5, 6), (-2, -4), torch.complex64)):
         g = torch.Generator().manual_seed(1)
         if dtype.is_complex:
             full = torch.complex(torch.randn(shape, generator=g), torch.randn(shape, generator=g))

@@ -228,6 +228,8 @@ def test_cfg3_rows_match_reference():
     del p
     assert np.max(np.abs(x[:, g["rows_k"]] - g["field_rows"])) / float(g["field_absmax"]) < 1e-11
     w, _, _ = orc.sht_weights(721, 1440, 720, 720, "equiangular")
-    assert rel(w[[0, 1, 2, 359, 719]][:, g["rows_l"]][:, :, ::40], g["weights_rows"]) < 1e-12
+    # the fixture keeps these rows of the reference's buffer in the precision the module held them in
+    wtol = 1e-12 if g["weights_rows"].dtype == np.float64 else 2e-7
+    assert rel(w[[0, 1, 2, 359, 719]][:, g["rows_l"]][:, :, ::40], g["weights_rows"]) < wtol
     c = orc.sht_forward(x, w)
     assert np.max(np.abs(c[:, g["rows_l"]] - g["coeff_rows"])) / float(g["coeff_absmax"]) < 1e-11

@@ -496,7 +496,6 @@ size_t shtb200_legendre_workspace_bytes(const shtb200_plan *pl, int nfields, int
 
 int shtb200_legendre(shtb200_plan *pl, const void *in_dev, void *out_dev, int nfields, int m0, int mloc, void *workspace_dev, size_t workspace_bytes, void *stream) {
     if (!pl) return fail(SHTB200_EINVAL, "plan is null");
-    if (pl->vector) return fail(SHTB200_EINVAL, "stage-wise Legendre entry point supports the scalar kinds only");
     if (nfields < 0 || m0 < 0 || mloc < 0 || m0 + mloc > pl->mmax) return fail(SHTB200_EINVAL, "bad (nfields, m0, mloc)");
     pl->last_launches = 0;
     if (nfields == 0 || mloc == 0) return SHTB200_OK;
@@ -512,15 +511,21 @@ int shtb200_legendre(shtb200_plan *pl, const void *in_dev, void *out_dev, int nf
         float *X = reinterpret_cast<float *>(workspace_dev);
         float *Z = reinterpret_cast<float *>(reinterpret_cast<char *>(workspace_dev) + align256(w.op_bytes));
         if ((rc = launch_fold_modes(*pl, reinterpret_cast<const float2 *>(in_dev), X, nfields, m0, mloc, st))) return rc;
-        GemmParams gp = gemm_params(*pl, nfields, m0, mloc, X, Z);
-        if ((rc = run_gemm(*pl, gp, st))) return rc;
-        if ((rc = launch_unpack_coeffs(*pl, Z, reinterpret_cast<float2 *>(out_dev), nfields, m0, mloc, st))) return rc;
+        if (pl->vector) {  // the contraction writes the coefficients itself; the l < m triangle is zeroed first
+            if ((rc = launch_zero_upper(*pl, reinterpret_cast<float2 *>(out_dev), nfields, m0, mloc, st))) return rc;
+            GemmParams gp = gemm_params(*pl, nfields, m0, mloc, X, reinterpret_cast<float *>(out_dev));
+            if ((rc = run_gemm(*pl, gp, st))) return rc;
+        } else {
+            GemmParams gp = gemm_params(*pl, nfields, m0, mloc, X, Z);
+            if ((rc = run_gemm(*pl, gp, st))) return rc;
+            if ((rc = launch_unpack_coeffs(*pl, Z, reinterpret_cast<float2 *>(out_dev), nfields, m0, mloc, st))) return rc;
+        }
         pl->last_launches += 2;
     } else {
         float *Ct = reinterpret_cast<float *>(workspace_dev);
         float *Y = reinterpret_cast<float *>(reinterpret_cast<char *>(workspace_dev) + align256(w.op_bytes));
         if ((rc = launch_pack_coeffs(*pl, reinterpret_cast<const float2 *>(in_dev), Ct, nfields, m0, mloc, st))) return rc;
-        if ((rc = clear_empty_groups(*pl, Y, 2 * nfields, m0, mloc, st))) return rc;
+        if ((rc = clear_empty_groups(*pl, Y, (pl->vector ? 4 : 2) * nfields, m0, mloc, st))) return rc;
         GemmParams gp = gemm_params(*pl, nfields, m0, mloc, Ct, Y);
         if ((rc = run_gemm(*pl, gp, st))) return rc;
         if ((rc = launch_unfold_modes(*pl, Y, reinterpret_cast<float2 *>(out_dev), nfields, m0, mloc, st))) return rc;

@@ -289,6 +289,44 @@ __global__ void fold_modes_kernel(const float2 *__restrict__ Xc, float *__restri
     }
 }
 
+// Vector analysis: Xc (pair, component, k, mloc) complex -> the two-segment operand the vector contraction reads
+// (the layout fft_analysis_kernel<.., 2, ..> emits): columns 4 f .. 4 f + 3 feed (s_re, s_im, t_re, t_im); rows
+// k' < Kh contract against the d/dtheta table and carry the fold of parity 1 - p, rows Kh + k' against the
+// m/sin(theta) table with the fold of parity p; signs as in torch_harmonics/sht.py:488-493.
+__global__ void fold_modes_vec_kernel(const float2 *__restrict__ Xc, float *__restrict__ X, int npairs, int nlat, int Kh, int ncp, int mloc) {
+    const int Ka = 2 * Kh, Kr = (Ka + kBK - 1) / kBK * kBK;
+    const int ngroups = 2 * mloc;
+    const long long total = (long long)mloc * (Kh + (Kr - Ka)) * npairs;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int f = (int)(i % npairs);
+        const long long t = i / npairs;
+        const int k = (int)(t % (Kh + (Kr - Ka)));
+        const int mi = (int)(t / (Kh + (Kr - Ka)));
+        if (k >= Kh) {  // rows that pad the contraction length to a multiple of 32
+            const int kk = Ka + (k - Kh);
+            for (int p = 0; p < 2; ++p) *reinterpret_cast<float4 *>(X + (size_t)blocked_row(2 * mi + p, kk, ngroups) * ncp + 4 * f) = make_float4(0.f, 0.f, 0.f, 0.f);
+            continue;
+        }
+        const int ks = nlat - 1 - k;
+        float2 e[2], o[2];
+        for (int comp = 0; comp < 2; ++comp) {
+            const float2 a = Xc[(((size_t)f * 2 + comp) * nlat + k) * mloc + mi];
+            e[comp] = a;
+            o[comp] = make_float2(0.f, 0.f);
+            if (ks != k) {
+                const float2 b = Xc[(((size_t)f * 2 + comp) * nlat + ks) * mloc + mi];
+                e[comp] = make_float2(a.x + b.x, a.y + b.y);
+                o[comp] = make_float2(a.x - b.x, a.y - b.y);
+            }
+        }
+        for (int p = 0; p < 2; ++p) {
+            const float2 *fa = p ? e : o, *fb = p ? o : e;
+            *reinterpret_cast<float4 *>(X + (size_t)blocked_row(2 * mi + p, k, ngroups) * ncp + 4 * f) = make_float4(fa[0].x, fa[0].y, -fa[1].x, -fa[1].y);
+            *reinterpret_cast<float4 *>(X + (size_t)blocked_row(2 * mi + p, Kh + k, ngroups) * ncp + 4 * f) = make_float4(-fb[1].y, fb[1].x, -fb[0].y, fb[0].x);
+        }
+    }
+}
+
 // Y[blocked_row(2 mi + p, k')][2 f + ri] -> Xc (field, k, mloc) complex
 // (rows above krow0[2 (m0 + mi) + p] were not produced by the contraction: they count as zeros)
 __global__ void unfold_modes_kernel(const float *__restrict__ Y, float2 *__restrict__ Xc, int nfields, int nlat, int Kh, int ncp, int mloc, const int *__restrict__ krow0, int m0) {
@@ -388,7 +426,14 @@ int launch_zero_upper(const Plan &pl, float2 *c, int nfields, int m0, int mloc, 
 
 int launch_fold_modes(const Plan &pl, const float2 *Xc, float *X, int nfields, int m0, int mloc, cudaStream_t st) {
     (void)m0;
-    if (pl.vector) return fail(SHTB200_EINVAL, "stage-wise Legendre entry point supports the scalar kinds only");
+    if (pl.vector) {
+        const int pad = (int)(round_up(pl.Ka, kBK) - pl.Ka);
+        const long long total = (long long)mloc * nfields * (pl.Kh + pad);
+        if (total == 0) return SHTB200_OK;
+        fold_modes_vec_kernel<<<grid_x_for(total), 256, 0, st>>>(Xc, X, nfields, pl.nlat, pl.Kh, (int)col_pitch(4 * nfields), mloc);
+        SHT_CUDA_CHECK(cudaGetLastError());
+        return SHTB200_OK;
+    }
     const long long total = (long long)mloc * nfields * round_up(pl.Kh, kBK);
     if (total == 0) return SHTB200_OK;
     fold_modes_kernel<<<grid_x_for(total), 256, 0, st>>>(Xc, X, nfields, pl.nlat, pl.Kh, (int)col_pitch(2 * nfields), mloc);
@@ -397,10 +442,11 @@ int launch_fold_modes(const Plan &pl, const float2 *Xc, float *X, int nfields, i
 }
 
 int launch_unfold_modes(const Plan &pl, const float *Y, float2 *Xc, int nfields, int m0, int mloc, cudaStream_t st) {
-    if (pl.vector) return fail(SHTB200_EINVAL, "stage-wise Legendre entry point supports the scalar kinds only");
-    const long long total = (long long)nfields * pl.Kh * mloc;
+    // a vector pair is two complex fields side by side (theta, phi): same kernel on 2 x nfields fields
+    const int nf = pl.vector ? 2 * nfields : nfields;
+    const long long total = (long long)nf * pl.Kh * mloc;
     if (total == 0) return SHTB200_OK;
-    unfold_modes_kernel<<<grid_x_for(total), 256, 0, st>>>(Y, Xc, nfields, pl.nlat, pl.Kh, (int)col_pitch(2 * nfields), mloc, pl.d_krow0, m0);
+    unfold_modes_kernel<<<grid_x_for(total), 256, 0, st>>>(Y, Xc, nf, pl.nlat, pl.Kh, (int)col_pitch(2 * nf), mloc, pl.d_krow0, m0);
     SHT_CUDA_CHECK(cudaGetLastError());
     return SHTB200_OK;
 }

@@ -3,7 +3,7 @@
 Mirrors the SHT-related exports of torch_harmonics/distributed/__init__.py:33-71.
 """
 
-from .distributed_sht import DistributedInverseRealSHT, DistributedRealSHT
+from .distributed_sht import DistributedInverseRealSHT, DistributedInverseRealVectorSHT, DistributedRealSHT, DistributedRealVectorSHT
 from .primitives import (
     compute_split_shapes,
     distributed_transpose_azimuth,

@@ -1,7 +1,7 @@
-"""Spatially distributed scalar SHT modules on the shtb200 kernels.
+"""Spatially distributed SHT modules (scalar and vector) on the shtb200 kernels.
 
-Counterparts of ``DistributedRealSHT`` / ``DistributedInverseRealSHT``
-(torch_harmonics/distributed/distributed_sht.py:51-222, :225-391): same constructor arguments, attributes
+Counterparts of ``DistributedRealSHT`` / ``DistributedInverseRealSHT`` / ``DistributedRealVectorSHT`` /
+``DistributedInverseRealVectorSHT`` (torch_harmonics/distributed/distributed_sht.py:51-222, :225-391, :394-555, :558-711): same constructor arguments, attributes
 (``comm_size_*``, ``comm_rank_*``, ``lat_shapes``, ``lon_shapes``, ``l_shapes``, ``m_shapes``, ``nlat_local``,
 ``nlon_local``, ``lmax_local``, ``mmax_local``), local tensor layouts and autograd behaviour.  Latitudes and
 degrees are sharded over the polar group, longitudes and orders over the azimuth group; four all-to-all
@@ -17,7 +17,7 @@ import torch
 import torch.nn as nn
 
 from .. import _lib
-from ..legendre import _precompute_legpoly
+from ..legendre import _precompute_dlegpoly, _precompute_legpoly
 from ..quadrature import sht_colatitudes
 from ..sht import _default_engine, _require
 from ..truncation import truncate_sht
@@ -96,14 +96,15 @@ class _IrfftStage(torch.autograd.Function):
 
 
 class _LegendreStage(torch.autograd.Function):
-    """Contraction with the packed table for the local orders [m0, m0 + mloc): (N, nlat, mloc) <-> (N, lmax, mloc)."""
+    """Contraction with the packed table for the local orders [m0, m0 + mloc): (N, nlat, mloc) <-> (N, lmax, mloc);
+    vector plans carry the component axis, (N, 2, nlat, mloc) <-> (N, 2, lmax, mloc)."""
 
     @staticmethod
     def forward(ctx, x, owner, adjoint, out_rows):
         ctx.owner, ctx.adjoint, ctx.in_rows = owner, adjoint, x.shape[-2]
         xc = x.contiguous()
         n, mloc = xc.shape[0], xc.shape[-1]
-        out = torch.empty((n, out_rows, mloc), dtype=torch.complex64, device=x.device)
+        out = torch.empty(xc.shape[:-2] + (out_rows, mloc), dtype=torch.complex64, device=x.device)
         if n == 0 or mloc == 0:
             return out
         plan = owner._plan(x.device, adjoint)
@@ -232,3 +233,86 @@ class DistributedInverseRealSHT(_DistributedBase):
         if self.comm_size_azimuth > 1:
             x = distributed_transpose_azimuth(x, (-1, -3), compute_split_shapes(num_chans, self.comm_size_azimuth))
         return unpad_and_unflatten_leading_dims(x, lead_shape, lead_size)
+
+
+class DistributedRealVectorSHT(_DistributedBase):
+    """Forward vector SHT on a local tile: ``(..., 2, nlat_local, nlon_local)`` float32 ->
+    ``(..., 2, lmax_local, mmax_local)`` complex64 (spheroidal, toroidal)."""
+
+    _kind, _adj_kind = _lib.VSHT, _lib.VSHT_ADJOINT
+
+    def __init__(self, nlat, nlon, lmax=None, mmax=None, grid="equiangular", norm="ortho", csphase=True):
+        super().__init__(nlat, nlon, lmax, mmax, grid, norm, csphase)
+        weights = self._full_table()
+        # this rank's orders only (distributed_sht.py:490)
+        weights = split_tensor_along_dim(weights, dim=1, num_chunks=self.comm_size_azimuth)[self.comm_rank_azimuth].contiguous()
+        self.register_buffer("weights", weights, persistent=False)
+
+    def _full_table(self):
+        dpct = _precompute_dlegpoly(self.mmax, self.lmax, self._tq, norm=self.norm, csphase=self.csphase)
+        # 1 / (l (l + 1)) in float32, like the serial module (torch_harmonics/sht.py:439-441)
+        l = torch.arange(0, self.lmax)
+        norm_factor = 1.0 / l / (l + 1)
+        norm_factor[0] = 1.0
+        weights = dpct * self._quad_w.to(dpct.device)[None, None, None, :] * norm_factor.to(dtype=torch.float64, device=dpct.device)[None, None, :, None]
+        weights[1] = -1 * weights[1]
+        return weights.contiguous()
+
+    def forward(self, x: torch.Tensor):
+        torch._check(x.dim() >= 4, lambda: f"Expected tensor with at least 4 dimensions but got {x.dim()} instead")
+        torch._check(x.shape[-3] == 2, lambda: f"Expected vector field shape[-3]==2, got {x.shape[-3]}")
+        torch._check(x.shape[-2] == self.nlat_local, lambda: f"Expected latitudes shape[-2]=={self.nlat_local}, got {x.shape[-2]}")
+        torch._check(x.shape[-1] == self.nlon_local, lambda: f"Expected longitudes shape[-1]=={self.nlon_local}, got {x.shape[-1]}")
+        _require(x, torch.float32, "DistributedRealVectorSHT")
+
+        x, lead_shape, lead_size = flatten_and_pad_leading_dims(x, max(self.comm_size_polar, self.comm_size_azimuth), num_trailing_dims=3)
+        num_chans = x.shape[-4]
+        if self.comm_size_azimuth > 1:
+            x = distributed_transpose_azimuth(x, (-4, -1), self.lon_shapes)
+        x = _RfftStage.apply(x, self.mmax, 2.0 * math.pi)
+        if self.comm_size_azimuth > 1:
+            x = distributed_transpose_azimuth(x, (-1, -4), compute_split_shapes(num_chans, self.comm_size_azimuth))
+        if self.comm_size_polar > 1:
+            x = distributed_transpose_polar(x, (-4, -2), self.lat_shapes)
+        x = _LegendreStage.apply(x, self, False, self.lmax)
+        if self.comm_size_polar > 1:
+            x = distributed_transpose_polar(x, (-2, -4), compute_split_shapes(num_chans, self.comm_size_polar))
+        return unpad_and_unflatten_leading_dims(x, lead_shape, lead_size, num_trailing_dims=3)
+
+
+class DistributedInverseRealVectorSHT(_DistributedBase):
+    """Inverse vector SHT on a local tile: ``(..., 2, lmax_local, mmax_local)`` complex64 ->
+    ``(..., 2, nlat_local, nlon_local)`` float32."""
+
+    _kind, _adj_kind = _lib.IVSHT, _lib.IVSHT_ADJOINT
+
+    def __init__(self, nlat, nlon, lmax=None, mmax=None, grid="equiangular", norm="ortho", csphase=True):
+        super().__init__(nlat, nlon, lmax, mmax, grid, norm, csphase)
+        dpct = self._full_table()
+        dpct = split_tensor_along_dim(dpct, dim=1, num_chunks=self.comm_size_azimuth)[self.comm_rank_azimuth].contiguous()
+        self.register_buffer("dpct", dpct, persistent=False)
+
+    def _full_table(self):
+        dpct = _precompute_dlegpoly(self.mmax, self.lmax, self._tq, norm=self.norm, inverse=True, csphase=self.csphase)
+        return dpct.permute(0, 1, 3, 2).contiguous()
+
+    def forward(self, x: torch.Tensor):
+        torch._check(x.dim() >= 4, lambda: f"Expected tensor with at least 4 dimensions but got {x.dim()} instead")
+        torch._check(x.shape[-3] == 2, lambda: f"Expected vector field shape[-3]==2, got {x.shape[-3]}")
+        torch._check(x.shape[-2] == self.lmax_local, lambda: f"Expected spherical harmonic degrees (lmax) shape[-2]=={self.lmax_local}, got {x.shape[-2]}")
+        torch._check(x.shape[-1] == self.mmax_local, lambda: f"Expected spherical harmonic orders (mmax) shape[-1]=={self.mmax_local}, got {x.shape[-1]}")
+        _require(x, torch.complex64, "DistributedInverseRealVectorSHT")
+
+        x, lead_shape, lead_size = flatten_and_pad_leading_dims(x, max(self.comm_size_polar, self.comm_size_azimuth), num_trailing_dims=3)
+        num_chans = x.shape[-4]
+        if self.comm_size_polar > 1:
+            x = distributed_transpose_polar(x, (-4, -2), self.l_shapes)
+        x = _LegendreStage.apply(x, self, False, self.nlat)
+        if self.comm_size_polar > 1:
+            x = distributed_transpose_polar(x, (-2, -4), compute_split_shapes(num_chans, self.comm_size_polar))
+        if self.comm_size_azimuth > 1:
+            x = distributed_transpose_azimuth(x, (-4, -1), self.m_shapes)
+        x = _IrfftStage.apply(x, self.nlon)
+        if self.comm_size_azimuth > 1:
+            x = distributed_transpose_azimuth(x, (-1, -4), compute_split_shapes(num_chans, self.comm_size_azimuth))
+        return unpad_and_unflatten_leading_dims(x, lead_shape, lead_size, num_trailing_dims=3)

@@ -86,7 +86,9 @@ int shtb200_execute(shtb200_plan *plan, const void *in_dev, void *out_dev, int n
 
 /*
  * Same transform on HOST buffers: copies `in_host` to the device, runs, copies the result back and
- * synchronises `stream`.  Device staging buffers are kept in the plan and grown on demand.
+ * synchronises `stream`.  Device staging buffers are kept in the plan and grown on demand.  The fields are
+ * processed in chunks of eight: upload, kernels and download of successive chunks overlap on three streams (the
+ * copies run on streams owned by the plan; give pinned host memory, pageable memory serialises the copies).
  * This is the call a host-side caller of the reference's CPU path would switch to.
  */
 int shtb200_execute_host(shtb200_plan *plan, const void *in_host, void *out_host, int nfields, void *stream);

@@ -379,6 +379,10 @@ int shtb200_plan_destroy(shtb200_plan *pl) {
     cudaFree(pl->d_grows);
     cudaFree(pl->d_gkb);
     cudaFree(pl->d_gkb0);
+    if (pl->copy_in) cudaStreamDestroy(pl->copy_in);
+    if (pl->copy_out) cudaStreamDestroy(pl->copy_out);
+    for (cudaEvent_t e : pl->ev_up) cudaEventDestroy(e);
+    for (cudaEvent_t e : pl->ev_done) cudaEventDestroy(e);
     cudaFree(pl->stage_in);
     cudaFree(pl->stage_out);
     cudaFree(pl->stage_ws);
@@ -415,14 +419,44 @@ int shtb200_execute_host(shtb200_plan *pl, const void *in_host, void *out_host, 
     const size_t spec_bytes = (size_t)nfields * comp * pl->lmax * pl->mmax * sizeof(float2);
     const size_t in_bytes = pl->analysis ? grid_bytes : spec_bytes;
     const size_t out_bytes = pl->analysis ? spec_bytes : grid_bytes;
-    const size_t ws_bytes = shtb200_workspace_bytes(pl, nfields);
+    // Fields are independent, so the transform is pipelined over chunks of fields: the upload of chunk i + 1, the
+    // kernels of chunk i and the download of chunk i - 1 run at the same time on three streams (both PCIe directions busy).
+    const int chunk = std::min(nfields, 8);
+    const int nchunks = ceil_div(nfields, chunk);
+    const size_t ws_bytes = shtb200_workspace_bytes(pl, chunk);
     int rc;
     if ((rc = grow(&pl->stage_in, &pl->stage_in_bytes, in_bytes)) || (rc = grow(&pl->stage_out, &pl->stage_out_bytes, out_bytes)) ||
         (rc = grow(&pl->stage_ws, &pl->stage_ws_bytes, ws_bytes)))
         return rc;
-    SHT_CUDA_CHECK(cudaMemcpyAsync(pl->stage_in, in_host, in_bytes, cudaMemcpyHostToDevice, st));
-    if ((rc = execute_full(*pl, pl->stage_in, pl->stage_out, nfields, pl->stage_ws, pl->stage_ws_bytes, st))) return rc;
-    SHT_CUDA_CHECK(cudaMemcpyAsync(out_host, pl->stage_out, out_bytes, cudaMemcpyDeviceToHost, st));
+    if (!pl->copy_in) SHT_CUDA_CHECK(cudaStreamCreateWithFlags(&pl->copy_in, cudaStreamNonBlocking));
+    if (!pl->copy_out) SHT_CUDA_CHECK(cudaStreamCreateWithFlags(&pl->copy_out, cudaStreamNonBlocking));
+    while ((int)pl->ev_up.size() < nchunks + 1) {
+        cudaEvent_t a = nullptr, b = nullptr;
+        SHT_CUDA_CHECK(cudaEventCreateWithFlags(&a, cudaEventDisableTiming));
+        pl->ev_up.push_back(a);
+        SHT_CUDA_CHECK(cudaEventCreateWithFlags(&b, cudaEventDisableTiming));
+        pl->ev_done.push_back(b);
+    }
+    const size_t in_per = in_bytes / nfields, out_per = out_bytes / nfields;
+    // the copy streams start after whatever the caller already queued on `stream`
+    SHT_CUDA_CHECK(cudaEventRecord(pl->ev_up[nchunks], st));
+    SHT_CUDA_CHECK(cudaStreamWaitEvent(pl->copy_in, pl->ev_up[nchunks], 0));
+    int launches = 0;
+    for (int i = 0; i < nchunks; ++i) {
+        const int f0 = i * chunk, nf = std::min(chunk, nfields - f0);
+        char *din = reinterpret_cast<char *>(pl->stage_in) + (size_t)f0 * in_per;
+        char *dout = reinterpret_cast<char *>(pl->stage_out) + (size_t)f0 * out_per;
+        SHT_CUDA_CHECK(cudaMemcpyAsync(din, reinterpret_cast<const char *>(in_host) + (size_t)f0 * in_per, (size_t)nf * in_per, cudaMemcpyHostToDevice, pl->copy_in));
+        SHT_CUDA_CHECK(cudaEventRecord(pl->ev_up[i], pl->copy_in));
+        SHT_CUDA_CHECK(cudaStreamWaitEvent(st, pl->ev_up[i], 0));
+        if ((rc = execute_full(*pl, din, dout, nf, pl->stage_ws, pl->stage_ws_bytes, st))) return rc;
+        launches += pl->last_launches;
+        SHT_CUDA_CHECK(cudaEventRecord(pl->ev_done[i], st));
+        SHT_CUDA_CHECK(cudaStreamWaitEvent(pl->copy_out, pl->ev_done[i], 0));
+        SHT_CUDA_CHECK(cudaMemcpyAsync(reinterpret_cast<char *>(out_host) + (size_t)f0 * out_per, dout, (size_t)nf * out_per, cudaMemcpyDeviceToHost, pl->copy_out));
+    }
+    pl->last_launches = launches;
+    SHT_CUDA_CHECK(cudaStreamSynchronize(pl->copy_out));
     SHT_CUDA_CHECK(cudaStreamSynchronize(st));
     return SHTB200_OK;
 }

@@ -155,6 +155,9 @@ struct Plan {
     // host-call staging
     void *stage_in = nullptr, *stage_out = nullptr, *stage_ws = nullptr;
     size_t stage_in_bytes = 0, stage_out_bytes = 0, stage_ws_bytes = 0;
+    // host-buffer entry point: copy streams and per-chunk events of its upload / compute / download pipeline
+    cudaStream_t copy_in = nullptr, copy_out = nullptr;
+    std::vector<cudaEvent_t> ev_up, ev_done;
 
     int last_launches = 0;
     // First folded latitude row (a multiple of 32) of each group that the contraction touches: towards the pole the

@@ -232,8 +232,7 @@ int shtb200_plan_create(shtb200_plan **plan_out, int kind, int nlat, int nlon, i
     pl->Lh = (lmax + 1) / 2;
     pl->negate_seg1 = (kind == SHTB200_VSHT_ADJOINT || kind == SHTB200_IVSHT_ADJOINT) ? 1 : 0;
 
-    int rc = build_fft_plan(nlon, mmax, pl->analysis ? kFftSplit : kFftPacked, &pl->fft, &pl->d_tw, &pl->d_perm);
-    if (rc) { shtb200_plan_destroy(pl); return rc; }
+    int rc;
 
     // per-order scale applied inside the FFT kernels
     {
@@ -268,6 +267,10 @@ int shtb200_plan_create(shtb200_plan **plan_out, int kind, int nlat, int nlon, i
         std::vector<int> first;
         if ((rc = launch_polar_extent(*pl, table_dev, 1e-14f, &first))) { shtb200_plan_destroy(pl); return rc; }
         for (int g = 0; g < ngroups; ++g) pl->group_krow0[g] = std::min(first[g], std::max(pl->Kh - 1, 0)) / kBK * kBK;
+    }
+    if ((rc = build_fft_plan(nlon, mmax, pl->analysis ? kFftSplit : kFftPacked, pl->group_krow0.data(), &pl->fft, &pl->d_tw, &pl->d_perm))) {
+        shtb200_plan_destroy(pl);
+        return rc;
     }
     pl->group_a0.assign(ngroups + 1, 0);
     pl->group_kblocks.assign(ngroups, 0);

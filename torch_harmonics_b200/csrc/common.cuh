@@ -178,7 +178,8 @@ struct Plan {
 // ------------------------------------------------------------------------------------------------
 // mmax_emit > 0 also builds the emit order for that many retained orders (the SHT kernels); 0 leaves it out
 enum { kFftRows = 0, kFftSplit = 1, kFftPacked = 2 };  // shared-memory layout the tables are built for (see FftPlanDev)
-int build_fft_plan(int nlon, int mmax_emit, int layout, FftPlanDev *out, float2 **d_tw, unsigned short **d_perm);
+// krow0 (2 mmax_emit entries, may be null): first latitude row of every (order, parity) group that the contraction touches
+int build_fft_plan(int nlon, int mmax_emit, int layout, const int *krow0, FftPlanDev *out, float2 **d_tw, unsigned short **d_perm);
 
 // analysis: rows of x -> folded, order-major operand X[blocked_row(group, k)][col] (row pitch round_up(ncols, 4))
 int launch_fft_analysis(const Plan &pl, const float *x, float *X, int nfields, cudaStream_t st);

@@ -168,7 +168,7 @@ std::vector<unsigned short> order_emit(int n, int mmax, int stride, int lanes, i
 
 }  // namespace
 
-int build_fft_plan(int nlon, int mmax_emit, int layout, FftPlanDev *out, float2 **d_tw, unsigned short **d_perm) {
+int build_fft_plan(int nlon, int mmax_emit, int layout, const int *krow0, FftPlanDev *out, float2 **d_tw, unsigned short **d_perm) {
     if (nlon < 2 || nlon > 65535) return fail(SHTB200_EINVAL, "nlon must be in [2, 65535]");
     // strip prime factors 7..31 (generic butterflies), split the rest into fast radices
     std::vector<int> slow;
@@ -283,17 +283,26 @@ int build_fft_plan(int nlon, int mmax_emit, int layout, FftPlanDev *out, float2 
     }
     fp.eorder_len = (int)eorder.size();
     // One device allocation: the tables the kernels keep in shared memory as one 16-byte granular blob
-    //   [pass twiddles float2 x tw_pass_total][bfly u32 x bf_total][perm u16 x n][eorder u16 x eorder_len][pad]
+    //   [pass twiddles float2 x tw_pass_total][bfly u32 x bf_total][perm u16 x n][eorder u16 x eorder_len]
+    //   [kfirst u8 x eorder_len: first 32-row latitude block of the even (low nibble) / odd (high nibble) group of
+    //    each order that the contraction touches][pad]
     // followed by the n roots of unity the generic prime-radix butterflies read from global memory.
     const size_t o_bf = sizeof(float2) * tw.size();
     const size_t o_perm = o_bf + sizeof(unsigned) * bfly.size();
     const size_t o_eo = o_perm + sizeof(unsigned short) * perm.size();
-    const size_t tab_bytes = (o_eo + sizeof(unsigned short) * eorder.size() + 15) / 16 * 16;
+    const size_t o_kf = o_eo + sizeof(unsigned short) * eorder.size();
+    const size_t tab_bytes = (o_kf + eorder.size() + 15) / 16 * 16;
     std::vector<unsigned char> tab(tab_bytes + sizeof(float2) * nlon, 0);
     memcpy(tab.data(), tw.data(), sizeof(float2) * tw.size());
     memcpy(tab.data() + o_bf, bfly.data(), sizeof(unsigned) * bfly.size());
     memcpy(tab.data() + o_perm, perm.data(), sizeof(unsigned short) * perm.size());
     if (!eorder.empty()) memcpy(tab.data() + o_eo, eorder.data(), sizeof(unsigned short) * eorder.size());
+    if (krow0)
+        for (size_t m = 0; m < eorder.size(); ++m) {
+            const int b0 = krow0[2 * m] / kBK, b1 = krow0[2 * m + 1] / kBK;
+            if (b0 > 15 || b1 > 15) return fail(SHTB200_EINVAL, "polar extent does not fit the 4-bit block index");
+            tab[o_kf + m] = (unsigned char)(b0 | (b1 << 4));
+        }
     {
         float2 *roots = reinterpret_cast<float2 *>(tab.data() + tab_bytes);
         for (int k = 0; k < nlon; ++k) {
@@ -615,7 +624,7 @@ __device__ __forceinline__ bool tables_wait(uint32_t bar, int *err) {
 template <int NW, int VEC, int G>
 __global__ void __launch_bounds__(32 * NW * G, (NW * G >= 16) ? 2 : 1) fft_analysis_kernel(const float *__restrict__ x, float *__restrict__ X, FftPlanDev fp,
                                                                                             int nlat, int Kh, int nfields, int ncp, int mmax,
-                                                                                            const float *__restrict__ mscale, const int *__restrict__ krow0, int zero_imag_edges, int bulk_rows, int *err) {
+                                                                                            const float *__restrict__ mscale, int zero_imag_edges, int bulk_rows, int *err) {
     extern __shared__ __align__(16) float smem_f[];
     const int n = fp.n;
     constexpr int NF = NW / VEC;                    // fields (or component pairs) per CTA
@@ -688,6 +697,7 @@ __global__ void __launch_bounds__(32 * NW * G, (NW * G >= 16) ? 2 : 1) fft_analy
     constexpr int LPM = NW / 2;  // lanes per order
     const int c = threadIdx.x % LPM;
     const unsigned short *eo_s = (fp.eorder && fp.eorder_len == mmax) ? perm_s + n : nullptr;
+    const unsigned char *kf_s = eo_s ? reinterpret_cast<const unsigned char *>(eo_s + mmax) : nullptr;
     for (int i = threadIdx.x / LPM; i < mmax; i += blockDim.x / LPM) {
         const int m = eo_s ? eo_s[i] : i;
         float e[4], o[4];  // (re, im) of the even / odd fold of transforms 2c, 2c+1
@@ -717,8 +727,9 @@ __global__ void __launch_bounds__(32 * NW * G, (NW * G >= 16) ? 2 : 1) fft_analy
             const int col = 2 * f0 + 4 * c;
             if (col < ncp) {
                 // (the contraction does not read rows above the group's polar extent)
-                if (kn >= krow0[2 * m]) *reinterpret_cast<float4 *>(X + (size_t)blocked_row(2 * m, kn, ngroups) * ncp + col) = make_float4(e[0], e[1], e[2], e[3]);
-                if (kn >= krow0[2 * m + 1]) *reinterpret_cast<float4 *>(X + (size_t)blocked_row(2 * m + 1, kn, ngroups) * ncp + col) = make_float4(o[0], o[1], o[2], o[3]);
+                const int kf = kf_s ? kf_s[m] : 0;
+                if (kn >= (kf & 15) * kBK) *reinterpret_cast<float4 *>(X + (size_t)blocked_row(2 * m, kn, ngroups) * ncp + col) = make_float4(e[0], e[1], e[2], e[3]);
+                if (kn >= (kf >> 4) * kBK) *reinterpret_cast<float4 *>(X + (size_t)blocked_row(2 * m + 1, kn, ngroups) * ncp + col) = make_float4(o[0], o[1], o[2], o[3]);
             }
         } else {
             // transforms 2c (theta component X0) and 2c + 1 (phi component X1) of pair f0 + c: four columns 4 (f0 + c)..
@@ -745,7 +756,7 @@ __global__ void __launch_bounds__(32 * NW * G, (NW * G >= 16) ? 2 : 1) fft_analy
 template <int NW, int VEC, int G>
 __global__ void __launch_bounds__(32 * NW * G, (NW * G >= 16) ? 2 : 1) fft_synthesis_kernel(const float *__restrict__ Y, float *__restrict__ x, FftPlanDev fp,
                                                                                              int nlat, int Kh, int nfields, int ncp, int mmax,
-                                                                                             const float *__restrict__ mscale, const int *__restrict__ krow0, int vec4ok, int *err) {
+                                                                                             const float *__restrict__ mscale, int vec4ok, int *err) {
     extern __shared__ float2 smem[];
     const int n = fp.n;
     constexpr int NF = NW / VEC;
@@ -773,37 +784,57 @@ __global__ void __launch_bounds__(32 * NW * G, (NW * G >= 16) ? 2 : 1) fft_synth
             data[(size_t)u * np + perm_s[m]] = make_float2(0.f, 0.f);
         }
     }
-    // NW / 2 adjacent lanes share one order; lane c reads the 16-byte piece of both runs that holds transforms 2c, 2c+1
+    // NW / 2 adjacent lanes share one order; lane c reads the 16-byte piece of both runs that holds transforms 2c, 2c+1.
+    // The loads of three orders are issued before the first of them is consumed.
     {
         constexpr int LPM = NW / 2;
+        constexpr int NB = 3;
         const int c = threadIdx.x % LPM;
         const int col = colbase + 4 * c;
+        const int step = blockDim.x / LPM;
         const unsigned short *eo_s = (fp.eorder && fp.eorder_len == mmax) ? perm_s + n : nullptr;
-        for (int i = threadIdx.x / LPM; i < mmax; i += blockDim.x / LPM) {
-            const int m = eo_s ? eo_s[i] : i;
-            if (m >= mtop) continue;
-            float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
-            if (col < ncp) {
-                // (the contraction does not produce rows above the group's polar extent: they are zeros)
-                if (kn >= krow0[2 * m]) a = *reinterpret_cast<const float4 *>(Y + (size_t)blocked_row(2 * m, kn, 2 * mmax) * ncp + col);
-                if (kn >= krow0[2 * m + 1]) b = *reinterpret_cast<const float4 *>(Y + (size_t)blocked_row(2 * m + 1, kn, 2 * mmax) * ncp + col);
-            }
-            const float sc = mscale[m];
-            const bool edge = (m == 0) || (2 * m == n);
-            const int pm = perm_s[m];
-            const int pn = perm_s[m == 0 ? 0 : n - m];
-            const float e[4] = {a.x, a.y, a.z, a.w}, o[4] = {b.x, b.y, b.z, b.w};
+        const unsigned char *kf_s = eo_s ? reinterpret_cast<const unsigned char *>(eo_s + mmax) : nullptr;
+        for (int i0 = threadIdx.x / LPM; i0 < mmax; i0 += NB * step) {
+            int mm[NB];
+            float4 av[NB], bv[NB];
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                // north row spectrum A = even + odd, south row spectrum B = even - odd; Z = A + i B
-                const float ar = sc * (e[2 * h] + o[2 * h]), ai = sc * (e[2 * h + 1] + o[2 * h + 1]);
-                const float br = sc * (e[2 * h] - o[2 * h]), bi = sc * (e[2 * h + 1] - o[2 * h + 1]);
-                float2 *dd = data + (size_t)(2 * c + h) * np;
-                if (edge) {
-                    dd[pm] = make_float2(ar, br);  // imaginary parts of DC / Nyquist are dropped
-                } else {
-                    dd[pm] = make_float2(ar - bi, ai + br);
-                    dd[pn] = make_float2(ar + bi, br - ai);
+            for (int u = 0; u < NB; ++u) {
+                const int i = i0 + u * step;
+                int m = -1;
+                if (i < mmax) {
+                    m = eo_s ? eo_s[i] : i;
+                    if (m >= mtop) m = -1;
+                }
+                mm[u] = m;
+                av[u] = bv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (m >= 0 && col < ncp) {
+                    // (the contraction does not produce rows above the group's polar extent: they are zeros)
+                    const int kf = kf_s ? kf_s[m] : 0;
+                    if (kn >= (kf & 15) * kBK) av[u] = __ldg(reinterpret_cast<const float4 *>(Y + (size_t)blocked_row(2 * m, kn, 2 * mmax) * ncp + col));
+                    if (kn >= (kf >> 4) * kBK) bv[u] = __ldg(reinterpret_cast<const float4 *>(Y + (size_t)blocked_row(2 * m + 1, kn, 2 * mmax) * ncp + col));
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < NB; ++u) {
+                const int m = mm[u];
+                if (m < 0) continue;
+                const float sc = mscale[m];
+                const bool edge = (m == 0) || (2 * m == n);
+                const int pm = perm_s[m];
+                const int pn = perm_s[m == 0 ? 0 : n - m];
+                const float e[4] = {av[u].x, av[u].y, av[u].z, av[u].w}, o[4] = {bv[u].x, bv[u].y, bv[u].z, bv[u].w};
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    // north row spectrum A = even + odd, south row spectrum B = even - odd; Z = A + i B
+                    const float ar = sc * (e[2 * h] + o[2 * h]), ai = sc * (e[2 * h + 1] + o[2 * h + 1]);
+                    const float br = sc * (e[2 * h] - o[2 * h]), bi = sc * (e[2 * h + 1] - o[2 * h + 1]);
+                    float2 *dd = data + (size_t)(2 * c + h) * np;
+                    if (edge) {
+                        dd[pm] = make_float2(ar, br);  // imaginary parts of DC / Nyquist are dropped
+                    } else {
+                        dd[pm] = make_float2(ar - bi, ai + br);
+                        dd[pn] = make_float2(ar + bi, br - ai);
+                    }
                 }
             }
         }
@@ -953,7 +984,7 @@ int launch_fft_analysis(const Plan &pl, const float *x, float *X, int nfields, c
     do {                                                                                                                                    \
         if ((rc = set_smem(fft_analysis_kernel<WW, VV, kGroupWarps>, smem)) != 0) return rc;                                                \
         fft_analysis_kernel<WW, VV, kGroupWarps><<<grid, 32 * WW * kGroupWarps, smem, st>>>(x, X, pl.fft, pl.nlat, pl.Kh, nfields, ncp,     \
-                                                                                            pl.mmax, pl.d_mscale, pl.d_krow0, pl.zero_imag_edges, al, pl.d_err); \
+                                                                                            pl.mmax, pl.d_mscale, pl.zero_imag_edges, al, pl.d_err); \
     } while (0)
     if (vec == 1) {
         if (NW == 8) LAUNCH_A(8, 1);
@@ -980,7 +1011,7 @@ int launch_fft_synthesis(const Plan &pl, const float *Y, float *x, int nfields, 
     do {                                                                                                                                 \
         if ((rc = set_smem(fft_synthesis_kernel<WW, VV, kGroupWarps>, smem)) != 0) return rc;                                            \
         fft_synthesis_kernel<WW, VV, kGroupWarps><<<grid, 32 * WW * kGroupWarps, smem, st>>>(Y, x, pl.fft, pl.nlat, pl.Kh, nfields, ncp, \
-                                                                                             pl.mmax, pl.d_mscale, pl.d_krow0, al, pl.d_err); \
+                                                                                             pl.mmax, pl.d_mscale, al, pl.d_err); \
     } while (0)
     if (vec == 1) {
         if (NW == 8) LAUNCH_S(8, 1);
@@ -1011,7 +1042,7 @@ static int cached_fft(int nlon, FftPlanDev *fp) {
         if (c.n == nlon && c.device == dev) { *fp = c.fp; return SHTB200_OK; }
     for (auto &c : g_cache)
         if (c.n == 0) {
-            int rc = build_fft_plan(nlon, 0, kFftRows, &c.fp, &c.tw, &c.perm);
+            int rc = build_fft_plan(nlon, 0, kFftRows, nullptr, &c.fp, &c.tw, &c.perm);
             if (rc) return rc;
             c.n = nlon;
             c.device = dev;

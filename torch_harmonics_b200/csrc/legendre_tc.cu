@@ -14,7 +14,8 @@
 //               swizzled layout, so the pass is a straight elementwise sweep).
 //   warp 1      MMA issuer: per k-step three tcgen05.mma chains (A_lo B, A B_lo, A B; the tensor core reads
 //               fp32 words as TF32 by dropping the low mantissa bits), fp32 accumulation in one of two
-//               tensor-memory accumulators; tcgen05.commit releases stages, lo slots, A slots and accumulators.
+//               tensor-memory accumulators.  It waits on ONE barrier per k-step (both splitters done) and commits to
+//               ONE barrier per k-step (MMAs done), which everybody who recycles a stage, lo slot or A slot watches.
 //   warps 10-17 epilogue: tcgen05.ld of a finished accumulator while the next units are being multiplied,
 //               stores to the degree-slab array / coefficient array (analysis) or the latitude-row operand of the
 //               synthesis FFT.
@@ -53,8 +54,10 @@ constexpr int NSPLIT_A = 4, NSPLIT_B = 4, NSPLIT_WARPS = NSPLIT_A + NSPLIT_B, NE
 constexpr int NTHREADS = 32 * (2 + NSPLIT_WARPS + NEPI_WARPS);  // 576
 constexpr long long WAIT_LIMIT = 4000000000LL;                  // ~2 s of SM clock
 
-constexpr int NBARS = 2 * NSTAGE + 2 * NLO + 2 * NACC + 2 * NATM;
-constexpr int SMEM_BYTES = NSTAGE * STAGE_BYTES + NLO * B_TILE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+constexpr int NRING = 12;               // k-steps that own a (ready, done) barrier pair before it is reused: a multiple of NSTAGE, NLO and NATM
+constexpr int NBARS = NSTAGE + 2 * NRING + 2 * NACC;
+static_assert(NRING % NSTAGE == 0 && NRING % NLO == 0 && NRING % NATM == 0 && NRING >= 2 * NSTAGE, "ring sizes");
+constexpr int SMEM_BYTES = NSTAGE * STAGE_BYTES + NLO * B_TILE_BYTES + 1024 /* alignment slack */ + 512 /* barriers */;
 static_assert(NACC * BN_MAX + NATM * 2 * TK <= TMEM_COLS, "accumulators and the A ring must fit tensor memory");
 static_assert(kItemRowsMax == TILE_M, "one work item = one 128-row tensor-core tile");
 
@@ -73,7 +76,7 @@ __device__ __forceinline__ float tf32_hi(float x) { return __uint_as_float(__flo
 __device__ __forceinline__ float tf32_lo(float x) { return x - tf32_hi(x); }
 
 __global__ void __launch_bounds__(NTHREADS, 1)
-legendre_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const TcParams P) {
+legendre_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ TcParams P) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *base_ptr = smem_raw + (base - ptx::smem_u32(smem_raw));
@@ -81,14 +84,15 @@ legendre_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     const uint32_t lo0 = base + NSTAGE * STAGE_BYTES;
     const uint32_t bar0 = lo0 + NLO * B_TILE_BYTES;
     // barrier slots (8 bytes each)
+    // full[s]: the TMA boxes of ring stage s have landed.  ready[k % NRING]: both splitters are done with k-step k (it
+    // implies full).  done[k % NRING]: the MMAs of k-step k have completed; whoever wants to overwrite something k-step
+    // k read (stage: k + NSTAGE, lo slot: k + NLO, tensor-memory A slot: k + NATM) waits for it.  The MMA thread, which
+    // must never leave the tensor pipe idle, thus waits on one barrier and commits to one barrier per k-step.
     auto bar_full = [&](int s) { return bar0 + 8u * s; };
-    auto bar_empty = [&](int s) { return bar0 + 8u * (NSTAGE + s); };
-    auto bar_lofull = [&](int c) { return bar0 + 8u * (2 * NSTAGE + c); };
-    auto bar_loempty = [&](int c) { return bar0 + 8u * (2 * NSTAGE + NLO + c); };
-    auto bar_accfull = [&](int a) { return bar0 + 8u * (2 * NSTAGE + 2 * NLO + a); };
-    auto bar_accempty = [&](int a) { return bar0 + 8u * (2 * NSTAGE + 2 * NLO + NACC + a); };
-    auto bar_afull = [&](int t) { return bar0 + 8u * (2 * NSTAGE + 2 * NLO + 2 * NACC + t); };
-    auto bar_aempty = [&](int t) { return bar0 + 8u * (2 * NSTAGE + 2 * NLO + 2 * NACC + NATM + t); };
+    auto bar_ready = [&](int i) { return bar0 + 8u * (NSTAGE + i); };
+    auto bar_done = [&](int i) { return bar0 + 8u * (NSTAGE + NRING + i); };
+    auto bar_accfull = [&](int a) { return bar0 + 8u * (NSTAGE + 2 * NRING + a); };
+    auto bar_accempty = [&](int a) { return bar0 + 8u * (NSTAGE + 2 * NRING + NACC + a); };
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(base_ptr + NSTAGE * STAGE_BYTES + NLO * B_TILE_BYTES + 8 * NBARS);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
@@ -96,10 +100,9 @@ legendre_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     const GemmParams &gp = P.gp;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < NSTAGE; ++s) { ptx::mbar_init(bar_full(s), 1); ptx::mbar_init(bar_empty(s), 1); }
-        for (int c = 0; c < NLO; ++c) { ptx::mbar_init(bar_lofull(c), 32 * NSPLIT_B); ptx::mbar_init(bar_loempty(c), 1); }
-        for (int t = 0; t < NATM; ++t) { ptx::mbar_init(bar_afull(t), 32 * NSPLIT_A); ptx::mbar_init(bar_aempty(t), 1); }
-        for (int a = 0; a < NACC; ++a) { ptx::mbar_init(bar_accfull(a), 1); ptx::mbar_init(bar_accempty(a), 32 * NEPI_WARPS); }
+        for (int s = 0; s < NSTAGE; ++s) ptx::mbar_init(bar_full(s), 1);
+        for (int i = 0; i < NRING; ++i) { ptx::mbar_init(bar_ready(i), NSPLIT_WARPS); ptx::mbar_init(bar_done(i), 1); }
+        for (int a = 0; a < NACC; ++a) { ptx::mbar_init(bar_accfull(a), 1); ptx::mbar_init(bar_accempty(a), NEPI_WARPS); }
         *abort_flag = 0;
         ptx::fence_barrier_init();
         ptx::prefetch_tensormap(&tmA);
@@ -128,11 +131,17 @@ legendre_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         return w;
     };
 
+    // wait until the MMAs of k-step kc - depth have completed (nothing to wait for during the first `depth` k-steps)
+    auto wait_done = [&](int kc, int depth) {
+        if (kc < depth) return true;
+        const int q = kc - depth;
+        return ptx::mbar_wait_bounded(bar_done(q % NRING), (uint32_t)((q / NRING) & 1), abort_flag, WAIT_LIMIT);
+    };
+
     if (warp == 0) {
         // =========================== TMA producer ===========================
         if (lane == 0) {
-            int s = 0;
-            uint32_t ph = 0;
+            int s = 0, kc = 0;
             bool ok = true;
             const uint32_t bytes = (uint32_t)(A_TILE_BYTES + (gp.b_mn ? P.bblk * B_BLK_BYTES : P.bn * TK * 4));
             for (int u = blockIdx.x; u < P.nunits && ok; u += gridDim.x) {
@@ -142,7 +151,7 @@ legendre_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                                               : ((long long)w.it.b_y0 - gp.b_unit0) * gp.ncols + (long long)w.ntile * P.bn;
                 for (int ki = 0; ki < w.ksteps; ++ki) {
                     const int ks = ki + w.it.kfirst;  // slice of the operands
-                    if (!(ok = ptx::mbar_wait_bounded(bar_empty(s), ph ^ 1u, abort_flag, WAIT_LIMIT))) break;
+                    if (!(ok = wait_done(kc, NSTAGE))) break;
                     ptx::mbar_arrive_expect_tx(bar_full(s), bytes);
                     const uint32_t dst = stage0 + s * STAGE_BYTES;
                     ptx::tma_load_2d(dst, &tmA, row_packed_a ? ks * TK : 0, w.it.a_y0 + (row_packed_a ? 0 : ks * w.it.a_dy), bar_full(s));
@@ -154,17 +163,22 @@ legendre_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                         const long long by = by0 + (row_packed_b ? 0 : (long long)ks * w.it.b_dy * gp.ncols);
                         ptx::tma_load_2d(dst + B_OFF, &tmB, row_packed_b ? ks * TK : 0, (int)by, bar_full(s));
                     }
-                    if (++s == NSTAGE) { s = 0; ph ^= 1u; }
+                    if (++s == NSTAGE) s = 0;
+                    ++kc;
                 }
             }
         }
     } else if (warp == 1) {
         // =========================== MMA issuer ===========================
         if (lane == 0) {
-            int s = 0, c = 0, a = 0, t = 0;
-            uint32_t ph = 0, phc = 0, pha = 0, pht = 0;
+            int s = 0, c = 0, a = 0, t = 0, r = 0;
+            uint32_t pha = 0, phr = 0;
             bool ok = true;
             const uint32_t idesc = ptx::idesc_tf32_m128((uint32_t)P.bn) | (gp.b_mn ? (1u << 16) : 0u);  // bit 16: B is column (MN) major
+            // one MMA consumes 8 contraction indices: 8 columns of A in tensor memory; of B 32 bytes along a K-major row or
+            // one 8-row (1 KiB) group of a column-major tile
+            const uint64_t bstep = gp.b_mn ? (uint64_t)(1024 >> 4) : (uint64_t)(32 >> 4);
+            const bool b_mn = gp.b_mn != 0;
             for (int u = blockIdx.x; u < P.nunits && ok; u += gridDim.x) {
                 const Unit w = get_unit(u);
                 if (w.skip) continue;
@@ -173,17 +187,12 @@ legendre_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                 ptx::tc_fence_after();
                 const uint32_t d = tmem_base + (uint32_t)(a * BN_MAX);
                 for (int ks = 0; ks < w.ksteps; ++ks) {
-                    if (!(ok = ptx::mbar_wait_bounded(bar_full(s), ph, abort_flag, WAIT_LIMIT))) break;
-                    if (!(ok = ptx::mbar_wait_bounded(bar_lofull(c), phc, abort_flag, WAIT_LIMIT))) break;
-                    if (!(ok = ptx::mbar_wait_bounded(bar_afull(t), pht, abort_flag, WAIT_LIMIT))) break;
+                    if (!(ok = ptx::mbar_wait_bounded(bar_ready(r), phr, abort_flag, WAIT_LIMIT))) break;
                     ptx::tc_fence_after();
                     const uint32_t hi = stage0 + s * STAGE_BYTES, lo = lo0 + c * B_TILE_BYTES;
                     const uint32_t ah = tmem_base + (uint32_t)(A_TM_COL0 + t * 2 * TK), al = ah + TK;  // A as it is / its low part
-                    const uint64_t bh = gp.b_mn ? ptx::smem_desc_sw128_mn(hi + B_OFF, B_BLK_BYTES) : ptx::smem_desc_sw128(hi + B_OFF);
-                    const uint64_t bl = gp.b_mn ? ptx::smem_desc_sw128_mn(lo, B_BLK_BYTES) : ptx::smem_desc_sw128(lo);
-                    // one MMA consumes 8 contraction indices: 8 columns of A in tensor memory; of B 32 bytes along a K-major row or
-                    // one 8-row (1 KiB) group of a column-major tile
-                    const uint64_t bstep = gp.b_mn ? (uint64_t)(1024 >> 4) : (uint64_t)(32 >> 4);
+                    const uint64_t bh = b_mn ? ptx::smem_desc_sw128_mn(hi + B_OFF, B_BLK_BYTES) : ptx::smem_desc_sw128(hi + B_OFF);
+                    const uint64_t bl = b_mn ? ptx::smem_desc_sw128_mn(lo, B_BLK_BYTES) : ptx::smem_desc_sw128(lo);
 #pragma unroll
                     for (int k8 = 0; k8 < TK / 8; ++k8) {
                         const uint32_t koff = (uint32_t)(k8 * 8);
@@ -192,12 +201,11 @@ legendre_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                         ptx::mma_tf32_ta(d, ah + koff, bl + kb, idesc, 1u);
                         ptx::mma_tf32_ta(d, ah + koff, bh + kb, idesc, 1u);
                     }
-                    ptx::tc_commit(bar_empty(s));
-                    ptx::tc_commit(bar_loempty(c));
-                    ptx::tc_commit(bar_aempty(t));
-                    if (++s == NSTAGE) { s = 0; ph ^= 1u; }
-                    if (++c == NLO) { c = 0; phc ^= 1u; }
-                    if (++t == NATM) { t = 0; pht ^= 1u; }
+                    ptx::tc_commit(bar_done(r));
+                    if (++s == NSTAGE) s = 0;
+                    if (++c == NLO) c = 0;
+                    if (++t == NATM) t = 0;
+                    if (++r == NRING) { r = 0; phr ^= 1u; }
                 }
                 if (!ok) break;
                 ptx::tc_commit(bar_accfull(a));
@@ -208,15 +216,15 @@ legendre_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         // =========================== A splitter: shared memory -> tensor memory ===========================
         const int q = warp & 3;              // tensor-memory lane quarter this warp may write
         const int row = q * 32 + lane;       // row of the A tile = lane of tensor memory
-        int s = 0, t = 0;
-        uint32_t ph = 0, pht = 0;
+        int s = 0, t = 0, kc = 0;
+        uint32_t ph = 0;
         bool ok = true;
         for (int u = blockIdx.x; u < P.nunits && ok; u += gridDim.x) {
             const Unit w = get_unit(u);
             if (w.skip) continue;
             for (int ks = 0; ks < w.ksteps; ++ks) {
                 if (!(ok = ptx::mbar_wait_bounded(bar_full(s), ph, abort_flag, WAIT_LIMIT))) break;
-                if (!(ok = ptx::mbar_wait_bounded(bar_aempty(t), pht ^ 1u, abort_flag, WAIT_LIMIT))) break;
+                if (!(ok = wait_done(kc, NATM))) break;
                 ptx::tc_fence_after();
                 // row `row` of the 128-byte-swizzled tile: 16-byte chunk j sits at position j ^ (row & 7)
                 const uint8_t *arow = base_ptr + s * STAGE_BYTES + row * 128;
@@ -233,17 +241,19 @@ legendre_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                 ptx::tmem_st32(ta + TK, v);
                 ptx::tmem_st_wait();
                 ptx::tc_fence_before();
-                ptx::mbar_arrive(bar_afull(t));
+                __syncwarp();  // one arrival per warp
+                if (lane == 0) ptx::mbar_arrive(bar_ready(kc % NRING));
                 if (++s == NSTAGE) { s = 0; ph ^= 1u; }
-                if (++t == NATM) { t = 0; pht ^= 1u; }
+                if (++t == NATM) t = 0;
+                ++kc;
             }
         }
     } else if (warp < 2 + NSPLIT_WARPS) {
         // =========================== B splitter ===========================
         const int tid = threadIdx.x - 32 * (2 + NSPLIT_A);
         constexpr int NT = 32 * NSPLIT_B;
-        int s = 0, c = 0;
-        uint32_t ph = 0, phc = 0;
+        int s = 0, c = 0, kc = 0;
+        uint32_t ph = 0;
         bool ok = true;
         const int nb4 = (gp.b_mn ? P.bblk * B_BLK_BYTES : P.bn * TK * 4) / 16;
         for (int u = blockIdx.x; u < P.nunits && ok; u += gridDim.x) {
@@ -251,7 +261,7 @@ legendre_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             if (w.skip) continue;
             for (int ks = 0; ks < w.ksteps; ++ks) {
                 if (!(ok = ptx::mbar_wait_bounded(bar_full(s), ph, abort_flag, WAIT_LIMIT))) break;
-                if (!(ok = ptx::mbar_wait_bounded(bar_loempty(c), phc ^ 1u, abort_flag, WAIT_LIMIT))) break;
+                if (!(ok = wait_done(kc, NLO))) break;
                 float4 *src = reinterpret_cast<float4 *>(base_ptr + s * STAGE_BYTES + B_OFF);
                 float4 *dst = reinterpret_cast<float4 *>(base_ptr + NSTAGE * STAGE_BYTES + c * B_TILE_BYTES);
                 // all loads of a thread are issued before the first store
@@ -271,9 +281,11 @@ legendre_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                     }
                 }
                 ptx::fence_proxy_async_smem();
-                ptx::mbar_arrive(bar_lofull(c));
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(bar_ready(kc % NRING));
                 if (++s == NSTAGE) { s = 0; ph ^= 1u; }
-                if (++c == NLO) { c = 0; phc ^= 1u; }
+                if (++c == NLO) c = 0;
+                ++kc;
             }
         }
     } else {
@@ -352,7 +364,8 @@ legendre_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                 }
             }
             ptx::tc_fence_before();
-            ptx::mbar_arrive(bar_accempty(a));
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(bar_accempty(a));
             if (++a == NACC) { a = 0; pha ^= 1u; }
         }
     }

@@ -175,10 +175,19 @@ legendre_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             uint32_t pha = 0, phr = 0;
             bool ok = true;
             const uint32_t idesc = ptx::idesc_tf32_m128((uint32_t)P.bn) | (gp.b_mn ? (1u << 16) : 0u);  // bit 16: B is column (MN) major
-            // one MMA consumes 8 contraction indices: 8 columns of A in tensor memory; of B 32 bytes along a K-major row or
-            // one 8-row (1 KiB) group of a column-major tile
-            const uint64_t bstep = gp.b_mn ? (uint64_t)(1024 >> 4) : (uint64_t)(32 >> 4);
+            // One MMA consumes 8 contraction indices: 8 columns of A in tensor memory; of B 32 bytes along a K-major row or
+            // one 8-row (1 KiB) group of a column-major tile (in the 16-byte units of the descriptor's address field).
             const bool b_mn = gp.b_mn != 0;
+            const uint32_t bstep = b_mn ? (1024u >> 4) : (32u >> 4);
+            // descriptors of the B tiles: everything but the start address is the same for all of them
+            const uint64_t bdesc0 = b_mn ? ptx::smem_desc_sw128_mn(0, B_BLK_BYTES) : ptx::smem_desc_sw128(0);
+            const uint32_t b_hi32 = (uint32_t)(bdesc0 >> 32), b_lo_fixed = (uint32_t)bdesc0;
+            uint32_t b_raw_lo[NSTAGE], b_lo_lo[NLO];
+#pragma unroll
+            for (int i = 0; i < NSTAGE; ++i) b_raw_lo[i] = b_lo_fixed | (((stage0 + i * STAGE_BYTES + B_OFF) & 0x3FFFFu) >> 4);
+#pragma unroll
+            for (int i = 0; i < NLO; ++i) b_lo_lo[i] = b_lo_fixed | (((lo0 + i * B_TILE_BYTES) & 0x3FFFFu) >> 4);
+            const uint32_t a_tm0 = tmem_base + (uint32_t)A_TM_COL0;
             for (int u = blockIdx.x; u < P.nunits && ok; u += gridDim.x) {
                 const Unit w = get_unit(u);
                 if (w.skip) continue;
@@ -189,18 +198,13 @@ legendre_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                 for (int ks = 0; ks < w.ksteps; ++ks) {
                     if (!(ok = ptx::mbar_wait_bounded(bar_ready(r), phr, abort_flag, WAIT_LIMIT))) break;
                     ptx::tc_fence_after();
-                    const uint32_t hi = stage0 + s * STAGE_BYTES, lo = lo0 + c * B_TILE_BYTES;
-                    const uint32_t ah = tmem_base + (uint32_t)(A_TM_COL0 + t * 2 * TK), al = ah + TK;  // A as it is / its low part
-                    const uint64_t bh = b_mn ? ptx::smem_desc_sw128_mn(hi + B_OFF, B_BLK_BYTES) : ptx::smem_desc_sw128(hi + B_OFF);
-                    const uint64_t bl = b_mn ? ptx::smem_desc_sw128_mn(lo, B_BLK_BYTES) : ptx::smem_desc_sw128(lo);
+                    const uint32_t ah = a_tm0 + (uint32_t)(t * 2 * TK);  // A as it is; its low part TK columns further
+                    uint32_t brl = b_raw_lo[0], bll = b_lo_lo[0];  // (selects instead of indexed local arrays)
 #pragma unroll
-                    for (int k8 = 0; k8 < TK / 8; ++k8) {
-                        const uint32_t koff = (uint32_t)(k8 * 8);
-                        const uint64_t kb = bstep * k8;
-                        ptx::mma_tf32_ta(d, al + koff, bh + kb, idesc, (ks | k8) ? 1u : 0u);  // small terms first
-                        ptx::mma_tf32_ta(d, ah + koff, bl + kb, idesc, 1u);
-                        ptx::mma_tf32_ta(d, ah + koff, bh + kb, idesc, 1u);
-                    }
+                    for (int i = 1; i < NSTAGE; ++i) brl = (s == i) ? b_raw_lo[i] : brl;
+#pragma unroll
+                    for (int i = 1; i < NLO; ++i) bll = (c == i) ? b_lo_lo[i] : bll;
+                    ptx::mma_tf32_kstep32(d, ah, ah + TK, brl, bll, b_hi32, bstep, idesc, ks ? 1u : 0u);
                     ptx::tc_commit(bar_done(r));
                     if (++s == NSTAGE) s = 0;
                     if (++c == NLO) c = 0;

@@ -108,6 +108,57 @@ __device__ __forceinline__ void mma_tf32_ta(uint32_t d_tmem, uint32_t a_tmem, ui
         "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// One k-step of the split-TF32 contraction as ONE instruction sequence: 4 slices of 8 contraction indices, each with the
+// three products A_lo B, A B_lo, A B (small terms first).  A comes from tensor memory (`a_raw`, `a_lo`: column addresses,
+// +8 columns per slice), B from shared memory through descriptors whose high words are equal (`b_hi32`) and whose low
+// words (`b_raw_lo32`, `b_lo_lo32`) advance by `b_step` per slice.  `accumulate` = 0 makes the very first product
+// overwrite the accumulator.  Written as a single asm block because the issuing thread's scalar instruction latency,
+// not the tensor pipe, bounds the issue rate otherwise: this keeps it to two adds per operand and slice.
+__device__ __forceinline__ void mma_tf32_kstep32(uint32_t d_tmem, uint32_t a_raw, uint32_t a_lo, uint32_t b_raw_lo32, uint32_t b_lo_lo32, uint32_t b_hi32,
+                                                 uint32_t b_step, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p0, p1;\n\t"
+        ".reg .b32 ar1, ar2, ar3, al1, al2, al3, br1, br2, br3, bl1, bl2, bl3;\n\t"
+        ".reg .b64 dr0, dr1, dr2, dr3, dl0, dl1, dl2, dl3;\n\t"
+        "setp.ne.b32 p0, %8, 0;\n\t"
+        "setp.eq.b32 p1, %8, %8;\n\t"
+        "add.u32 ar1, %1, 8;\n\t"
+        "add.u32 ar2, %1, 16;\n\t"
+        "add.u32 ar3, %1, 24;\n\t"
+        "add.u32 al1, %2, 8;\n\t"
+        "add.u32 al2, %2, 16;\n\t"
+        "add.u32 al3, %2, 24;\n\t"
+        "add.u32 br1, %3, %6;\n\t"
+        "add.u32 br2, br1, %6;\n\t"
+        "add.u32 br3, br2, %6;\n\t"
+        "add.u32 bl1, %4, %6;\n\t"
+        "add.u32 bl2, bl1, %6;\n\t"
+        "add.u32 bl3, bl2, %6;\n\t"
+        "mov.b64 dr0, {%3, %5};\n\t"
+        "mov.b64 dl0, {%4, %5};\n\t"
+        "mov.b64 dr1, {br1, %5};\n\t"
+        "mov.b64 dl1, {bl1, %5};\n\t"
+        "mov.b64 dr2, {br2, %5};\n\t"
+        "mov.b64 dl2, {bl2, %5};\n\t"
+        "mov.b64 dr3, {br3, %5};\n\t"
+        "mov.b64 dl3, {bl3, %5};\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%2], dr0, %7, p0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], dl0, %7, p1;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], dr0, %7, p1;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [al1], dr1, %7, p1;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [ar1], dl1, %7, p1;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [ar1], dr1, %7, p1;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [al2], dr2, %7, p1;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [ar2], dl2, %7, p1;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [ar2], dr2, %7, p1;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [al3], dr3, %7, p1;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [ar3], dl3, %7, p1;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [ar3], dr3, %7, p1;\n\t"
+        "}" ::"r"(d_tmem),
+        "r"(a_raw), "r"(a_lo), "r"(b_raw_lo32), "r"(b_lo_lo32), "r"(b_hi32), "r"(b_step), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
 // 32 lanes x 32 consecutive 32-bit columns <- 32 registers per thread (lane = thread); completion by tmem_st_wait()
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float *v) {
     asm volatile(

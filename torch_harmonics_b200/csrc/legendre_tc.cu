@@ -6,12 +6,12 @@
 // walks a longest-first list of work units (128-row item, column tile):
 //
 //   warp 0      TMA producer: cp.async.bulk.tensor loads of one 128 x 32 A tile and one B tile per k-step into a
-//               4-deep ring of 128-byte-swizzled shared-memory stages (full/empty mbarriers).
+//               5-deep ring of 128-byte-swizzled shared-memory stages (full/empty mbarriers).
 //   warps 2-5   A splitter, one warp per tensor-memory lane quarter: a thread reads its row of the landed A tile and
 //               stores it twice into a 3-deep ring in TENSOR MEMORY, as it is and as lo = x - tf32_trunc(x)
 //               (tcgen05.st), so the table never occupies shared-memory bandwidth again: the MMAs take A from there.
-//   warps 6-9   B splitter: lo = x - tf32_trunc(x) of the B tile into one of three shared-memory "lo" slots (same
-//               swizzled layout, so the pass is a straight elementwise sweep).
+//   warps 6-9   B splitter: lo = x - tf32_trunc(x) of the B tile, written over the region of the stage the A tile came in
+//               (same swizzled layout as the B tile, so the pass is a straight elementwise sweep).
 //   warp 1      MMA issuer: per k-step three tcgen05.mma chains (A_lo B, A B_lo, A B; the tensor core reads
 //               fp32 words as TF32 by dropping the low mantissa bits), fp32 accumulation in one of two
 //               tensor-memory accumulators.  It waits on ONE barrier per k-step (both splitters done) and commits to
@@ -39,14 +39,18 @@ namespace {
 constexpr int TK = kBK;                // floats per k-step: one 128-byte swizzle row
 constexpr int TILE_M = 128;
 constexpr int BN_MAX = 160;
-constexpr int NSTAGE = 4;              // TMA ring
-constexpr int NLO = 4;                 // shared-memory slots for the low-order part of B
+constexpr int NSTAGE = 5;              // TMA ring
 constexpr int NACC = 2;                // accumulator buffers in tensor memory
 constexpr int NATM = 3;                // A slots in tensor memory (raw + lo: 2 x 32 columns each)
 constexpr int A_TILE_BYTES = TILE_M * TK * 4;                // 16 KiB
 constexpr int B_TILE_BYTES = BN_MAX * TK * 4;                // 20 KiB
-constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;     // 36 KiB
-constexpr int B_OFF = A_TILE_BYTES;
+// A stage is two 20 KiB regions.  The first receives the A tile (16 KiB); once the A splitter has moved it to tensor
+// memory the B splitter overwrites the region with the low-order part of B.  The second holds the B tile as loaded.
+// Sharing the region is what buys the fifth stage: the ring's depth times the bytes of a stage has to cover the
+// latency from "MMAs done" through the refill (HBM / L2) and both splitters back to "ready".
+constexpr int STAGE_BYTES = 2 * B_TILE_BYTES;                // 40 KiB
+constexpr int B_OFF = B_TILE_BYTES;
+static_assert(A_TILE_BYTES <= B_TILE_BYTES, "the A tile shares the region of B's low-order part");
 constexpr int B_BLK_BYTES = 32 * TK * 4;  // column-contiguous B: one 32 (k) x 32 (columns) block, 4 KiB
 constexpr int TMEM_COLS = 512;
 constexpr int A_TM_COL0 = NACC * BN_MAX;  // first tensor-memory column of the A ring
@@ -54,10 +58,10 @@ constexpr int NSPLIT_A = 4, NSPLIT_B = 4, NSPLIT_WARPS = NSPLIT_A + NSPLIT_B, NE
 constexpr int NTHREADS = 32 * (2 + NSPLIT_WARPS + NEPI_WARPS);  // 576
 constexpr long long WAIT_LIMIT = 4000000000LL;                  // ~2 s of SM clock
 
-constexpr int NRING = 12;               // k-steps that own a (ready, done) barrier pair before it is reused: a multiple of NSTAGE, NLO and NATM
-constexpr int NBARS = NSTAGE + 2 * NRING + 2 * NACC;
-static_assert(NRING % NSTAGE == 0 && NRING % NLO == 0 && NRING % NATM == 0 && NRING >= 2 * NSTAGE, "ring sizes");
-constexpr int SMEM_BYTES = NSTAGE * STAGE_BYTES + NLO * B_TILE_BYTES + 1024 /* alignment slack */ + 512 /* barriers */;
+constexpr int NRING = 15;               // k-steps that own a (ready, done) barrier pair before it is reused: a multiple of NSTAGE and NATM
+constexpr int NBARS = 2 * NSTAGE + 2 * NRING + 2 * NACC;
+static_assert(NRING % NSTAGE == 0 && NRING % NATM == 0 && NRING >= 2 * NSTAGE, "ring sizes");
+constexpr int SMEM_BYTES = NSTAGE * STAGE_BYTES + 1024 /* alignment slack */ + 512 /* barriers */;
 static_assert(NACC * BN_MAX + NATM * 2 * TK <= TMEM_COLS, "accumulators and the A ring must fit tensor memory");
 static_assert(kItemRowsMax == TILE_M, "one work item = one 128-row tensor-core tile");
 
@@ -81,26 +85,27 @@ legendre_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     const uint32_t base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t *base_ptr = smem_raw + (base - ptx::smem_u32(smem_raw));
     const uint32_t stage0 = base;
-    const uint32_t lo0 = base + NSTAGE * STAGE_BYTES;
-    const uint32_t bar0 = lo0 + NLO * B_TILE_BYTES;
+    const uint32_t bar0 = base + NSTAGE * STAGE_BYTES;
     // barrier slots (8 bytes each)
     // full[s]: the TMA boxes of ring stage s have landed.  ready[k % NRING]: both splitters are done with k-step k (it
     // implies full).  done[k % NRING]: the MMAs of k-step k have completed; whoever wants to overwrite something k-step
-    // k read (stage: k + NSTAGE, lo slot: k + NLO, tensor-memory A slot: k + NATM) waits for it.  The MMA thread, which
+    // k read (stage: k + NSTAGE, tensor-memory A slot: k + NATM) waits for it.  aread[s]: the A splitter has read the A tile of
+    // stage s out of shared memory (the B splitter may now overwrite that region).  The MMA thread, which
     // must never leave the tensor pipe idle, thus waits on one barrier and commits to one barrier per k-step.
     auto bar_full = [&](int s) { return bar0 + 8u * s; };
-    auto bar_ready = [&](int i) { return bar0 + 8u * (NSTAGE + i); };
-    auto bar_done = [&](int i) { return bar0 + 8u * (NSTAGE + NRING + i); };
-    auto bar_accfull = [&](int a) { return bar0 + 8u * (NSTAGE + 2 * NRING + a); };
-    auto bar_accempty = [&](int a) { return bar0 + 8u * (NSTAGE + 2 * NRING + NACC + a); };
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(base_ptr + NSTAGE * STAGE_BYTES + NLO * B_TILE_BYTES + 8 * NBARS);
+    auto bar_aread = [&](int s) { return bar0 + 8u * (NSTAGE + s); };
+    auto bar_ready = [&](int i) { return bar0 + 8u * (2 * NSTAGE + i); };
+    auto bar_done = [&](int i) { return bar0 + 8u * (2 * NSTAGE + NRING + i); };
+    auto bar_accfull = [&](int a) { return bar0 + 8u * (2 * NSTAGE + 2 * NRING + a); };
+    auto bar_accempty = [&](int a) { return bar0 + 8u * (2 * NSTAGE + 2 * NRING + NACC + a); };
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(base_ptr + NSTAGE * STAGE_BYTES + 8 * NBARS);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const GemmParams &gp = P.gp;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < NSTAGE; ++s) ptx::mbar_init(bar_full(s), 1);
+        for (int s = 0; s < NSTAGE; ++s) { ptx::mbar_init(bar_full(s), 1); ptx::mbar_init(bar_aread(s), NSPLIT_A); }
         for (int i = 0; i < NRING; ++i) { ptx::mbar_init(bar_ready(i), NSPLIT_WARPS); ptx::mbar_init(bar_done(i), 1); }
         for (int a = 0; a < NACC; ++a) { ptx::mbar_init(bar_accfull(a), 1); ptx::mbar_init(bar_accempty(a), NEPI_WARPS); }
         *abort_flag = 0;
@@ -171,7 +176,7 @@ legendre_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     } else if (warp == 1) {
         // =========================== MMA issuer ===========================
         if (lane == 0) {
-            int s = 0, c = 0, a = 0, t = 0, r = 0;
+            int s = 0, a = 0, t = 0, r = 0;
             uint32_t pha = 0, phr = 0;
             bool ok = true;
             const uint32_t idesc = ptx::idesc_tf32_m128((uint32_t)P.bn) | (gp.b_mn ? (1u << 16) : 0u);  // bit 16: B is column (MN) major
@@ -182,11 +187,12 @@ legendre_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             // descriptors of the B tiles: everything but the start address is the same for all of them
             const uint64_t bdesc0 = b_mn ? ptx::smem_desc_sw128_mn(0, B_BLK_BYTES) : ptx::smem_desc_sw128(0);
             const uint32_t b_hi32 = (uint32_t)(bdesc0 >> 32), b_lo_fixed = (uint32_t)bdesc0;
-            uint32_t b_raw_lo[NSTAGE], b_lo_lo[NLO];
+            uint32_t b_raw_lo[NSTAGE], b_lo_lo[NSTAGE];
 #pragma unroll
-            for (int i = 0; i < NSTAGE; ++i) b_raw_lo[i] = b_lo_fixed | (((stage0 + i * STAGE_BYTES + B_OFF) & 0x3FFFFu) >> 4);
-#pragma unroll
-            for (int i = 0; i < NLO; ++i) b_lo_lo[i] = b_lo_fixed | (((lo0 + i * B_TILE_BYTES) & 0x3FFFFu) >> 4);
+            for (int i = 0; i < NSTAGE; ++i) {
+                b_raw_lo[i] = b_lo_fixed | (((stage0 + i * STAGE_BYTES + B_OFF) & 0x3FFFFu) >> 4);
+                b_lo_lo[i] = b_lo_fixed | (((stage0 + i * STAGE_BYTES) & 0x3FFFFu) >> 4);
+            }
             const uint32_t a_tm0 = tmem_base + (uint32_t)A_TM_COL0;
             for (int u = blockIdx.x; u < P.nunits && ok; u += gridDim.x) {
                 const Unit w = get_unit(u);
@@ -201,13 +207,13 @@ legendre_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                     const uint32_t ah = a_tm0 + (uint32_t)(t * 2 * TK);  // A as it is; its low part TK columns further
                     uint32_t brl = b_raw_lo[0], bll = b_lo_lo[0];  // (selects instead of indexed local arrays)
 #pragma unroll
-                    for (int i = 1; i < NSTAGE; ++i) brl = (s == i) ? b_raw_lo[i] : brl;
-#pragma unroll
-                    for (int i = 1; i < NLO; ++i) bll = (c == i) ? b_lo_lo[i] : bll;
+                    for (int i = 1; i < NSTAGE; ++i) {
+                        brl = (s == i) ? b_raw_lo[i] : brl;
+                        bll = (s == i) ? b_lo_lo[i] : bll;
+                    }
                     ptx::mma_tf32_kstep32(d, ah, ah + TK, brl, bll, b_hi32, bstep, idesc, ks ? 1u : 0u);
                     ptx::tc_commit(bar_done(r));
                     if (++s == NSTAGE) s = 0;
-                    if (++c == NLO) c = 0;
                     if (++t == NATM) t = 0;
                     if (++r == NRING) { r = 0; phr ^= 1u; }
                 }
@@ -228,8 +234,6 @@ legendre_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             if (w.skip) continue;
             for (int ks = 0; ks < w.ksteps; ++ks) {
                 if (!(ok = ptx::mbar_wait_bounded(bar_full(s), ph, abort_flag, WAIT_LIMIT))) break;
-                if (!(ok = wait_done(kc, NATM))) break;
-                ptx::tc_fence_after();
                 // row `row` of the 128-byte-swizzled tile: 16-byte chunk j sits at position j ^ (row & 7)
                 const uint8_t *arow = base_ptr + s * STAGE_BYTES + row * 128;
                 float v[TK];
@@ -238,6 +242,10 @@ legendre_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                     const float4 x = *reinterpret_cast<const float4 *>(arow + ((j ^ (row & 7)) << 4));
                     v[4 * j] = x.x, v[4 * j + 1] = x.y, v[4 * j + 2] = x.z, v[4 * j + 3] = x.w;
                 }
+                __syncwarp();  // the tile is in registers: its region of the stage may be overwritten
+                if (lane == 0) ptx::mbar_arrive(bar_aread(s));
+                if (!(ok = wait_done(kc, NATM))) break;
+                ptx::tc_fence_after();
                 const uint32_t ta = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(A_TM_COL0 + t * 2 * TK);
                 ptx::tmem_st32(ta, v);
 #pragma unroll
@@ -256,7 +264,7 @@ legendre_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         // =========================== B splitter ===========================
         const int tid = threadIdx.x - 32 * (2 + NSPLIT_A);
         constexpr int NT = 32 * NSPLIT_B;
-        int s = 0, c = 0, kc = 0;
+        int s = 0, kc = 0;
         uint32_t ph = 0;
         bool ok = true;
         const int nb4 = (gp.b_mn ? P.bblk * B_BLK_BYTES : P.bn * TK * 4) / 16;
@@ -265,9 +273,8 @@ legendre_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             if (w.skip) continue;
             for (int ks = 0; ks < w.ksteps; ++ks) {
                 if (!(ok = ptx::mbar_wait_bounded(bar_full(s), ph, abort_flag, WAIT_LIMIT))) break;
-                if (!(ok = wait_done(kc, NLO))) break;
                 float4 *src = reinterpret_cast<float4 *>(base_ptr + s * STAGE_BYTES + B_OFF);
-                float4 *dst = reinterpret_cast<float4 *>(base_ptr + NSTAGE * STAGE_BYTES + c * B_TILE_BYTES);
+                float4 *dst = reinterpret_cast<float4 *>(base_ptr + s * STAGE_BYTES);  // the region the A tile arrived in
                 // all loads of a thread are issued before the first store
                 constexpr int PER = (B_TILE_BYTES / 16 + NT - 1) / NT;
                 float4 v[PER];
@@ -276,19 +283,26 @@ legendre_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                     const int i = tid + j * NT;
                     if (i < nb4) v[j] = src[i];
                 }
+                if (P.write_hi) {
+#pragma unroll
+                    for (int j = 0; j < PER; ++j) {
+                        const int i = tid + j * NT;
+                        if (i < nb4) src[i] = make_float4(tf32_hi(v[j].x), tf32_hi(v[j].y), tf32_hi(v[j].z), tf32_hi(v[j].w));
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < PER; ++j) v[j] = make_float4(tf32_lo(v[j].x), tf32_lo(v[j].y), tf32_lo(v[j].z), tf32_lo(v[j].w));
+                // the A splitter must have taken the A tile out of the region first
+                if (!(ok = ptx::mbar_wait_bounded(bar_aread(s), ph, abort_flag, WAIT_LIMIT))) break;
 #pragma unroll
                 for (int j = 0; j < PER; ++j) {
                     const int i = tid + j * NT;
-                    if (i < nb4) {
-                        dst[i] = make_float4(tf32_lo(v[j].x), tf32_lo(v[j].y), tf32_lo(v[j].z), tf32_lo(v[j].w));
-                        if (P.write_hi) src[i] = make_float4(tf32_hi(v[j].x), tf32_hi(v[j].y), tf32_hi(v[j].z), tf32_hi(v[j].w));
-                    }
+                    if (i < nb4) dst[i] = v[j];
                 }
                 ptx::fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(bar_ready(kc % NRING));
                 if (++s == NSTAGE) { s = 0; ph ^= 1u; }
-                if (++c == NLO) c = 0;
                 ++kc;
             }
         }

@@ -141,12 +141,12 @@ def kernel_bytes(nf, table_fwd_bytes, table_inv_bytes, slabs):
 # The FFT and transpose kernels only stream per-field data; the Legendre kernels also read the packed table once per
 # launch, so their figure holds for the captured field count only.
 NCU_TRAFFIC = {
-    "fft_analysis": (132.98e6 + 62.55e6, 32, True),
-    "fft_synthesis": (98.67e6 + 86.32e6, 32, True),
-    "pack_coeffs": (67.86e6 + 26.47e6, 32, True),
-    "unpack_coeffs": (72.31e6 + 77.94e6, 32, True),
-    "legendre_analysis": (611.81e6 + 136.64e6, 73, False),
-    "legendre_synthesis": (551.93e6 + 199.38e6, 73, False),
+    "fft_analysis": (132.96e6 + 64.42e6, 32, True),
+    "fft_synthesis": (98.66e6 + 87.81e6, 32, True),
+    "pack_coeffs": (67.86e6 + 26.12e6, 32, True),
+    "unpack_coeffs": (72.31e6 + 78.94e6, 32, True),
+    "legendre_analysis": (611.80e6 + 135.90e6, 73, False),
+    "legendre_synthesis": (551.98e6 + 198.46e6, 73, False),
 }
 
 

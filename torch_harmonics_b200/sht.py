@@ -7,7 +7,10 @@ methods run hand-written sm_100a kernels through the C ABI in ``include/shtb200.
 tensors (float32 on the grid side, complex64 on the spectral side) — there is no CPU or PyTorch fallback.
 """
 
+import itertools
 import os
+import weakref
+from typing import List
 
 import torch
 import torch.nn as nn
@@ -31,6 +34,7 @@ class _ShtOp:
         self.table_name = table_name
         self.vector = vector
         self.plans = {}
+        _register_op(self)
 
     def plan(self, device, adjoint):
         key = (device.index, adjoint, self.module.engine)
@@ -62,24 +66,63 @@ def _run(plan, x, out_tail, out_dtype, nfields):
     return out
 
 
-class _LinearTransform(torch.autograd.Function):
-    """y = A x for a real-linear map A realised by one plan; the gradient is A^T g, realised by the partner
-    plan, and differentiating that again lands back on A (any order of differentiation works)."""
+# The transforms are exposed to PyTorch as ONE custom operator, so that modules that use them stay traceable by
+# torch.compile (fake implementation for shape / dtype inference, autograd registered on the operator).  Non-tensor
+# state (the pair of plans) is looked up through an integer handle.
+_OPS = weakref.WeakValueDictionary()
+_HANDLES = itertools.count(1)
+
+
+def _register_op(op):
+    op.handle = next(_HANDLES)
+    _OPS[op.handle] = op
+    return op.handle
+
+
+@torch.library.custom_op("shtb200::linear_transform", mutates_args=(), device_types="cuda")
+def _linear_transform(x: torch.Tensor, handle: int, adjoint: bool, out_tail: List[int], out_complex: bool, lead_dims: int) -> torch.Tensor:
+    """y = A x for the real-linear map A of plan pair `handle` (its transpose when `adjoint`)."""
+    op = _OPS[handle]
+    xc = x.contiguous()
+    nfields = 1
+    for s in xc.shape[:lead_dims]:
+        nfields *= s
+    return _run(op.plan(xc.device, adjoint), xc, tuple(out_tail), torch.complex64 if out_complex else torch.float32, nfields)
+
+
+@_linear_transform.register_fake
+def _(x, handle, adjoint, out_tail, out_complex, lead_dims):
+    return x.new_empty(tuple(x.shape[:lead_dims]) + tuple(out_tail), dtype=torch.complex64 if out_complex else torch.float32)
+
+
+def _lt_setup(ctx, inputs, output):
+    x, handle, adjoint, out_tail, out_complex, lead_dims = inputs
+    ctx.handle, ctx.adjoint, ctx.lead_dims = handle, adjoint, lead_dims
+    ctx.in_tail, ctx.in_complex = [int(v) for v in x.shape[lead_dims:]], x.is_complex()
+
+
+def _lt_backward(ctx, g):
+    # the gradient is A^T g, realised by the partner plan; differentiating that again lands back on A
+    gx = _linear_transform(g, ctx.handle, not ctx.adjoint, ctx.in_tail, ctx.in_complex, ctx.lead_dims)
+    return gx, None, None, None, None, None
+
+
+_linear_transform.register_autograd(_lt_backward, setup_context=_lt_setup)
+
+
+class _LinearTransform:
+    """Call shim with the signature the modules use."""
 
     @staticmethod
-    def forward(ctx, x, op, adjoint, out_tail, out_dtype, lead_dims):
-        ctx.op, ctx.adjoint = op, adjoint
-        ctx.in_tail, ctx.in_dtype, ctx.lead_dims = tuple(x.shape[lead_dims:]), x.dtype, lead_dims
-        xc = x.contiguous()
-        nfields = 1
-        for s in xc.shape[:lead_dims]:
-            nfields *= s
-        return _run(op.plan(xc.device, adjoint), xc, out_tail, out_dtype, nfields)
+    def apply(x, op, adjoint, out_tail, out_dtype, lead_dims):
+        return _linear_transform(x, op.handle, adjoint, [int(v) for v in out_tail], out_dtype == torch.complex64, lead_dims)
 
-    @staticmethod
-    def backward(ctx, g):
-        gx = _LinearTransform.apply(g, ctx.op, not ctx.adjoint, ctx.in_tail, ctx.in_dtype, ctx.lead_dims)
-        return gx, None, None, None, None, None
+
+def _check(cond, message):
+    """torch._check with the reference's messages (RuntimeError), written as a plain branch: the message closures
+    refer to the input tensor, which torch.compile does not accept inside torch._check."""
+    if not cond:
+        raise RuntimeError(message())
 
 
 def _require(x, dtype, what):
@@ -142,9 +185,9 @@ class RealSHT(_ShtBase):
         self._op = _ShtOp(self, _lib.SHT, _lib.SHT_ADJOINT, "weights", False)
 
     def forward(self, x: torch.Tensor):
-        torch._check(x.dim() >= 2, lambda: f"Expected tensor with at least 2 dimensions but got {x.dim()} instead")
-        torch._check(x.shape[-2] == self.nlat, lambda: f"Expected latitudes shape[-2]=={self.nlat}, got {x.shape[-2]}")
-        torch._check(x.shape[-1] == self.nlon, lambda: f"Expected longitudes shape[-1]=={self.nlon}, got {x.shape[-1]}")
+        _check(x.dim() >= 2, lambda: f"Expected tensor with at least 2 dimensions but got {x.dim()} instead")
+        _check(x.shape[-2] == self.nlat, lambda: f"Expected latitudes shape[-2]=={self.nlat}, got {x.shape[-2]}")
+        _check(x.shape[-1] == self.nlon, lambda: f"Expected longitudes shape[-1]=={self.nlon}, got {x.shape[-1]}")
         _require(x, torch.float32, "RealSHT")
         return _LinearTransform.apply(x, self._op, False, (self.lmax, self.mmax), torch.complex64, x.dim() - 2)
 
@@ -165,9 +208,9 @@ class InverseRealSHT(_ShtBase):
         self._op = _ShtOp(self, _lib.ISHT, _lib.ISHT_ADJOINT, "pct", False)
 
     def forward(self, x: torch.Tensor):
-        torch._check(x.dim() >= 2, lambda: f"Expected tensor with at least 2 dimensions but got {x.dim()} instead")
-        torch._check(x.shape[-2] == self.lmax, lambda: f"Expected spherical harmonic degrees (lmax) shape[-2]=={self.lmax}, got {x.shape[-2]}")
-        torch._check(x.shape[-1] == self.mmax, lambda: f"Expected spherical harmonic orders (mmax) shape[-1]=={self.mmax}, got {x.shape[-1]}")
+        _check(x.dim() >= 2, lambda: f"Expected tensor with at least 2 dimensions but got {x.dim()} instead")
+        _check(x.shape[-2] == self.lmax, lambda: f"Expected spherical harmonic degrees (lmax) shape[-2]=={self.lmax}, got {x.shape[-2]}")
+        _check(x.shape[-1] == self.mmax, lambda: f"Expected spherical harmonic orders (mmax) shape[-1]=={self.mmax}, got {x.shape[-1]}")
         _require(x, torch.complex64, "InverseRealSHT")
         return _LinearTransform.apply(x, self._op, False, (self.nlat, self.nlon), torch.float32, x.dim() - 2)
 
@@ -196,10 +239,10 @@ class RealVectorSHT(_ShtBase):
         self._op = _ShtOp(self, _lib.VSHT, _lib.VSHT_ADJOINT, "weights", True)
 
     def forward(self, x: torch.Tensor):
-        torch._check(x.dim() >= 3, lambda: f"Expected tensor with at least 3 dimensions but got {x.dim()} instead")
-        torch._check(x.shape[-3] == 2, lambda: f"Expected vector field shape[-3]==2, got {x.shape[-3]}")
-        torch._check(x.shape[-2] == self.nlat, lambda: f"Expected latitudes shape[-2]=={self.nlat}, got {x.shape[-2]}")
-        torch._check(x.shape[-1] == self.nlon, lambda: f"Expected longitudes shape[-1]=={self.nlon}, got {x.shape[-1]}")
+        _check(x.dim() >= 3, lambda: f"Expected tensor with at least 3 dimensions but got {x.dim()} instead")
+        _check(x.shape[-3] == 2, lambda: f"Expected vector field shape[-3]==2, got {x.shape[-3]}")
+        _check(x.shape[-2] == self.nlat, lambda: f"Expected latitudes shape[-2]=={self.nlat}, got {x.shape[-2]}")
+        _check(x.shape[-1] == self.nlon, lambda: f"Expected longitudes shape[-1]=={self.nlon}, got {x.shape[-1]}")
         _require(x, torch.float32, "RealVectorSHT")
         return _LinearTransform.apply(x, self._op, False, (2, self.lmax, self.mmax), torch.complex64, x.dim() - 3)
 
@@ -220,9 +263,9 @@ class InverseRealVectorSHT(_ShtBase):
         self._op = _ShtOp(self, _lib.IVSHT, _lib.IVSHT_ADJOINT, "dpct", True)
 
     def forward(self, x: torch.Tensor):
-        torch._check(x.dim() >= 3, lambda: f"Expected tensor with at least 3 dimensions but got {x.dim()} instead")
-        torch._check(x.shape[-3] == 2, lambda: f"Expected vector field shape[-3]==2, got {x.shape[-3]}")
-        torch._check(x.shape[-2] == self.lmax, lambda: f"Expected spherical harmonic degrees (lmax) shape[-2]=={self.lmax}, got {x.shape[-2]}")
-        torch._check(x.shape[-1] == self.mmax, lambda: f"Expected spherical harmonic orders (mmax) shape[-1]=={self.mmax}, got {x.shape[-1]}")
+        _check(x.dim() >= 3, lambda: f"Expected tensor with at least 3 dimensions but got {x.dim()} instead")
+        _check(x.shape[-3] == 2, lambda: f"Expected vector field shape[-3]==2, got {x.shape[-3]}")
+        _check(x.shape[-2] == self.lmax, lambda: f"Expected spherical harmonic degrees (lmax) shape[-2]=={self.lmax}, got {x.shape[-2]}")
+        _check(x.shape[-1] == self.mmax, lambda: f"Expected spherical harmonic orders (mmax) shape[-1]=={self.mmax}, got {x.shape[-1]}")
         _require(x, torch.complex64, "InverseRealVectorSHT")
         return _LinearTransform.apply(x, self._op, False, (2, self.nlat, self.nlon), torch.float32, x.dim() - 3)

@@ -692,7 +692,7 @@ __global__ void __launch_bounds__(32 * NW * G, (NW * G >= 16) ? 2 : 1) fft_analy
     }
     if (!tables_wait(tab_bar, err)) return;  // (CTA-wide barrier: rows in place as well)
 
-    {
+    if (t < nvalid) {  // (a transform without a field holds zeros and stays zeros)
         float *re = data + (size_t)t * TS;
         fft_group<false, G>(CxSplit{re, re + IO}, fp, tw_s, lane, 1 + t);
     }
@@ -849,7 +849,7 @@ __global__ void __launch_bounds__(32 * NW * G, (NW * G >= 16) ? 2 : 1) fft_synth
     }
     __syncthreads();
 
-    fft_group<true, G>(CxPacked{data + (size_t)t * np}, fp, tw_s, lane, 1 + t);
+    if (f0 + t / VEC < nfields) fft_group<true, G>(CxPacked{data + (size_t)t * np}, fp, tw_s, lane, 1 + t);  // (rows of a transform without a field are not stored)
 
     // ---- each group stores its own pair of rows ----
     {

@@ -181,7 +181,7 @@ enum { kFftRows = 0, kFftSplit = 1, kFftPacked = 2 };  // shared-memory layout t
 // krow0 (2 mmax_emit entries, may be null): first latitude row of every (order, parity) group that the contraction touches
 int build_fft_plan(int nlon, int mmax_emit, int layout, const int *krow0, FftPlanDev *out, float2 **d_tw, unsigned short **d_perm);
 
-// analysis: rows of x -> folded, order-major operand X[blocked_row(group, k)][col] (row pitch round_up(ncols, 4))
+// analysis: rows of x -> folded, order-major operand X[blocked_row(group, k)][col] (row pitch col_pitch(ncols))
 int launch_fft_analysis(const Plan &pl, const float *x, float *X, int nfields, cudaStream_t st);
 // synthesis: Y[blocked_row(group, k')][col] -> rows of x
 int launch_fft_synthesis(const Plan &pl, const float *Y, float *x, int nfields, cudaStream_t st);

@@ -6,7 +6,7 @@
 // walks a longest-first list of work units (128-row item, column tile):
 //
 //   warp 0      TMA producer: cp.async.bulk.tensor loads of one 128 x 32 A tile and one B tile per k-step into a
-//               5-deep ring of 128-byte-swizzled shared-memory stages (full/empty mbarriers).
+//               5-deep ring of 128-byte-swizzled shared-memory stages.
 //   warps 2-5   A splitter, one warp per tensor-memory lane quarter: a thread reads its row of the landed A tile and
 //               stores it twice into a 3-deep ring in TENSOR MEMORY, as it is and as lo = x - tf32_trunc(x)
 //               (tcgen05.st), so the table never occupies shared-memory bandwidth again: the MMAs take A from there.
@@ -15,7 +15,7 @@
 //   warp 1      MMA issuer: per k-step three tcgen05.mma chains (A_lo B, A B_lo, A B; the tensor core reads
 //               fp32 words as TF32 by dropping the low mantissa bits), fp32 accumulation in one of two
 //               tensor-memory accumulators.  It waits on ONE barrier per k-step (both splitters done) and commits to
-//               ONE barrier per k-step (MMAs done), which everybody who recycles a stage, lo slot or A slot watches.
+//               ONE barrier per k-step (MMAs done), which everybody who recycles a stage or an A slot watches.
 //   warps 10-17 epilogue: tcgen05.ld of a finished accumulator while the next units are being multiplied,
 //               stores to the degree-slab array / coefficient array (analysis) or the latitude-row operand of the
 //               synthesis FFT.

@@ -180,12 +180,14 @@ __global__ void __launch_bounds__(256) coeff_slab_transpose_kernel(float2 *__res
     if (TO_SLABS) {
         // all twelve loads of a thread are in flight before the first store
         float2 v[kTileRows / 8];
+        const float2 *crow = c + ((size_t)f * lmax + lbase + warp) * mloc + mi_l;  // row ll = warp, then 8 rows further per step
+        const int d0 = warp - lane, lrem = lmax - lbase - warp;                    // d = l - m - 64 sb; rows left below lmax
+        const bool colok = mi_l < mloc;
 #pragma unroll
         for (int it = 0; it < kTileRows / 8; ++it) {
-            const int ll = warp + 8 * it;
-            const int l = lbase + ll, d = ll - lane;  // d = l - m - 64 sb
+            const int d = d0 + 8 * it;
             v[it] = make_float2(0.f, 0.f);
-            if (d >= 0 && d < 64 && l < lmax && mi_l < mloc) v[it] = __ldg(c + ((size_t)f * lmax + l) * mloc + mi_l);
+            if (colok && d >= 0 && d < 64 && 8 * it < lrem) v[it] = __ldg(crow + (size_t)(8 * it) * mloc);
         }
 #pragma unroll
         for (int it = 0; it < kTileRows / 8; ++it) {
@@ -244,11 +246,16 @@ __global__ void __launch_bounds__(256) coeff_slab_transpose_kernel(float2 *__res
     }
     if (!TO_SLABS) {
         __syncthreads();
-        for (int ll = warp; ll < kTileRows; ll += 8) {
-            const int l = lbase + ll, d = ll - lane;
-            if (l >= lmax || mi_l >= mloc) continue;
-            if (d >= 0 && d < 64) c[((size_t)f * lmax + l) * mloc + mi_l] = T[ll][lane ^ tile_swz(ll)];
-            else if (d < 0 && sb == 0) c[((size_t)f * lmax + l) * mloc + mi_l] = make_float2(0.f, 0.f);  // l < m
+        float2 *crow = c + ((size_t)f * lmax + lbase + warp) * mloc + mi_l;
+        const int d0 = warp - lane, lrem = lmax - lbase - warp;
+        if (mi_l < mloc) {
+#pragma unroll
+            for (int it = 0; it < kTileRows / 8; ++it) {
+                const int ll = warp + 8 * it, d = d0 + 8 * it;
+                if (8 * it >= lrem) break;
+                if (d >= 0 && d < 64) crow[(size_t)(8 * it) * mloc] = T[ll][lane ^ tile_swz(ll)];
+                else if (d < 0 && sb == 0) crow[(size_t)(8 * it) * mloc] = make_float2(0.f, 0.f);  // l < m
+            }
         }
     }
 }

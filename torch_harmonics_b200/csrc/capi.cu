@@ -424,8 +424,18 @@ int shtb200_execute_host(shtb200_plan *pl, const void *in_host, void *out_host, 
     const size_t out_bytes = pl->analysis ? spec_bytes : grid_bytes;
     // Fields are independent, so the transform is pipelined over chunks of fields: the upload of chunk i + 1, the
     // kernels of chunk i and the download of chunk i - 1 run at the same time on three streams (both PCIe directions busy).
+    // Chunks of eight fields, except at both ends: the first upload and the last download have nothing to hide behind,
+    // so the first and the last chunk are short (two fields).
     const int chunk = std::min(nfields, 8);
-    const int nchunks = ceil_div(nfields, chunk);
+    std::vector<int> sizes;
+    {
+        int left = nfields;
+        if (left > 16) { sizes.push_back(2); sizes.push_back(6); left -= 8; }
+        while (left > 10) { sizes.push_back(8); left -= 8; }
+        if (left > 2 && nfields > 16) { sizes.push_back(left - 2); left = 2; }
+        while (left > 0) { sizes.push_back(std::min(left, chunk)); left -= sizes.back(); }
+    }
+    const int nchunks = (int)sizes.size();
     const size_t ws_bytes = shtb200_workspace_bytes(pl, chunk);
     int rc;
     if ((rc = grow(&pl->stage_in, &pl->stage_in_bytes, in_bytes)) || (rc = grow(&pl->stage_out, &pl->stage_out_bytes, out_bytes)) ||
@@ -445,8 +455,8 @@ int shtb200_execute_host(shtb200_plan *pl, const void *in_host, void *out_host, 
     SHT_CUDA_CHECK(cudaEventRecord(pl->ev_up[nchunks], st));
     SHT_CUDA_CHECK(cudaStreamWaitEvent(pl->copy_in, pl->ev_up[nchunks], 0));
     int launches = 0;
-    for (int i = 0; i < nchunks; ++i) {
-        const int f0 = i * chunk, nf = std::min(chunk, nfields - f0);
+    for (int i = 0, f0 = 0; i < nchunks; f0 += sizes[i], ++i) {
+        const int nf = sizes[i];
         char *din = reinterpret_cast<char *>(pl->stage_in) + (size_t)f0 * in_per;
         char *dout = reinterpret_cast<char *>(pl->stage_out) + (size_t)f0 * out_per;
         SHT_CUDA_CHECK(cudaMemcpyAsync(din, reinterpret_cast<const char *>(in_host) + (size_t)f0 * in_per, (size_t)nf * in_per, cudaMemcpyHostToDevice, pl->copy_in));

@@ -652,7 +652,7 @@ __global__ void __launch_bounds__(32 * NW * G, (NW * G >= 16) ? 2 : 1) fft_analy
         const int kk = Ka + (kn - Kh);
         for (int i = threadIdx.x; i < ngroups * (2 * NW / 4); i += blockDim.x) {
             const int g = i / (2 * NW / 4), c = (i - g * (2 * NW / 4)) * 4;
-            if (2 * VEC * f0 + c < ncp) *reinterpret_cast<float4 *>(X + (size_t)blocked_row(g, kk, ngroups) * ncp + 2 * VEC * f0 + c) = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (2 * VEC * f0 + c < 2 * VEC * nfields) *reinterpret_cast<float4 *>(X + (size_t)blocked_row(g, kk, ngroups) * ncp + 2 * VEC * f0 + c) = make_float4(0.f, 0.f, 0.f, 0.f);
         }
         return;
     }
@@ -733,7 +733,7 @@ __global__ void __launch_bounds__(32 * NW * G, (NW * G >= 16) ? 2 : 1) fft_analy
         if (VEC == 1) {
             // columns 2 (f0 + 2c), ..: (re, im) of two consecutive fields
             const int col = 2 * f0 + 4 * c;
-            if (col < ncp) {
+            if (col < 2 * nfields) {  // (columns past the last field pad the row pitch: nobody reads them)
                 // (the contraction does not read rows above the group's polar extent)
                 const int kf = kf_s ? kf_s[m] : 0;
                 if (kn >= (kf & 15) * kBK) *reinterpret_cast<float4 *>(X + (size_t)blocked_row(2 * m, kn, ngroups) * ncp + col) = make_float4(e[0], e[1], e[2], e[3]);
@@ -742,7 +742,7 @@ __global__ void __launch_bounds__(32 * NW * G, (NW * G >= 16) ? 2 : 1) fft_analy
         } else {
             // transforms 2c (theta component X0) and 2c + 1 (phi component X1) of pair f0 + c: four columns 4 (f0 + c)..
             const int col = 4 * (f0 + c);
-            if (col < ncp) {
+            if (col < 4 * nfields) {
 #pragma unroll
                 for (int p = 0; p < 2; ++p) {
                     const float *fa = p ? e : o;  // d/dtheta rows take the fold of parity 1 - p
@@ -815,7 +815,7 @@ __global__ void __launch_bounds__(32 * NW * G, (NW * G >= 16) ? 2 : 1) fft_synth
                 }
                 mm[u] = m;
                 av[u] = bv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (m >= 0 && col < ncp) {
+                if (m >= 0 && col < 2 * VEC * nfields) {
                     // (the contraction does not produce rows above the group's polar extent: they are zeros)
                     const int kf = kf_s ? kf_s[m] : 0;
                     if (kn >= (kf & 15) * kBK) av[u] = __ldg(reinterpret_cast<const float4 *>(Y + (size_t)blocked_row(2 * m, kn, 2 * mmax) * ncp + col));

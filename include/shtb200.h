@@ -78,7 +78,8 @@ size_t shtb200_workspace_bytes(const shtb200_plan *plan, int nfields);
  *        out complex64 [nfields, (2,) lmax, mmax]   (interleaved re, im; exact zeros where l < m)
  *   spectral -> grid kinds (ISHT, SHT_ADJOINT, IVSHT, VSHT_ADJOINT): the reverse.
  * `workspace_dev` must hold shtb200_workspace_bytes(plan, nfields) bytes and be 256-byte aligned.
- * Work is enqueued on `stream`; the call does not synchronise.
+ * Work is enqueued on `stream`; the call does not synchronise.  A plan is not re-entrant: calls on the same plan from
+ * several host threads must be serialised by the caller (different plans may be used concurrently).
  * Replaces RealSHT.forward / InverseRealSHT.forward / RealVectorSHT.forward /
  * InverseRealVectorSHT.forward (sht.py:151-186, 306-342, 454-495, 606-649) and their autograd.
  */
@@ -89,7 +90,8 @@ int shtb200_execute(shtb200_plan *plan, const void *in_dev, void *out_dev, int n
  * synchronises `stream`.  Device staging buffers are kept in the plan and grown on demand.  The fields are
  * processed in chunks of eight: upload, kernels and download of successive chunks overlap on three streams (the
  * copies run on streams owned by the plan; give pinned host memory, pageable memory serialises the copies).
- * This is the call a host-side caller of the reference's CPU path would switch to.
+ * This is the call a host-side caller of the reference's CPU path would switch to.  The staging buffers, copy streams
+ * and events belong to the plan, so two host-buffer calls on one plan must not overlap.
  */
 int shtb200_execute_host(shtb200_plan *plan, const void *in_host, void *out_host, int nfields, void *stream);
 
@@ -146,6 +148,8 @@ size_t shtb200_plan_table_bytes(const shtb200_plan *plan);
  *                        the first global order held locally and `mloc` the number of local orders.
  *                        Vector kinds (distributed_sht.py:497-555, 651-711): nfields counts (theta, phi) pairs and both
  *                        tensors carry the component axis, [nfields, 2, nlat, mloc] <-> [nfields, 2, lmax, mloc].
+ * shtb200_rfft_modes / shtb200_irfft_modes take no plan: they run on the calling thread's CURRENT device (their tables
+ * are built on first use and cached per (nlon, device) until the process exits).
  */
 int shtb200_rfft_modes(const float *in_dev, void *out_dev, long long nrows, int nlon, int nmodes, float scale, void *stream);
 int shtb200_irfft_modes(const void *in_dev, float *out_dev, long long nrows, int nlon, int nmodes, void *stream);

@@ -1,8 +1,9 @@
 """Generate the golden fixtures in this directory from the reference implementation itself.
 
-Run once in a container that has the reference checked out (default ``/root/reference``):
+Run once on a machine that has a checkout of the reference (torch-harmonics); its path is a required argument
+(or the environment variable ``TORCH_HARMONICS_REFERENCE``):
 
-    python tests/golden/make_golden.py [--reference /path/to/torch-harmonics] [--skip-large]
+    python tests/golden/make_golden.py --reference /path/to/torch-harmonics [--skip-large] [--only NAME ...]
 
 The reference package's ``__init__`` imports compiled extensions that are not built there, so the
 SHT submodules (pure torch) are imported through synthetic package objects.  Inputs come from
@@ -121,6 +122,28 @@ def cfg3(ref):
     )
 
 
+def cfg5(ref):
+    """Equiangular 721x1440, lmax=mmax=720; N(0,1) coefficients (band-limited fields), seed 4; two fields of the
+    global batch.  The spatially distributed transforms must reproduce the serial reference on every rank's tile
+    (tests/test_distributed_sht.py:109-163), so the serial reference's rows are the fixture."""
+    a = orc.random_coeffs((2,), 720, 720, seed=4, power=0.0)
+    sht = ref.RealSHT(721, 1440, lmax=720, mmax=720, grid="equiangular", norm="ortho")
+    isht = ref.InverseRealSHT(721, 1440, lmax=720, mmax=720, grid="equiangular", norm="ortho")
+    x = isht(t64(a))
+    c = sht(x)
+    rt = isht(c)
+    np.savez_compressed(
+        os.path.join(HERE, "cfg5_equiangular_721x1440.npz"),
+        rows_k=ROWS_K,
+        rows_l=ROWS_L,
+        field_rows=x.numpy()[:, ROWS_K, :],
+        coeff_rows=c.numpy()[:, ROWS_L, :],
+        roundtrip_rows=rt.numpy()[:, ROWS_K, :],
+        field_absmax=np.array(float(x.abs().max())),
+        coeff_absmax=np.array(float(c.abs().max())),
+    )
+
+
 def vector_small(ref):
     out = {}
     for grid, nlat, nlon in (("equiangular", 33, 64), ("legendre-gauss", 32, 64), ("lobatto", 33, 66)):
@@ -214,19 +237,16 @@ def truncation_cases(ref):
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("TORCH_HARMONICS_REFERENCE"), required="TORCH_HARMONICS_REFERENCE" not in os.environ)
     ap.add_argument("--skip-large", action="store_true")
+    ap.add_argument("--only", nargs="*", default=None, help="names of the generator functions to run (default: all)")
     args = ap.parse_args()
     warnings.simplefilter("ignore")
     torch.set_grad_enabled(True)
     ref = import_reference(args.reference)
-    tables(ref)
-    cfg1(ref)
-    cfg2(ref)
-    vector_small(ref)
-    autograd_small(ref)
-    truncation_cases(ref)
-    if not args.skip_large:
-        cfg3(ref)
-        cfg4(ref)
+    small = [tables, cfg1, cfg2, vector_small, autograd_small, truncation_cases]
+    large = [cfg3, cfg4, cfg5]
+    for fn in small + ([] if args.skip_large else large):
+        if args.only is None or fn.__name__ in args.only:
+            fn(ref)
     print("golden fixtures written to", HERE)

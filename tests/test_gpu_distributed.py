@@ -96,18 +96,48 @@ def _tile(t, dim_h, dim_w, gh, gw, rh, rw):
     return thd.split_tensor_along_dim(thd.split_tensor_along_dim(t, dim_h, gh)[rh], dim_w, gw)[rw].contiguous()
 
 
-def _dist_worker(rank, world, port, gh, gw):
+# (nlat, nlon, lmax, leading dims, grid): the reference's parameter list (tests/test_distributed_sht.py:109-163) -- even and odd
+# nlat (uneven 17 + 16 latitude split), default / reduced / enlarged lmax (8, 9, 64, 65), batches smaller than the process
+# groups (the leading dimension is zero-padded up to the group size), plus a 91 x 180 grid and a lobatto grid
+SCALAR_CASES = [
+    (32, 64, None, (32, 8), "equiangular"),
+    (32, 64, None, (32, 8), "legendre-gauss"),
+    (33, 64, None, (1, 10), "equiangular"),
+    (33, 64, None, (1, 10), "legendre-gauss"),
+    (8, 16, None, (1, 10), "equiangular"),
+    (32, 64, None, (1, 1), "equiangular"),
+    (32, 64, None, (1, 1), "legendre-gauss"),
+    (32, 64, None, (1, 2), "equiangular"),
+    (32, 64, 8, (4, 8), "equiangular"),
+    (33, 64, 9, (1, 10), "equiangular"),
+    (33, 64, 8, (1, 10), "legendre-gauss"),
+    (32, 64, 64, (4, 8), "legendre-gauss"),
+    (33, 64, 65, (1, 10), "equiangular"),
+    (33, 64, 9, (3,), "lobatto"),
+    (91, 180, 90, (4, 2), "equiangular"),
+]
+VECTOR_CASES = [
+    (32, 64, None, (4, 8), "equiangular"),
+    (33, 64, None, (1, 10), "legendre-gauss"),
+    (32, 64, None, (1, 1), "equiangular"),
+    (32, 64, None, (1, 2), "equiangular"),
+    (33, 64, 9, (1, 10), "equiangular"),
+    (32, 64, 64, (2, 3), "legendre-gauss"),
+    (33, 64, 65, (1, 10), "equiangular"),
+]
+
+
+def _init_grid(rank, world, port, gh, gw):
     import torch
     import torch.distributed as dist
+
+    import torch_harmonics_b200.distributed as thd
 
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
-    import torch_harmonics_b200 as th
-    import torch_harmonics_b200.distributed as thd
-
     rh, rw = rank // gw, rank % gw
     az = pol = None
     for r in range(gh):  # rows share a polar index -> azimuth groups
@@ -119,66 +149,15 @@ def _dist_worker(rank, world, port, gh, gw):
         if c == rw:
             pol = grp
     thd.init(pol if gh > 1 else None, az if gw > 1 else None)
-    ok = True
-    msgs = []
-    for nlat, nlon, lmax, grid, lead in ((33, 64, 17, "equiangular", (2, 5)), (32, 64, None, "legendre-gauss", (1, 1)), (33, 64, 9, "lobatto", (3,)), (91, 180, 90, "equiangular", (4, 2))):
-        with warnings.catch_warnings():
-            warnings.simplefilter("ignore")
-            sht, isht = th.RealSHT(nlat, nlon, lmax=lmax, grid=grid).cuda(), th.InverseRealSHT(nlat, nlon, lmax=lmax, grid=grid).cuda()
-            dsht, disht = thd.DistributedRealSHT(nlat, nlon, lmax=lmax, grid=grid).cuda(), thd.DistributedInverseRealSHT(nlat, nlon, lmax=lmax, grid=grid).cuda()
-        gen = torch.Generator(device="cuda").manual_seed(7)
-        x = torch.randn(*lead, nlat, nlon, device="cuda", generator=gen)
-        gc = torch.randn(*lead, sht.lmax, sht.mmax, device="cuda", generator=gen, dtype=torch.complex64)
-        xs = x.clone().requires_grad_(True)
-        cs = sht(xs)
-        cs.backward(gc)
-        xl = _tile(x, -2, -1, gh, gw, rh, rw).requires_grad_(True)
-        cl = dsht(xl)
-        cl.backward(_tile(gc, -2, -1, gh, gw, rh, rw))
-        scale = float(cs.detach().abs().max())
-        e1 = float((cl.detach() - _tile(cs.detach(), -2, -1, gh, gw, rh, rw)).abs().max()) / scale
-        e2 = float((xl.grad - _tile(xs.grad, -2, -1, gh, gw, rh, rw)).abs().max()) / float(xs.grad.abs().max())
-        c0 = cs.detach().clone().requires_grad_(True)
-        ys = isht(c0)
-        gy = torch.randn(ys.shape, device="cuda", generator=gen)  # same numbers on every rank
-        ys.backward(gy)
-        cloc = _tile(cs.detach(), -2, -1, gh, gw, rh, rw).requires_grad_(True)
-        yl = disht(cloc)
-        yl.backward(_tile(gy, -2, -1, gh, gw, rh, rw))
-        e3 = float((yl.detach() - _tile(ys.detach(), -2, -1, gh, gw, rh, rw)).abs().max()) / float(ys.abs().max())
-        e4 = float((cloc.grad - _tile(c0.grad, -2, -1, gh, gw, rh, rw)).abs().max()) / float(c0.grad.abs().max())
-        if max(e1, e2, e3, e4) > 3e-6:
-            ok = False
-            msgs.append(f"rank {rank} {nlat}x{nlon} {grid}: {e1:.2e} {e2:.2e} {e3:.2e} {e4:.2e}")
-    # vector transforms: (..., 2, lat, lon) tiles
-    for nlat, nlon, lmax, grid, lead in ((33, 64, 17, "equiangular", (2, 3)), (32, 64, None, "legendre-gauss", (1,))):
-        with warnings.catch_warnings():
-            warnings.simplefilter("ignore")
-            vsht, ivsht = th.RealVectorSHT(nlat, nlon, lmax=lmax, grid=grid).cuda(), th.InverseRealVectorSHT(nlat, nlon, lmax=lmax, grid=grid).cuda()
-            dv, div = thd.DistributedRealVectorSHT(nlat, nlon, lmax=lmax, grid=grid).cuda(), thd.DistributedInverseRealVectorSHT(nlat, nlon, lmax=lmax, grid=grid).cuda()
-        gen = torch.Generator(device="cuda").manual_seed(11)
-        x = torch.randn(*lead, 2, nlat, nlon, device="cuda", generator=gen)
-        gc = torch.randn(*lead, 2, vsht.lmax, vsht.mmax, device="cuda", generator=gen, dtype=torch.complex64)
-        xs = x.clone().requires_grad_(True)
-        cs = vsht(xs)
-        cs.backward(gc)
-        xl = _tile(x, -2, -1, gh, gw, rh, rw).requires_grad_(True)
-        cl = dv(xl)
-        cl.backward(_tile(gc, -2, -1, gh, gw, rh, rw))
-        e1 = float((cl.detach() - _tile(cs.detach(), -2, -1, gh, gw, rh, rw)).abs().max()) / float(cs.detach().abs().max())
-        e2 = float((xl.grad - _tile(xs.grad, -2, -1, gh, gw, rh, rw)).abs().max()) / float(xs.grad.abs().max())
-        c0 = cs.detach().clone().requires_grad_(True)
-        ys = ivsht(c0)
-        gy = torch.randn(ys.shape, device="cuda", generator=gen)
-        ys.backward(gy)
-        cloc = _tile(cs.detach(), -2, -1, gh, gw, rh, rw).requires_grad_(True)
-        yl = div(cloc)
-        yl.backward(_tile(gy, -2, -1, gh, gw, rh, rw))
-        e3 = float((yl.detach() - _tile(ys.detach(), -2, -1, gh, gw, rh, rw)).abs().max()) / float(ys.abs().max())
-        e4 = float((cloc.grad - _tile(c0.grad, -2, -1, gh, gw, rh, rw)).abs().max()) / float(c0.grad.abs().max())
-        if max(e1, e2, e3, e4) > 3e-6:
-            ok = False
-            msgs.append(f"rank {rank} vector {nlat}x{nlon} {grid}: {e1:.2e} {e2:.2e} {e3:.2e} {e4:.2e}")
+    return rh, rw
+
+
+def _finish(ok, msgs):
+    import torch
+    import torch.distributed as dist
+
+    import torch_harmonics_b200.distributed as thd
+
     flag = torch.tensor([0 if ok else 1], device="cuda")
     dist.all_reduce(flag)
     thd.finalize()
@@ -186,7 +165,118 @@ def _dist_worker(rank, world, port, gh, gw):
     assert int(flag.item()) == 0, "; ".join(msgs) or "another rank failed"
 
 
-@pytest.mark.parametrize("gh,gw", [(1, 2), (2, 1), (2, 2)])
+def _dist_worker(rank, world, port, gh, gw):
+    """Every rank computes the serial transform of the whole (seeded) batch and the distributed transform of its tile;
+    the tile must equal the serial result's tile AND the float64 oracle's, forward and input gradient, both directions."""
+    import torch
+
+    import torch_harmonics_b200 as th
+    import torch_harmonics_b200.distributed as thd
+
+    rh, rw = _init_grid(rank, world, port, gh, gw)
+    ok = True
+    msgs = []
+
+    def tile(t):
+        return _tile(t, -2, -1, gh, gw, rh, rw)
+
+    for vector, cases in ((False, SCALAR_CASES), (True, VECTOR_CASES)):
+        for nlat, nlon, lmax, lead, grid in cases:
+            with warnings.catch_warnings():
+                warnings.simplefilter("ignore")
+                if vector:
+                    sht, isht = th.RealVectorSHT(nlat, nlon, lmax=lmax, grid=grid).cuda(), th.InverseRealVectorSHT(nlat, nlon, lmax=lmax, grid=grid).cuda()
+                    dsht, disht = thd.DistributedRealVectorSHT(nlat, nlon, lmax=lmax, grid=grid).cuda(), thd.DistributedInverseRealVectorSHT(nlat, nlon, lmax=lmax, grid=grid).cuda()
+                    w, _, _ = orc.vsht_weights(nlat, nlon, lmax=lmax, grid=grid)
+                    p, _, _ = orc.ivsht_dpct(nlat, nlon, lmax=lmax, grid=grid)
+                else:
+                    sht, isht = th.RealSHT(nlat, nlon, lmax=lmax, grid=grid).cuda(), th.InverseRealSHT(nlat, nlon, lmax=lmax, grid=grid).cuda()
+                    dsht, disht = thd.DistributedRealSHT(nlat, nlon, lmax=lmax, grid=grid).cuda(), thd.DistributedInverseRealSHT(nlat, nlon, lmax=lmax, grid=grid).cuda()
+                    w, _, _ = orc.sht_weights(nlat, nlon, lmax=lmax, grid=grid)
+                    p, _, _ = orc.isht_pct(nlat, nlon, lmax=lmax, grid=grid)
+            if min(sht.lmax, nlat) < gh or min(sht.mmax, nlon) < gw:
+                continue  # a chunk would be empty on this grid (the reference refuses such splits too)
+            comp = (2,) if vector else ()
+            gen = torch.Generator(device="cuda").manual_seed(333)  # same numbers on every rank
+            x = torch.randn(*lead, *comp, nlat, nlon, device="cuda", generator=gen)
+            gc = torch.randn(*lead, *comp, sht.lmax, sht.mmax, device="cuda", generator=gen, dtype=torch.complex64)
+            xs = x.clone().requires_grad_(True)
+            cs = sht(xs)
+            cs.backward(gc)
+            xl = tile(x).requires_grad_(True)
+            cl = dsht(xl)
+            cl.backward(tile(gc))
+            xn = x.double().cpu().numpy()
+            c64 = torch.from_numpy(orc.vsht_forward(xn, w) if vector else orc.sht_forward(xn, w)).cuda()
+            e0 = float((cl.detach() - tile(c64)).abs().max()) / float(c64.abs().max())
+            e1 = float((cl.detach() - tile(cs.detach())).abs().max()) / float(cs.detach().abs().max())
+            e2 = float((xl.grad - tile(xs.grad)).abs().max()) / float(xs.grad.abs().max())
+            c0 = cs.detach().clone().requires_grad_(True)
+            ys = isht(c0)
+            gy = torch.randn(ys.shape, device="cuda", generator=gen)
+            ys.backward(gy)
+            cloc = tile(cs.detach()).requires_grad_(True)
+            yl = disht(cloc)
+            yl.backward(tile(gy))
+            cn = cs.detach().to(torch.complex128).cpu().numpy()
+            y64 = torch.from_numpy(orc.vsht_inverse(cn, p, nlon) if vector else orc.sht_inverse(cn, p, nlon)).cuda()
+            e3 = float((yl.detach() - tile(ys.detach())).abs().max()) / float(ys.abs().max())
+            e4 = float((cloc.grad - tile(c0.grad)).abs().max()) / float(c0.grad.abs().max())
+            e5 = float((yl.detach() - tile(y64)).abs().max()) / float(y64.abs().max())
+            if max(e1, e2, e3, e4) > 3e-6 or max(e0, e5) > TOL:
+                ok = False
+                msgs.append(f"rank {rank} {'vector ' if vector else ''}{nlat}x{nlon} lmax={lmax} {lead} {grid}: oracle {e0:.2e} {e5:.2e} serial {e1:.2e} {e2:.2e} {e3:.2e} {e4:.2e}")
+    if rank == 0:
+        print(f"distributed parity {gh}x{gw}: {len(SCALAR_CASES)} scalar + {len(VECTOR_CASES)} vector cases, ok={ok}", flush=True)
+    _finish(ok, msgs)
+
+
+def _cfg5_worker(rank, world, port, gh, gw):
+    """721 x 1440, lmax = mmax = 720 (uneven 361 + 360 latitude split on a polar group of two): two fields with N(0,1)
+    coefficients of seed 4, fewer than the ranks of the larger group.  Tiles against rows of the reference's own float64
+    results (committed fixture) and against the serial transform."""
+    import torch
+
+    import torch_harmonics_b200 as th
+    import torch_harmonics_b200.distributed as thd
+
+    rh, rw = _init_grid(rank, world, port, gh, gw)
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "cfg5_equiangular_721x1440.npz"))
+    a = torch.from_numpy(orc.random_coeffs((2,), 720, 720, seed=4, power=0.0)).to(torch.complex64).cuda()
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        with torch.device("cuda"):
+            sht, isht = th.RealSHT(721, 1440, lmax=720, mmax=720), th.InverseRealSHT(721, 1440, lmax=720, mmax=720)
+            dsht, disht = thd.DistributedRealSHT(721, 1440, lmax=720, mmax=720), thd.DistributedInverseRealSHT(721, 1440, lmax=720, mmax=720)
+    x = isht(a)
+    cs = sht(x)
+    rs = isht(cs)
+    cl = dsht(_tile(x, -2, -1, gh, gw, rh, rw))
+    rl = disht(cl)
+    cmax, fmax = float(g["coeff_absmax"]), float(g["field_absmax"])
+    e_ser_c = float((cl - _tile(cs, -2, -1, gh, gw, rh, rw)).abs().max()) / cmax
+    e_ser_r = float((rl - _tile(rs, -2, -1, gh, gw, rh, rw)).abs().max()) / fmax
+    l0, m0 = sum(dsht.l_shapes[:rh]), sum(dsht.m_shapes[:rw])
+    k0, j0 = sum(dsht.lat_shapes[:rh]), sum(dsht.lon_shapes[:rw])
+    e_ref_c = e_ref_r = 0.0
+    for i, l in enumerate(g["rows_l"]):
+        if l0 <= l < l0 + dsht.lmax_local:
+            ref = torch.from_numpy(g["coeff_rows"][:, i, m0:m0 + dsht.mmax_local]).cuda()
+            e_ref_c = max(e_ref_c, float((cl[:, l - l0, :].to(torch.complex128) - ref).abs().max()) / cmax)
+    for i, k in enumerate(g["rows_k"]):
+        if k0 <= k < k0 + dsht.nlat_local:
+            ref = torch.from_numpy(g["roundtrip_rows"][:, i, j0:j0 + dsht.nlon_local]).cuda()
+            e_ref_r = max(e_ref_r, float((rl[:, k - k0, :].double() - ref).abs().max()) / fmax)
+    ok = max(e_ser_c, e_ser_r) <= 3e-6 and e_ref_c <= TOL and e_ref_r <= 2 * TOL
+    msgs = [] if ok else [f"rank {rank}: serial {e_ser_c:.2e} {e_ser_r:.2e} reference rows {e_ref_c:.2e} {e_ref_r:.2e}"]
+    print(f"cfg5 tile {gh}x{gw} rank {rank} ({dsht.nlat_local}x{dsht.nlon_local} -> {dsht.lmax_local}x{dsht.mmax_local}): vs serial {e_ser_c:.2e} {e_ser_r:.2e}, vs reference rows {e_ref_c:.2e} {e_ref_r:.2e}", flush=True)
+    _finish(ok, msgs)
+
+
+GRIDS = [(1, 2), (2, 1), (2, 2), (2, 4), (4, 2)]
+
+
+@pytest.mark.parametrize("gh,gw", GRIDS)
 def test_multi_gpu_equals_serial(gh, gw):
     import torch
     import torch.multiprocessing as mp
@@ -194,3 +284,13 @@ def test_multi_gpu_equals_serial(gh, gw):
     if torch.cuda.device_count() < gh * gw:
         pytest.skip(f"needs {gh * gw} GPUs")
     mp.spawn(_dist_worker, args=(gh * gw, _free_port(), gh, gw), nprocs=gh * gw, join=True)
+
+
+@pytest.mark.parametrize("gh,gw", [(1, 2), (2, 2), (2, 4)])
+def test_multi_gpu_cfg5_reference_rows(gh, gw):
+    import torch
+    import torch.multiprocessing as mp
+
+    if torch.cuda.device_count() < gh * gw:
+        pytest.skip(f"needs {gh * gw} GPUs")
+    mp.spawn(_cfg5_worker, args=(gh * gw, _free_port(), gh, gw), nprocs=gh * gw, join=True)

@@ -183,3 +183,68 @@ def test_custom_operator_traces_and_matches_eager():
     ya.backward(g)
     yb.backward(g)
     assert torch.equal(xa.grad, xb.grad)
+
+
+@pytest.mark.parametrize("family", ["scalar", "vector", "distributed"])
+def test_autocast_region_leaves_the_transforms_in_float32(family):
+    """Inside torch.autocast the transforms still take float32 / complex64 tensors and compute in float32, forward and
+    backward (the reference asks callers to guard its modules with autocast(enabled=False), torch_harmonics/sht.py:95-107;
+    SpectralConvS2 does so at spectral_convolution.py:226-243): results equal those outside the region bit for bit, and a
+    half-precision input is refused rather than silently converted."""
+    import torch
+
+    import torch_harmonics_b200 as th
+    import torch_harmonics_b200.distributed as thd
+
+    nlat, nlon = 33, 64
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        if family == "scalar":
+            fwd, inv = th.RealSHT(nlat, nlon, lmax=17).cuda(), th.InverseRealSHT(nlat, nlon, lmax=17).cuda()
+            shape = (2, 3, nlat, nlon)
+        elif family == "vector":
+            fwd, inv = th.RealVectorSHT(nlat, nlon, lmax=17).cuda(), th.InverseRealVectorSHT(nlat, nlon, lmax=17).cuda()
+            shape = (2, 2, nlat, nlon)
+        else:
+            fwd, inv = thd.DistributedRealSHT(nlat, nlon, lmax=17).cuda(), thd.DistributedInverseRealSHT(nlat, nlon, lmax=17).cuda()
+            shape = (2, 3, nlat, nlon)
+    x = torch.randn(*shape, device="cuda", generator=torch.Generator(device="cuda").manual_seed(3))
+    xa = x.clone().requires_grad_(True)
+    ya = inv(fwd(xa))
+    ya.square().sum().backward()
+    xb = x.clone().requires_grad_(True)
+    with torch.autocast(device_type="cuda", dtype=torch.bfloat16):
+        cb = fwd(xb)
+        yb = inv(cb)
+        assert cb.dtype == torch.complex64 and yb.dtype == torch.float32
+        lin = torch.nn.functional.linear(yb, torch.eye(nlon, device="cuda"))  # an op autocast does convert
+        assert lin.dtype == torch.bfloat16
+        with pytest.raises(TypeError):
+            fwd(x.to(torch.bfloat16))
+    yb.square().sum().backward()
+    assert torch.equal(ya.detach(), yb.detach())
+    assert torch.equal(xa.grad, xb.grad)
+
+
+def test_module_release_frees_plans():
+    """Dropping a module destroys its plans at once (no reference cycle keeps the packed tables alive), and close()
+    releases them explicitly; the next call rebuilds them."""
+    import gc
+
+    import torch
+
+    sht, _ = _mods(33, 64, lmax=17)
+    x = torch.randn(2, 33, 64, device="cuda")
+    c0 = sht(x)
+    plans = list(sht._op.plans.values())
+    assert plans and all(p.handle for p in plans)
+    sht.close()
+    assert all(p.handle is None for p in plans) and not sht._op.plans
+    assert torch.equal(sht(x), c0)
+    plans = list(sht._op.plans.values())
+    gc.disable()
+    try:
+        del sht
+        assert all(p.handle is None for p in plans)
+    finally:
+        gc.enable()

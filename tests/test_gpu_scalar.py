@@ -133,7 +133,8 @@ def test_cfg2_reference_outputs(engine):
     ("down", 16, 48, 6, 6, "equiangular"),
     ("nyq", 20, 16, 9, 9, "legendre-gauss"),
 ])
-def test_truncation_reference_outputs(tag, nlat, nlon, lmax, mmax, grid):
+@pytest.mark.parametrize("engine", ENGINES)
+def test_truncation_reference_outputs(tag, nlat, nlon, lmax, mmax, grid, engine):
     import torch
 
     from torch_harmonics_b200 import _lib
@@ -143,13 +144,14 @@ def test_truncation_reference_outputs(tag, nlat, nlon, lmax, mmax, grid):
     rng = np.random.default_rng(50)
     x = rng.standard_normal((2, nlat, nlon))
     cin = rng.standard_normal((2, L, M)) + 1j * rng.standard_normal((2, L, M))
-    c = run_plan(make_plan(_lib.SHT, nlat, nlon, L, M, w), x.astype(np.float32), (2, L, M), torch.complex64, 2)
+    c = run_plan(make_plan(_lib.SHT, nlat, nlon, L, M, w, engine), x.astype(np.float32), (2, L, M), torch.complex64, 2)
     assert err(c, g[f"{tag}|coeffs"]) <= TOL
-    y = run_plan(make_plan(_lib.ISHT, nlat, nlon, L, M, p), cin.astype(np.complex64), (2, nlat, nlon), torch.float32, 2)
+    y = run_plan(make_plan(_lib.ISHT, nlat, nlon, L, M, p, engine), cin.astype(np.complex64), (2, nlat, nlon), torch.float32, 2)
     assert err(y, g[f"{tag}|field"]) <= TOL
 
 
-def test_host_buffer_call_and_errors():
+@pytest.mark.parametrize("engine", ENGINES)
+def test_host_buffer_call_and_errors(engine):
     import ctypes
 
     import torch
@@ -157,7 +159,7 @@ def test_host_buffer_call_and_errors():
     from torch_harmonics_b200 import _lib
 
     w, p, L, M = oracle_tables(33, 64, 17, 17, "equiangular")
-    plan = make_plan(_lib.SHT, 33, 64, L, M, w)
+    plan = make_plan(_lib.SHT, 33, 64, L, M, w, engine)
     x = np.random.default_rng(3).standard_normal((6, 33, 64)).astype(np.float32)
     xt = torch.from_numpy(x).pin_memory()
     out = torch.empty((6, L, M), dtype=torch.complex64).pin_memory()
@@ -198,8 +200,10 @@ def test_linearity_and_batch_independence():
     assert err(c1, cx[2:3]) <= 1e-6
 
 
-def test_stage_entry_points():
-    """rfft / irfft row transforms and the stand-alone Legendre stage used by the distributed modules."""
+@pytest.mark.parametrize("engine", ENGINES)
+def test_stage_entry_points(engine):
+    """rfft / irfft row transforms and the stand-alone Legendre stage used by the distributed modules
+    (the latter on a window of orders that does not start at m = 0)."""
     import ctypes
 
     import torch
@@ -228,7 +232,7 @@ def test_stage_entry_points():
     w, p, L, M = oracle_tables(nlat, nlon, 20, 20, grid)
     nf, m0, mloc = 3, 5, 9
     Xc = (rng.standard_normal((nf, nlat, mloc)) + 1j * rng.standard_normal((nf, nlat, mloc))).astype(np.complex64)
-    plan = make_plan(_lib.SHT, nlat, nlon, L, M, w)
+    plan = make_plan(_lib.SHT, nlat, nlon, L, M, w, engine)
     xd = torch.from_numpy(Xc).cuda()
     out = torch.full((nf, L, mloc), float("nan"), dtype=torch.complex64, device="cuda")
     ws = torch.empty(plan.legendre_workspace_bytes(nf, mloc), dtype=torch.uint8, device="cuda")
@@ -236,7 +240,7 @@ def test_stage_entry_points():
     torch.cuda.synchronize()
     ref = np.einsum("nkm,mlk->nlm", Xc.astype(np.complex128), w[m0:m0 + mloc])
     assert err(out.cpu().numpy(), ref) <= TOL
-    plan = make_plan(_lib.ISHT, nlat, nlon, L, M, p)
+    plan = make_plan(_lib.ISHT, nlat, nlon, L, M, p, engine)
     c = (rng.standard_normal((nf, L, mloc)) + 1j * rng.standard_normal((nf, L, mloc))).astype(np.complex64)
     cd = torch.from_numpy(c).cuda()
     out = torch.full((nf, nlat, mloc), float("nan"), dtype=torch.complex64, device="cuda")
@@ -247,7 +251,8 @@ def test_stage_entry_points():
     assert err(out.cpu().numpy(), ref) <= TOL
 
 
-def test_host_buffer_call_pipelined_chunks():
+@pytest.mark.parametrize("engine", ENGINES)
+def test_host_buffer_call_pipelined_chunks(engine):
     """More fields than one chunk: the host-buffer entry point uploads, transforms and downloads chunks of fields on
     three streams; the result must equal the device-resident call (same kernels on the same numbers), in both directions."""
     import torch
@@ -258,7 +263,7 @@ def test_host_buffer_call_pipelined_chunks():
     w, p, L, M = oracle_tables(nlat, nlon, 17, 17, "equiangular")
     rng = np.random.default_rng(11)
     x = rng.standard_normal((nf, nlat, nlon)).astype(np.float32)
-    pf, pi = make_plan(_lib.SHT, nlat, nlon, L, M, w), make_plan(_lib.ISHT, nlat, nlon, L, M, p)
+    pf, pi = make_plan(_lib.SHT, nlat, nlon, L, M, w, engine), make_plan(_lib.ISHT, nlat, nlon, L, M, p, engine)
     xh = torch.from_numpy(x).pin_memory()
     ch = torch.empty((nf, L, M), dtype=torch.complex64).pin_memory()
     pf.execute_host(xh, ch, nf)
@@ -269,3 +274,36 @@ def test_host_buffer_call_pipelined_chunks():
     pi.execute_host(ch, yh, nf)
     yd = run_plan(pi, cd, (nf, nlat, nlon), torch.float32, nf)
     assert err(yh.numpy(), yd) <= 1e-7
+
+
+@pytest.mark.parametrize("engine", ENGINES)
+def test_tall_grid_polar_extent_is_clamped(engine):
+    """A grid with more than 16 blocks of 32 folded latitudes (nlat = 1601) whose high orders vanish over more than
+    half of them: the first live block of those orders lies beyond what the FFT kernels' 4-bit field can carry, so
+    plan creation must clamp the extent (skip fewer rows), not fail, and the results must be those of the full
+    contraction.  The table is synthetic (the C ABI takes any table with the Legendre tables' equatorial parity):
+    W[m, l, k] = sin(theta_k)^(24 m) * cos(theta_k)^((l + m) % 2) * (1 + l / lmax), zero for l < m."""
+    import torch
+
+    from torch_harmonics_b200 import _lib
+
+    nlat, nlon, L, M = 1601, 192, 96, 96
+    theta = (np.arange(nlat) + 0.5) * np.pi / nlat  # symmetric about the equator
+    s, c = np.sin(theta), np.cos(theta)
+    m = np.arange(M)[:, None, None]
+    l = np.arange(L)[None, :, None]
+    w = (s[None, None, :] ** (24.0 * m)) * np.where((l + m) % 2 == 1, c[None, None, :], 1.0) * (1.0 + l / L) * (l >= m)
+    # the extent the plan derives: first row reaching 1e-14 of the row's maximum, in 32-row blocks
+    first = np.array([np.argmax(np.abs(w[mm, L - 1]) >= 1e-14 * np.abs(w[mm, L - 1]).max()) for mm in range(M)])
+    assert first.max() // 32 > 15, "the case must reach beyond block 15 to exercise the clamp"
+    rng = np.random.default_rng(77)
+    x = rng.standard_normal((3, nlat, nlon)).astype(np.float32)
+    plan = make_plan(_lib.SHT, nlat, nlon, L, M, w, engine)
+    cf = run_plan(plan, x, (3, L, M), torch.complex64, 3)
+    assert err(cf, orc.sht_forward(x.astype(np.float64), w)) <= TOL
+    # synthesis with the transposed table
+    pt = np.ascontiguousarray(w.transpose(0, 2, 1))
+    cin = (rng.standard_normal((3, L, M)) + 1j * rng.standard_normal((3, L, M))).astype(np.complex64)
+    plan = make_plan(_lib.ISHT, nlat, nlon, L, M, pt, engine)
+    y = run_plan(plan, cin, (3, nlat, nlon), torch.float32, 3)
+    assert err(y, orc.sht_inverse(cin.astype(np.complex128), pt, nlon)) <= TOL

@@ -231,6 +231,10 @@ int shtb200_plan_create(shtb200_plan **plan_out, int kind, int nlat, int nlon, i
     pl->Ka = pl->ncomp * pl->Kh;
     pl->Lh = (lmax + 1) / 2;
     pl->negate_seg1 = (kind == SHTB200_VSHT_ADJOINT || kind == SHTB200_IVSHT_ADJOINT) ? 1 : 0;
+    if (cudaDeviceGetAttribute(&pl->sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || pl->sm_count < 1) {
+        delete pl;
+        return fail(SHTB200_ECUDA, "cannot read the multiprocessor count");
+    }
 
     int rc;
 
@@ -266,7 +270,9 @@ int shtb200_plan_create(shtb200_plan **plan_out, int kind, int nlat, int nlon, i
     if (kind == SHTB200_SHT || kind == SHTB200_ISHT) {
         std::vector<int> first;
         if ((rc = launch_polar_extent(*pl, table_dev, 1e-14f, &first))) { shtb200_plan_destroy(pl); return rc; }
-        for (int g = 0; g < ngroups; ++g) pl->group_krow0[g] = std::min(first[g], std::max(pl->Kh - 1, 0)) / kBK * kBK;
+        // The FFT kernels carry the extent as a 4-bit block index per group: blocks beyond 15 are not skipped (skipping
+        // fewer rows is always correct; the contraction and the FFT kernels read the same clamped value).
+        for (int g = 0; g < ngroups; ++g) pl->group_krow0[g] = std::min(std::min(first[g], std::max(pl->Kh - 1, 0)) / kBK, kMaxPolarBlock) * kBK;
     }
     if ((rc = build_fft_plan(nlon, mmax, pl->analysis ? kFftSplit : kFftPacked, pl->group_krow0.data(), &pl->fft, &pl->d_tw, &pl->d_perm))) {
         shtb200_plan_destroy(pl);

@@ -67,6 +67,7 @@ struct FftPlanDev {
 //   "block-packed" (dx = 0, dy = rows of a block): one [rows x BK] slab per BK-wide slice of k.
 // ------------------------------------------------------------------------------------------------
 constexpr int kBK = 32;  // contraction slice width (floats): one 128-byte swizzle row
+constexpr int kMaxPolarBlock = 15;  // largest first-live latitude block a group may carry (a 4-bit field in the FFT tables)
 
 struct GemmItem {
     int a_y0;      // first table row of this item
@@ -119,6 +120,7 @@ struct GemmParams {
 // ------------------------------------------------------------------------------------------------
 struct Plan {
     int kind = 0, engine = 0, device = 0;
+    int sm_count = 0;  // multiprocessors of `device` (grid size of the persistent contraction kernel)
     int nlat = 0, nlon = 0, lmax = 0, mmax = 0;
     int Kh = 0;   // folded latitude count, (nlat + 1) / 2
     int Ka = 0;   // contraction length of the analysis kinds, ncomp * Kh

@@ -23,6 +23,7 @@
 #include <string.h>
 
 #include <algorithm>
+#include <mutex>
 #include <vector>
 
 #include "common.cuh"
@@ -199,23 +200,6 @@ int build_fft_plan(int nlon, int mmax_emit, int layout, const int *krow0, FftPla
     std::sort(rad.begin(), rad.end(), [](int a, int b) { return a > b; });
     for (size_t i = 0; i + 1 < rad.size(); ++i)
         if (rad.back() % 2 == 0 && rad[i] % 2 == 1) { std::swap(rad[i], rad.back()); break; }
-    if (const char *ov = getenv("SHTB200_FFT_RADICES")) {  // e.g. "16,9,10": explicit pass order (tuning aid)
-        std::vector<int> r2;
-        long long prod = 1;
-        for (const char *q = ov; *q;) {
-            int v = atoi(q);
-            if (v > 1) { r2.push_back(v); prod *= v; }
-            while (*q && *q != ',') ++q;
-            if (*q == ',') ++q;
-        }
-        bool okr = prod == n;
-        for (int v : r2) {
-            bool known = false;
-            for (int f : kFastRadices) known |= (f == v);
-            okr &= known;
-        }
-        if (okr) rad = r2;
-    }
     rad.insert(rad.begin(), slow.begin(), slow.end());
     if ((int)rad.size() > kMaxFftStages) return fail(SHTB200_EINVAL, "nlon has too many factors");
 
@@ -308,7 +292,7 @@ int build_fft_plan(int nlon, int mmax_emit, int layout, const int *krow0, FftPla
     if (krow0)
         for (size_t m = 0; m < eorder.size(); ++m) {
             const int b0 = krow0[2 * m] / kBK, b1 = krow0[2 * m + 1] / kBK;
-            if (b0 > 15 || b1 > 15) return fail(SHTB200_EINVAL, "polar extent does not fit the 4-bit block index");
+            if (b0 > kMaxPolarBlock || b1 > kMaxPolarBlock) return fail(SHTB200_EINVAL, "polar extent was not clamped to the 4-bit block index");
             tab[o_kf + m] = (unsigned char)(b0 | (b1 << 4));
         }
     {
@@ -1034,30 +1018,31 @@ int launch_fft_synthesis(const Plan &pl, const float *Y, float *x, int nfields, 
     return SHTB200_OK;
 }
 
-// The stage entry points build (and cache per nlon and device) their own FFT tables.
+// The stage entry points build their own FFT tables, cached per (nlon, device) for the life of the process.
 struct CachedFft {
     int n = 0, device = -1;
     FftPlanDev fp{};
     float2 *tw = nullptr;
     unsigned short *perm = nullptr;
 };
-static CachedFft g_cache[8];
+static std::mutex g_cache_mutex;
+static std::vector<CachedFft> g_cache;
 
+// Tables for `nlon` on the CURRENT device (the stage calls run on the caller's current device and stream).
 static int cached_fft(int nlon, FftPlanDev *fp) {
     int dev = 0;
     SHT_CUDA_CHECK(cudaGetDevice(&dev));
-    for (auto &c : g_cache)
+    std::lock_guard<std::mutex> lock(g_cache_mutex);
+    for (const CachedFft &c : g_cache)
         if (c.n == nlon && c.device == dev) { *fp = c.fp; return SHTB200_OK; }
-    for (auto &c : g_cache)
-        if (c.n == 0) {
-            int rc = build_fft_plan(nlon, 0, kFftRows, nullptr, &c.fp, &c.tw, &c.perm);
-            if (rc) return rc;
-            c.n = nlon;
-            c.device = dev;
-            *fp = c.fp;
-            return SHTB200_OK;
-        }
-    return fail(SHTB200_EINVAL, "too many distinct nlon values in the stage FFT cache");
+    CachedFft c;
+    int rc = build_fft_plan(nlon, 0, kFftRows, nullptr, &c.fp, &c.tw, &c.perm);
+    if (rc) return rc;
+    c.n = nlon;
+    c.device = dev;
+    g_cache.push_back(c);
+    *fp = c.fp;
+    return SHTB200_OK;
 }
 
 int launch_rfft_modes(const float *in, float2 *out, long long nrows, int nlon, int nmodes, float scale, cudaStream_t st) {

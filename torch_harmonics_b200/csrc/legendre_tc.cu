@@ -72,7 +72,6 @@ struct TcParams {
     int nunits;      // nitems * ntiles
     int ksteps_cap;  // row-packed operands: k-steps that cover the valid extent
     int bblk;        // column-contiguous B: 32-column blocks per tile
-    int write_hi;    // also store the TF32-truncated value back (only needed if the tensor core rounded instead of truncating)
     int *err;        // device error word
 };
 
@@ -283,13 +282,6 @@ legendre_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                     const int i = tid + j * NT;
                     if (i < nb4) v[j] = src[i];
                 }
-                if (P.write_hi) {
-#pragma unroll
-                    for (int j = 0; j < PER; ++j) {
-                        const int i = tid + j * NT;
-                        if (i < nb4) src[i] = make_float4(tf32_hi(v[j].x), tf32_hi(v[j].y), tf32_hi(v[j].z), tf32_hi(v[j].w));
-                    }
-                }
 #pragma unroll
                 for (int j = 0; j < PER; ++j) v[j] = make_float4(tf32_lo(v[j].x), tf32_lo(v[j].y), tf32_lo(v[j].z), tf32_lo(v[j].w));
                 // the A splitter must have taken the A tile out of the region first
@@ -446,13 +438,10 @@ bool gemm_tc_supported(const Plan &pl, const GemmParams &gp) {
 }
 
 int launch_gemm_tc(const Plan &pl, const GemmParams &gp, cudaStream_t st) {
-    static int sm_count = 0;
-    if (!sm_count) {
-        int dev = 0;
-        SHT_CUDA_CHECK(cudaGetDevice(&dev));
-        SHT_CUDA_CHECK(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev));
-        SHT_CUDA_CHECK(cudaFuncSetAttribute(legendre_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    }
+    // The opt-in to large dynamic shared memory is a per-device attribute of the kernel: set it for the current device
+    // (the plan's, made current by the caller) on every launch; the SM count is the plan's device's as well.
+    SHT_CUDA_CHECK(cudaFuncSetAttribute(legendre_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    const int sm_count = pl.sm_count;
     TcParams P{};
     P.gp = gp;
     P.bn = std::min<int>(BN_MAX, (int)round_up(gp.ncols, 16));
@@ -461,10 +450,6 @@ int launch_gemm_tc(const Plan &pl, const GemmParams &gp, cudaStream_t st) {
     P.ksteps_cap = ceil_div(gp.a_kext, TK);
     P.bblk = ceil_div(P.bn, 32);
     P.err = pl.d_err;
-    {
-        const char *e = getenv("SHTB200_TC_WRITE_HI");
-        P.write_hi = (e && e[0] == '1') ? 1 : 0;
-    }
 
     // extents of the two operands as 2-D row-major tensors
     const bool analysis = gp.mode != EPI_LATROWS;

@@ -63,11 +63,39 @@ def _verify(msg, local_value, expected, group):
             raise ValueError(f"{msg} shapes are not correct. Expected {b}, got {a} for index {idx}. Please check that the number of chunks is correct.")
 
 
+# Optional record of the exchanges (benchmarking): while a list is installed, every NCCL all-to-all appends
+# (bytes sent to other ranks, bytes received from other ranks, start event, end event).
+_EXCHANGE_LOG = None
+
+
+def exchange_log_start():
+    """Start recording the all-to-all exchanges of this process (byte counts and CUDA events around each one)."""
+    global _EXCHANGE_LOG
+    _EXCHANGE_LOG = []
+
+
+def exchange_log_stop():
+    """Stop recording; returns [(bytes_sent, bytes_received, milliseconds)] after synchronising the device."""
+    global _EXCHANGE_LOG
+    log, _EXCHANGE_LOG = _EXCHANGE_LOG or [], None
+    if log:
+        torch.cuda.synchronize()
+    return [(s, r, e0.elapsed_time(e1)) for s, r, e0, e1 in log]
+
+
 def _exchange(send: torch.Tensor, send_counts, recv_counts, group):
     """Flat all-to-all with per-peer element counts."""
     recv = send.new_empty(sum(recv_counts))
     if dist.get_backend(group) == "nccl":
+        if _EXCHANGE_LOG is not None:
+            me = dist.get_rank(group)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
         dist.all_to_all_single(recv, send, output_split_sizes=list(recv_counts), input_split_sizes=list(send_counts), group=group)
+        if _EXCHANGE_LOG is not None:
+            e1.record()
+            es = send.element_size()
+            _EXCHANGE_LOG.append(((sum(send_counts) - send_counts[me]) * es, (sum(recv_counts) - recv_counts[me]) * es, e0, e1))
         return recv
     # point-to-point fallback
     rank = dist.get_rank(group)
@@ -136,7 +164,12 @@ def _transpose(x: torch.Tensor, dim0: int, dim1: int, dim1_split_sizes, group):
 
 
 class _Transpose(torch.autograd.Function):
+    """The transposes move bytes and never compute, so they run on whatever dtype arrives; ``custom_fwd`` /
+    ``custom_bwd`` make the backward exchange run under the autocast state the forward one saw
+    (torch_harmonics/distributed/primitives.py:279-311)."""
+
     @staticmethod
+    @torch.amp.custom_fwd(device_type="cuda")
     def forward(ctx, x, dims, dim1_split_sizes, which):
         group = azimuth_group() if which == "azimuth" else polar_group()
         active = is_distributed_azimuth() if which == "azimuth" else is_distributed_polar()
@@ -149,6 +182,7 @@ class _Transpose(torch.autograd.Function):
         return _transpose(x, dims[0], dims[1], dim1_split_sizes, group)
 
     @staticmethod
+    @torch.amp.custom_bwd(device_type="cuda")
     def backward(ctx, go):
         go = go.contiguous()
         if not ctx.active:

@@ -29,18 +29,27 @@ class _ShtOp:
     """A pair of plans (operator, adjoint) created lazily per device from a module's table."""
 
     def __init__(self, module, kind, adj_kind, table_name, vector):
-        self.module = module
+        # weak: the module owns this object, so a strong reference back would keep the plans (and their packed tables,
+        # hundreds of MB of device memory at 721 x 1440) alive until the cycle collector runs
+        self._module = weakref.ref(module)
         self.kind, self.adj_kind = kind, adj_kind
         self.table_name = table_name
         self.vector = vector
         self.plans = {}
         _register_op(self)
 
+    @property
+    def module(self):
+        mod = self._module()
+        if mod is None:
+            raise RuntimeError("the SHT module of this operator has been deleted")
+        return mod
+
     def plan(self, device, adjoint):
-        key = (device.index, adjoint, self.module.engine)
+        mod = self.module
+        key = (device.index, adjoint, mod.engine)
         pl = self.plans.get(key)
         if pl is None:
-            mod = self.module
             table = getattr(mod, self.table_name)
             with torch.cuda.device(device):
                 t32 = table.detach().to(device=device, dtype=torch.float32).contiguous()
@@ -53,6 +62,12 @@ class _ShtOp:
         for pl in self.plans.values():
             pl.close()
         self.plans.clear()
+
+    def __del__(self):
+        try:
+            self.clear()
+        except Exception:
+            pass
 
 
 def _run(plan, x, out_tail, out_dtype, nfields):
@@ -156,6 +171,11 @@ class _ShtBase(nn.Module):
         if hasattr(self, "_op"):
             self._op.clear()
         return out
+
+    def close(self):
+        """Release the device memory of the plans built so far (they are rebuilt on the next call)."""
+        if hasattr(self, "_op"):
+            self._op.clear()
 
     def __getstate__(self):
         state = self.__dict__.copy()

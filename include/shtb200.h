@@ -115,6 +115,30 @@ int shtb200_execute_host(shtb200_plan *plan, const void *in_host, void *out_host
 size_t shtb200_static_scratch_bytes(void);
 int shtb200_execute_static_scratch(shtb200_plan *plan, const void *in_dev, void *out_dev, int nfields, void *stream);
 
+/*
+ * Spectral convolution on the sphere in one call: forward SHT of `batch * in_channels` fields, per-degree complex channel
+ * mixing  out[b, g, o, l, m] = sum_i weight[g, i, o, l] * in[b, g, i, l, m]  within `num_groups` channel groups, inverse SHT
+ * of the `batch * out_channels` results.  Replaces SpectralConvS2.forward without bias,
+ * torch_harmonics/spectral_convolution.py:203-247 (sht :227, reshape + einsum "bgixy,giox->bgoxy" :236-239, isht :242).
+ *   analysis  : a SHTB200_SHT plan (grid nlat_in x nlon_in); synthesis: a SHTB200_ISHT plan (grid nlat_out x nlon_out, which
+ *               may differ); both with the same lmax and mmax, on the same device
+ *   x_dev     : float32 [batch, in_channels, nlat_in, nlon_in]       y_dev: float32 [batch, out_channels, nlat_out, nlon_out]
+ *   weight_dev: complex64 [num_groups, in_channels / num_groups, out_channels / num_groups, lmax]
+ * The coefficients stay in the degree-slab layout both contraction kernels share: the (.., l, m) coefficient arrays and
+ * the two transposes around them are never produced.  The adjoint kinds may be passed as well (SHTB200_ISHT_ADJOINT as
+ * `analysis`, SHTB200_SHT_ADJOINT as `synthesis`): with the conjugated, (in, out)-swapped weights that is the input gradient.
+ */
+size_t shtb200_spectral_conv_workspace_bytes(const shtb200_plan *analysis, const shtb200_plan *synthesis, int batch, int in_channels, int out_channels, int num_groups);
+int shtb200_spectral_conv(shtb200_plan *analysis, shtb200_plan *synthesis, const float *x_dev, const void *weight_dev, float *y_dev, int batch, int in_channels,
+                          int out_channels, int num_groups, void *workspace_dev, size_t workspace_bytes, void *stream);
+
+/*
+ * Integral over the sphere: out[f] = sum_k lat_weights[k] * sum_j x[f, k, j] for `nfields` fields; pass the latitude
+ * quadrature weights times 2 pi / nlon (divided by 4 pi for the normalised variant).  Runs on the current device.
+ * Replaces QuadratureS2.forward, torch_harmonics/quadrature.py:447-463.
+ */
+int shtb200_quadrature(const float *x_dev, const float *lat_weights_dev, float *out_dev, long long nfields, int nlat, int nlon, void *stream);
+
 /* Introspection used by the tests and the benchmark. */
 int shtb200_plan_info(const shtb200_plan *plan, int *nlat, int *nlon, int *lmax, int *mmax, int *kind, int *engine);
 /* Kernel launches the last shtb200_execute on this plan enqueued. */

@@ -32,7 +32,11 @@ def import_reference(path):
         mod = types.ModuleType(name)
         mod.__path__ = [os.path.join(path, sub)]
         sys.modules[name] = mod
-    return importlib.import_module("torch_harmonics.sht")
+    sht = importlib.import_module("torch_harmonics.sht")
+    # names the reference's own modules import from the package root
+    for name in ("RealSHT", "InverseRealSHT", "RealVectorSHT", "InverseRealVectorSHT"):
+        setattr(sys.modules["torch_harmonics"], name, getattr(sht, name))
+    return sht
 
 
 def t64(a):
@@ -144,6 +148,63 @@ def cfg5(ref):
     )
 
 
+SPECTRAL_CONV_CASES = [
+    # tag, in_shape, out_shape, in_channels, out_channels, groups, grid_in, grid_out, bias
+    ("plain", (17, 32), (17, 32), 6, 4, 1, "equiangular", "equiangular", False),
+    ("groups_resample", (17, 32), (12, 24), 6, 4, 2, "equiangular", "legendre-gauss", False),
+    ("bias", (16, 32), (16, 32), 4, 4, 2, "legendre-gauss", "legendre-gauss", True),
+]
+
+
+def spectral_conv_inputs(tag, in_shape, cin, cout, groups, lmax, out_shape):
+    """Seeded inputs of one spectral-convolution case (the tests regenerate them with the same calls)."""
+    rng = np.random.default_rng(sum(map(ord, tag)))
+    w = 0.3 * (rng.standard_normal((groups, cin // groups, cout // groups, lmax)) + 1j * rng.standard_normal((groups, cin // groups, cout // groups, lmax)))
+    b = np.tril(0.1 * (rng.standard_normal((1, cin, lmax, lmax)) + 1j * rng.standard_normal((1, cin, lmax, lmax))))
+    b[..., 0] = b[..., 0].real
+    x = rng.standard_normal((2, cin) + tuple(in_shape))
+    gy = rng.standard_normal((2, cout) + tuple(out_shape))
+    return w.astype(np.complex64), b.astype(np.complex64), x.astype(np.float32), gy.astype(np.float32)
+
+
+def spectral_conv(ref):
+    """SpectralConvS2 (outputs, input / weight / bias gradients), QuadratureS2 weights and GaussianRandomFieldS2 samples of
+    the reference.  The reference wraps its channel contraction in torch.compile; it is run eagerly here."""
+    import torch._dynamo
+
+    torch._dynamo.config.disable = True
+    sc = importlib.import_module("torch_harmonics.spectral_convolution")
+    rf = importlib.import_module("torch_harmonics.random_fields")
+    quad = importlib.import_module("torch_harmonics.quadrature")
+    out = {}
+    for tag, ishape, oshape, cin, cout, groups, gin, gout, bias in SPECTRAL_CONV_CASES:
+        layer = sc.SpectralConvS2(ishape, oshape, cin, cout, num_groups=groups, grid_in=gin, grid_out=gout, bias=bias)
+        w, b, x, gy = spectral_conv_inputs(tag, ishape, cin, cout, groups, layer.lmax, oshape)
+        layer.weight.data = torch.from_numpy(w)
+        if bias:
+            layer.spectral_bias.data = torch.from_numpy(b)
+        xt = torch.from_numpy(x).requires_grad_(True)
+        y = layer(xt)
+        y.backward(torch.from_numpy(gy))
+        out[f"{tag}|lmax"] = np.array(layer.lmax)
+        out[f"{tag}|y"] = y.detach().numpy()
+        out[f"{tag}|gx"] = xt.grad.numpy()
+        out[f"{tag}|gw"] = layer.weight.grad.numpy()
+        if bias:
+            out[f"{tag}|gb"] = layer.spectral_bias.grad.numpy()
+    for grid in ("equiangular", "legendre-gauss", "lobatto", "equiangular-trapezoidal"):
+        for normalize in (False, True):
+            q = quad.QuadratureS2((13, 24), grid=grid, normalize=normalize)
+            out[f"quad|{grid}|{int(normalize)}"] = q.quad_weight[0, 0, :, 0].numpy()
+    grf = rf.GaussianRandomFieldS2(16, alpha=2.5, tau=4.0)
+    rng = np.random.default_rng(99)
+    xi = (rng.standard_normal((3, grf.isht.lmax, grf.isht.mmax)) + 1j * rng.standard_normal((3, grf.isht.lmax, grf.isht.mmax))).astype(np.complex64)
+    out["grf|lm"] = np.array([grf.isht.lmax, grf.isht.mmax])
+    out["grf|sqrt_eig"] = grf.sqrt_eig.numpy()
+    out["grf|u"] = grf(3, xi=torch.from_numpy(xi)).numpy()
+    np.savez_compressed(os.path.join(HERE, "spectral_conv.npz"), **out)
+
+
 def vector_small(ref):
     out = {}
     for grid, nlat, nlon in (("equiangular", 33, 64), ("legendre-gauss", 32, 64), ("lobatto", 33, 66)):
@@ -244,7 +305,7 @@ if __name__ == "__main__":
     warnings.simplefilter("ignore")
     torch.set_grad_enabled(True)
     ref = import_reference(args.reference)
-    small = [tables, cfg1, cfg2, vector_small, autograd_small, truncation_cases]
+    small = [tables, cfg1, cfg2, vector_small, autograd_small, truncation_cases, spectral_conv]
     large = [cfg3, cfg4, cfg5]
     for fn in small + ([] if args.skip_large else large):
         if args.only is None or fn.__name__ in args.only:

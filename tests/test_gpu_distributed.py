@@ -220,7 +220,7 @@ def _dist_worker(rank, world, port, gh, gw):
             yl.backward(tile(gy))
             cn = cs.detach().to(torch.complex128).cpu().numpy()
             y64 = torch.from_numpy(orc.vsht_inverse(cn, p, nlon) if vector else orc.sht_inverse(cn, p, nlon)).cuda()
-            e3 = float((yl.detach() - tile(ys.detach())).abs().max()) / float(ys.abs().max())
+            e3 = float((yl.detach() - tile(ys.detach())).abs().max()) / float(ys.detach().abs().max())
             e4 = float((cloc.grad - tile(c0.grad)).abs().max()) / float(c0.grad.abs().max())
             e5 = float((yl.detach() - tile(y64)).abs().max()) / float(y64.abs().max())
             if max(e1, e2, e3, e4) > 3e-6 or max(e0, e5) > TOL:

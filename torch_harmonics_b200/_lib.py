@@ -69,6 +69,12 @@ def load():
         lib.shtb200_legendre.restype = ci
         lib.shtb200_legendre_workspace_bytes.argtypes = [vp, ci, ci]
         lib.shtb200_legendre_workspace_bytes.restype = cs
+        lib.shtb200_spectral_conv_workspace_bytes.argtypes = [vp, vp, ci, ci, ci, ci]
+        lib.shtb200_spectral_conv_workspace_bytes.restype = cs
+        lib.shtb200_spectral_conv.argtypes = [vp, vp, vp, vp, vp, ci, ci, ci, ci, vp, cs, vp]
+        lib.shtb200_spectral_conv.restype = ci
+        lib.shtb200_quadrature.argtypes = [vp, vp, vp, cll, ci, ci, vp]
+        lib.shtb200_quadrature.restype = ci
         _lib = lib
         return lib
 
@@ -77,6 +83,27 @@ def check(rc, what):
     if rc != 0:
         msg = load().shtb200_last_error().decode("utf-8", "replace")
         raise ShtLibraryError(f"{what} failed (code {rc}): {msg}")
+
+
+def spectral_conv(analysis, synthesis, x, weight, y, batch, cin, cout, groups, stream):
+    """SHT -> per-degree channel mixing -> inverse SHT on device tensors (``shtb200_spectral_conv``)."""
+    import torch
+
+    lib = load()
+    nbytes = lib.shtb200_spectral_conv_workspace_bytes(analysis.handle, synthesis.handle, batch, cin, cout, groups)
+    if nbytes == 0:
+        check(-1, "shtb200_spectral_conv_workspace_bytes")
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=x.device)
+    rc = lib.shtb200_spectral_conv(
+        analysis.handle, synthesis.handle, ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(weight.data_ptr()), ctypes.c_void_p(y.data_ptr()),
+        batch, cin, cout, groups, ctypes.c_void_p(ws.data_ptr()), nbytes, ctypes.c_void_p(stream),
+    )
+    check(rc, "shtb200_spectral_conv")
+
+
+def quadrature(x, lat_weights, out, nfields, nlat, nlon, stream):
+    rc = load().shtb200_quadrature(ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(lat_weights.data_ptr()), ctypes.c_void_p(out.data_ptr()), nfields, nlat, nlon, ctypes.c_void_p(stream))
+    check(rc, "shtb200_quadrature")
 
 
 class Plan:

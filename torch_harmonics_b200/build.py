@@ -11,8 +11,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIBDIR = os.path.join(HERE, "lib")
 LIB = os.path.join(LIBDIR, "libshtb200.so")
-SOURCES = ["capi.cu", "fft_kernels.cu", "legendre_simt.cu", "legendre_tc.cu", "pack_kernels.cu", "no_alloc.cu"]
-HEADERS = ["common.cuh", "tc_ptx.cuh", "fft_consts.cuh", os.path.join("..", "..", "include", "shtb200.h")]
+SOURCES = ["capi.cu", "fft_kernels.cu", "fft_twopass.cu", "legendre_simt.cu", "legendre_tc.cu", "pack_kernels.cu", "spectral_conv.cu", "no_alloc.cu"]
+HEADERS = ["common.cuh", "tc_ptx.cuh", "fft_consts.cuh", "fft_butterflies.cuh", os.path.join("..", "..", "include", "shtb200.h")]
 
 
 def _stale():

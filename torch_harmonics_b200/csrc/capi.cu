@@ -239,8 +239,8 @@ int shtb200_plan_create(shtb200_plan **plan_out, int kind, int nlat, int nlon, i
     int rc;
 
     // per-order scale applied inside the FFT kernels
+    std::vector<float> ms(mmax);
     {
-        std::vector<float> ms(mmax);
         for (int m = 0; m < mmax; ++m) {
             const bool edge = (m == 0) || (2 * m == nlon);
             double s = 1.0;
@@ -274,7 +274,8 @@ int shtb200_plan_create(shtb200_plan **plan_out, int kind, int nlat, int nlon, i
         // fewer rows is always correct; the contraction and the FFT kernels read the same clamped value).
         for (int g = 0; g < ngroups; ++g) pl->group_krow0[g] = std::min(std::min(first[g], std::max(pl->Kh - 1, 0)) / kBK, kMaxPolarBlock) * kBK;
     }
-    if ((rc = build_fft_plan(nlon, mmax, pl->analysis ? kFftSplit : kFftPacked, pl->group_krow0.data(), &pl->fft, &pl->d_tw, &pl->d_perm))) {
+    if ((rc = build_fft_plan(nlon, mmax, pl->analysis ? kFftSplit : kFftPacked, pl->group_krow0.data(), &pl->fft, &pl->d_tw, &pl->d_perm)) ||
+        (rc = build_twopass_tables(*pl, ms))) {
         shtb200_plan_destroy(pl);
         return rc;
     }
@@ -381,6 +382,7 @@ int shtb200_plan_destroy(shtb200_plan *pl) {
     cudaFree(pl->d_tw);
     cudaFree(pl->d_perm);
     cudaFree(pl->d_mscale);
+    cudaFree(pl->d_tp_blob);
     cudaFree(pl->d_table);
     cudaFree(pl->d_items);
     cudaFree(pl->d_ga0);
@@ -478,6 +480,78 @@ int shtb200_execute_host(shtb200_plan *pl, const void *in_host, void *out_host, 
     SHT_CUDA_CHECK(cudaStreamSynchronize(pl->copy_out));
     SHT_CUDA_CHECK(cudaStreamSynchronize(st));
     return SHTB200_OK;
+}
+
+namespace {
+struct ConvLayout {
+    size_t op, zin, zout, wsplit;  // [X / Y (shared)][Z in][Z out][split weights]
+    size_t total() const { return align256(op) + align256(zin) + align256(zout) + align256(wsplit); }
+};
+int conv_layout(const Plan &pa, const Plan &ps, int batch, int cin, int cout, int ngroups, ConvLayout *out) {
+    if (pa.vector || ps.vector || !pa.analysis || ps.analysis) return fail(SHTB200_EINVAL, "spectral convolution needs a scalar analysis plan and a scalar synthesis plan");
+    if (pa.lmax != ps.lmax || pa.mmax != ps.mmax) return fail(SHTB200_EINVAL, "the two plans of a spectral convolution must share lmax and mmax");
+    if (pa.device != ps.device) return fail(SHTB200_EINVAL, "the two plans of a spectral convolution must live on the same device");
+    if (batch < 1 || cin < 1 || cout < 1 || ngroups < 1 || cin % ngroups || cout % ngroups) return fail(SHTB200_EINVAL, "bad (batch, channels, groups)");
+    if ((long long)batch * std::max(cin, cout) > 0x3fffffffLL) return fail(SHTB200_EINVAL, "too many fields");
+    const WsLayout wa = ws_layout(pa, batch * cin, 0, pa.mmax), wsyn = ws_layout(ps, batch * cout, 0, ps.mmax);
+    out->op = std::max(wa.op_bytes, wsyn.y_bytes);
+    out->zin = wa.y_bytes;
+    out->zout = wsyn.op_bytes;
+    out->wsplit = slab_mix_weight_bytes(cin, cout, ngroups, pa.lmax);
+    return SHTB200_OK;
+}
+}  // namespace
+
+size_t shtb200_spectral_conv_workspace_bytes(const shtb200_plan *analysis, const shtb200_plan *synthesis, int batch, int in_channels, int out_channels, int num_groups) {
+    ConvLayout L{};
+    if (!analysis || !synthesis || conv_layout(*analysis, *synthesis, batch, in_channels, out_channels, num_groups, &L)) return 0;
+    return L.total();
+}
+
+int shtb200_spectral_conv(shtb200_plan *analysis, shtb200_plan *synthesis, const float *x_dev, const void *weight_dev, float *y_dev, int batch, int in_channels,
+                          int out_channels, int num_groups, void *workspace_dev, size_t workspace_bytes, void *stream) {
+    if (!analysis || !synthesis) return fail(SHTB200_EINVAL, "plan is null");
+    if (!x_dev || !weight_dev || !y_dev) return fail(SHTB200_EINVAL, "null pointer");
+    Plan &pa = *analysis, &ps = *synthesis;
+    ConvLayout L{};
+    int rc;
+    if ((rc = conv_layout(pa, ps, batch, in_channels, out_channels, num_groups, &L))) return rc;
+    if (workspace_bytes < L.total() || !workspace_dev) return fail(SHTB200_EWORKSPACE, "workspace too small: need " + std::to_string(L.total()) + " bytes");
+    if (((uintptr_t)workspace_dev & 255) != 0) return fail(SHTB200_EINVAL, "workspace must be 256-byte aligned");
+    DeviceGuard guard(pa.device);
+    if (!guard.ok) return fail(SHTB200_ECUDA, "cudaSetDevice failed");
+    cudaStream_t st = (cudaStream_t)stream;
+    char *base = reinterpret_cast<char *>(workspace_dev);
+    float *XY = reinterpret_cast<float *>(base);
+    float *Zin = reinterpret_cast<float *>(base + align256(L.op));
+    float *Zout = reinterpret_cast<float *>(base + align256(L.op) + align256(L.zin));
+    float2 *Wsplit = reinterpret_cast<float2 *>(base + align256(L.op) + align256(L.zin) + align256(L.zout));
+    const int nin = batch * in_channels, nout = batch * out_channels;
+    pa.last_launches = ps.last_launches = 0;
+    // analysis: longitude FFT, Legendre contraction into the degree slabs
+    if ((rc = launch_fft_analysis(pa, x_dev, XY, nin, st))) return rc;
+    {
+        GemmParams gp = gemm_params(pa, nin, 0, pa.mmax, XY, Zin);
+        if ((rc = run_gemm(pa, gp, st))) return rc;
+    }
+    // per-degree channel mixing, slabs to slabs
+    if ((rc = launch_slab_mix(pa, Zin, Zout, reinterpret_cast<const float2 *>(weight_dev), Wsplit, batch, in_channels, out_channels, num_groups, st))) return rc;
+    // synthesis: Legendre contraction from the slabs, longitude FFT
+    if ((rc = clear_empty_groups(ps, XY, 2 * nout, 0, ps.mmax, st))) return rc;
+    {
+        GemmParams gp = gemm_params(ps, nout, 0, ps.mmax, Zout, XY);
+        if ((rc = run_gemm(ps, gp, st))) return rc;
+    }
+    if ((rc = launch_fft_synthesis(ps, XY, y_dev, nout, st))) return rc;
+    pa.last_launches = 6;  // FFT, contraction, weight split, mixing, contraction, FFT
+    return SHTB200_OK;
+}
+
+int shtb200_quadrature(const float *x_dev, const float *lat_weights_dev, float *out_dev, long long nfields, int nlat, int nlon, void *stream) {
+    if (nfields < 0 || nlat < 1 || nlon < 1) return fail(SHTB200_EINVAL, "bad quadrature shape");
+    if (nfields == 0) return SHTB200_OK;
+    if (!x_dev || !lat_weights_dev || !out_dev) return fail(SHTB200_EINVAL, "null pointer");
+    return launch_quadrature(x_dev, lat_weights_dev, out_dev, nfields, nlat, nlon, (cudaStream_t)stream);
 }
 
 int shtb200_plan_info(const shtb200_plan *pl, int *nlat, int *nlon, int *lmax, int *mmax, int *kind, int *engine) {

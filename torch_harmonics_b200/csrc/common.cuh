@@ -135,6 +135,10 @@ struct Plan {
     unsigned short *d_perm = nullptr;
     float *d_mscale = nullptr;  // per-order scale applied in the FFT kernel (2 pi / nlon, adjoint weights ...)
     int zero_imag_edges = 0;    // analysis adjoint: force Im = 0 at m = 0 and Nyquist
+    // two-pass FFT kernels (scalar kinds, nlon = R1 * R2 with a built factorisation): their table blob
+    bool twopass = false;
+    unsigned char *d_tp_blob = nullptr;
+    int tp_blob_bytes = 0, tp_mpad = 0;
 
     // packed table
     float *d_table = nullptr;
@@ -187,6 +191,11 @@ int build_fft_plan(int nlon, int mmax_emit, int layout, const int *krow0, FftPla
 int launch_fft_analysis(const Plan &pl, const float *x, float *X, int nfields, cudaStream_t st);
 // synthesis: Y[blocked_row(group, k')][col] -> rows of x
 int launch_fft_synthesis(const Plan &pl, const float *Y, float *x, int nfields, cudaStream_t st);
+// register-resident two-pass kernels (fft_twopass.cu); the launchers above pick them when the plan has their tables
+bool twopass_supported(int nlon, int *r1, int *r2);
+int build_twopass_tables(Plan &pl, const std::vector<float> &mscale);
+int launch_fft_analysis_twopass(const Plan &pl, const float *x, float *X, int nfields, cudaStream_t st);
+int launch_fft_synthesis_twopass(const Plan &pl, const float *Y, float *x, int nfields, cudaStream_t st);
 // plain row transforms for the distributed stages
 int launch_rfft_modes(const float *in, float2 *out, long long nrows, int nlon, int nmodes, float scale, cudaStream_t st);
 int launch_irfft_modes(const float2 *in, float *out, long long nrows, int nlon, int nmodes, cudaStream_t st);
@@ -205,6 +214,11 @@ int launch_unpack_coeffs(const Plan &pl, const float *Z, float2 *c, int nfields,
 int launch_zero_upper(const Plan &pl, float2 *c, int nfields, int m0, int mloc, cudaStream_t st);
 int launch_fold_modes(const Plan &pl, const float2 *Xc, float *X, int nfields, int m0, int mloc, cudaStream_t st);
 int launch_unfold_modes(const Plan &pl, const float *Y, float2 *Xc, int nfields, int m0, int mloc, cudaStream_t st);  // honours group_krow0
+
+// spectral convolution on the degree slabs, spherical quadrature (spectral_conv.cu)
+size_t slab_mix_weight_bytes(int cin, int cout, int ngroups, int lmax);
+int launch_slab_mix(const Plan &pl, const float *Zin, float *Zout, const float2 *weight, float2 *wsplit, int batch, int cin, int cout, int ngroups, cudaStream_t st);
+int launch_quadrature(const float *x, const float *w, float *out, long long nfields, int nlat, int nlon, cudaStream_t st);
 
 // Row of (group, k) in the column-contiguous operands X and Y: 32-row blocks of k are outermost, then the group,
 // then k inside the block.  CTAs of the FFT kernels that run at the same time work on neighbouring k for ALL groups,

@@ -9,6 +9,7 @@ from typing import Optional, Tuple
 
 import numpy as np
 import torch
+import torch.nn as nn
 
 
 def _rescale(x: torch.Tensor, w: torch.Tensor, a: float, b: float):
@@ -60,6 +61,16 @@ def clenshaw_curtiss_weights(n: int, a: Optional[float] = -1.0, b: Optional[floa
     return _rescale(nodes, w, a, b)
 
 
+def trapezoidal_weights(n: int, a: Optional[float] = -1.0, b: Optional[float] = 1.0, periodic: Optional[bool] = False) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Equispaced nodes with trapezoidal weights (torch_harmonics/quadrature.py:140-174)."""
+    x = torch.as_tensor(np.linspace(a, b, n, endpoint=not periodic))
+    w = (b - a) / (n - 1 + int(periodic)) * torch.ones(n, dtype=x.dtype)
+    if not periodic:
+        w[0] *= 0.5
+        w[-1] *= 0.5
+    return x, w
+
+
 def precompute_longitudes(nlon: int) -> torch.Tensor:
     return torch.linspace(0, 2 * math.pi, nlon + 1, dtype=torch.float64)[:-1]
 
@@ -89,3 +100,64 @@ def precompute_latitudes(nlat: int, grid: Optional[str] = "equiangular"):
     """(colatitudes, weights), both flipped to run north to south (torch_harmonics/quadrature.py:109-137)."""
     cost, w = _nodes(nlat, grid)
     return torch.flip(torch.arccos(cost), dims=(0,)).clone(), torch.flip(w, dims=(0,)).clone()
+
+
+class _Quadrature(torch.autograd.Function):
+    """Integral over the last two axes with latitude weights (already times 2 pi / nlon): one reduction kernel forward;
+    the gradient is the weights broadcast along longitude times the incoming gradient."""
+
+    @staticmethod
+    def forward(ctx, x, w):
+        from . import _lib
+
+        xc = x.contiguous()
+        nlat, nlon = xc.shape[-2], xc.shape[-1]
+        out = torch.empty(xc.shape[:-2], dtype=torch.float32, device=x.device)
+        n = out.numel()
+        if n:
+            with torch.cuda.device(x.device):
+                _lib.quadrature(xc, w, out, n, nlat, nlon, torch.cuda.current_stream(x.device).cuda_stream)
+        ctx.save_for_backward(w)
+        ctx.nlon = nlon
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        (w,) = ctx.saved_tensors
+        return (g[..., None, None] * w[:, None]).expand(*g.shape, w.shape[0], ctx.nlon), None
+
+
+class QuadratureS2(nn.Module):
+    """Integral of a signal over the sphere, ``(..., nlat, nlon) -> (...)``.
+
+    Counterpart of torch_harmonics/quadrature.py:328-463: same constructor, the same ``quad_weight`` buffer
+    (1, 1, nlat, nlon) float32 and the same result; the reduction runs in one CUDA kernel on float32 CUDA input."""
+
+    def __init__(self, img_shape: Tuple[int], grid: Optional[str] = "equiangular", normalize: Optional[bool] = False):
+        super().__init__()
+        self.grid = grid
+        self.normalize = normalize
+        if grid == "legendre-gauss":
+            _, weights = legendre_gauss_weights(img_shape[0], -1, 1)
+        elif grid == "lobatto":
+            _, weights = lobatto_weights(img_shape[0], -1, 1)
+        elif grid == "equiangular":
+            _, weights = clenshaw_curtiss_weights(img_shape[0], -1, 1)
+        elif grid == "equiangular-trapezoidal":
+            _, weights = trapezoidal_weights(img_shape[0], -1, 1)
+        else:
+            raise ValueError("Unknown quadrature mode")
+        lat = (2 * math.pi / img_shape[1]) * weights
+        if normalize:
+            lat = lat / (4.0 * math.pi)
+        quad_weight = lat.unsqueeze(1).tile(1, img_shape[1]).reshape(1, 1, *img_shape).to(torch.float32).contiguous()
+        self.register_buffer("quad_weight", quad_weight, persistent=False)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if not x.is_cuda:
+            raise RuntimeError("QuadratureS2: expected a CUDA tensor; torch_harmonics_b200 has no CPU path")
+        if x.dtype != torch.float32:
+            raise TypeError(f"QuadratureS2: expected dtype torch.float32, got {x.dtype}")
+        if x.shape[-2:] != self.quad_weight.shape[-2:]:
+            raise RuntimeError(f"Expected spatial shape {tuple(self.quad_weight.shape[-2:])}, got {tuple(x.shape[-2:])}")
+        return _Quadrature.apply(x, self.quad_weight[0, 0, :, 0].contiguous())

@@ -66,6 +66,13 @@ const char *shtb200_last_error(void);
  * Replaces the constructors' buffer set-up, sht.py:113-146, 269-301, 411-449, 569-601.
  */
 int shtb200_plan_create(shtb200_plan **plan, int kind, int nlat, int nlon, int lmax, int mmax, const float *table_dev, int device, int engine);
+/*
+ * The same for a WINDOW of orders m_first .. m_first + m_count - 1: `table_dev` holds those orders only ((m_count, lmax, nlat),
+ * (m_count, nlat, lmax), or the vector layouts with m_count in place of mmax).  This is what one azimuth rank of the spatially
+ * distributed transforms keeps (torch_harmonics/distributed/distributed_sht.py:164, :333, :490, :645 slice the tables the same
+ * way).  Such a plan serves shtb200_legendre only (first order m0 >= m_first); the whole-transform calls refuse it.
+ */
+int shtb200_plan_create_orders(shtb200_plan **plan, int kind, int nlat, int nlon, int lmax, int m_first, int m_count, const float *table_dev, int device, int engine);
 int shtb200_plan_destroy(shtb200_plan *plan);
 
 /* Bytes of device scratch a call on `nfields` 2-D fields needs (vector kinds: nfields = number of (u,v) pairs). */

@@ -250,6 +250,24 @@ def test_stage_entry_points(engine):
     ref = np.einsum("nlm,mkl->nkm", c.astype(np.complex128), p[m0:m0 + mloc])
     assert err(out.cpu().numpy(), ref) <= TOL
 
+    # plans that hold a window of orders only (what one azimuth rank of the distributed transforms keeps), called on the
+    # whole window and on a part of it
+    from torch_harmonics_b200 import _lib as L_
+
+    for kind, table, rows_in, rows_out, spec in ((L_.SHT, w, nlat, L, "nkm,mlk->nlm"), (L_.ISHT, p, L, nlat, "nlm,mkl->nkm")):
+        t32 = torch.from_numpy(np.ascontiguousarray(table[m0:m0 + mloc])).to(device="cuda", dtype=torch.float32)
+        wplan = L_.Plan(kind, nlat, nlon, L, M, t32, engine=engine, orders=(m0, mloc))
+        for a, n in ((m0, mloc), (m0 + 2, 4)):
+            xin = (rng.standard_normal((nf, rows_in, n)) + 1j * rng.standard_normal((nf, rows_in, n))).astype(np.complex64)
+            out = torch.full((nf, rows_out, n), float("nan"), dtype=torch.complex64, device="cuda")
+            ws = torch.empty(wplan.legendre_workspace_bytes(nf, n), dtype=torch.uint8, device="cuda")
+            wplan.legendre(torch.from_numpy(xin).cuda(), out, nf, a, n, ws, 0)
+            torch.cuda.synchronize()
+            assert err(out.cpu().numpy(), np.einsum(spec, xin.astype(np.complex128), table[a:a + n])) <= TOL
+        with pytest.raises(L_.ShtLibraryError, match="inside the plan"):
+            wplan.legendre(torch.from_numpy(xin).cuda(), out, nf, m0 - 1, 2, ws, 0)
+        assert wplan.workspace_bytes(nf) == 0  # whole-transform calls refuse a window plan
+
 
 @pytest.mark.parametrize("engine", ENGINES)
 def test_host_buffer_call_pipelined_chunks(engine):

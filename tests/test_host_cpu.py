@@ -76,3 +76,46 @@ def test_package_truncation():
         truncate_sht(8, 16, grid="nope")
     with pytest.warns(UserWarning):
         truncate_sht(8, 16, grid="equiangular")
+
+
+def test_quadrature_and_random_field_buffers_match_reference():
+    """Host-side set-up of QuadratureS2 / GaussianRandomFieldS2 / SpectralConvS2 against buffers of the reference
+    (tests/golden/spectral_conv.npz)."""
+    import torch_harmonics_b200 as th
+
+    g = np.load(os.path.join(ROOT, "tests", "golden", "spectral_conv.npz"))
+    for grid in ("equiangular", "legendre-gauss", "lobatto", "equiangular-trapezoidal"):
+        for normalize in (False, True):
+            q = th.QuadratureS2((13, 24), grid=grid, normalize=normalize)
+            assert q.quad_weight.shape == (1, 1, 13, 24) and q.quad_weight.dtype == torch.float32
+            assert np.allclose(q.quad_weight[0, 0, :, 0].numpy(), g[f"quad|{grid}|{int(normalize)}"], rtol=1e-6, atol=0)
+    with pytest.raises(ValueError):
+        th.QuadratureS2((13, 24), grid="nope")
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        grf = th.GaussianRandomFieldS2(16, alpha=2.5, tau=4.0)
+        assert [grf.isht.lmax, grf.isht.mmax] == list(g["grf|lm"])
+        assert np.allclose(grf.sqrt_eig.numpy(), g["grf|sqrt_eig"], rtol=1e-6)
+        with pytest.raises(ValueError):
+            th.GaussianRandomFieldS2(16, alpha=1.0)
+        conv = th.SpectralConvS2((17, 32), (12, 24), 6, 4, num_groups=2, grid_in="equiangular", grid_out="legendre-gauss", bias=True)
+        assert conv.lmax == int(g["groups_resample|lmax"]) and conv.weight.shape == (2, 3, 2, conv.lmax)
+        assert conv.spectral_bias.shape == (1, 6, conv.lmax, conv.mmax) and conv.weight.dtype == torch.complex64
+        with pytest.raises(ValueError):
+            th.SpectralConvS2((17, 32), (17, 32), 6, 4, num_groups=4)
+
+
+def test_windowed_tables_equal_slices_of_the_full_tables():
+    """A distributed rank builds the Legendre tables of its own orders only: bit-identical to the matching slice of the
+    full table, scalar and vector, every normalisation."""
+    from torch_harmonics_b200.legendre import _precompute_dlegpoly, _precompute_legpoly
+
+    t = torch.linspace(0.01, 3.13, 23, dtype=torch.float64)
+    for norm in ("ortho", "schmidt", "four-pi"):
+        for inverse in (False, True):
+            for cs in (True, False):
+                full = _precompute_legpoly(12, 14, t, norm=norm, inverse=inverse, csphase=cs)
+                dfull = _precompute_dlegpoly(12, 14, t, norm=norm, inverse=inverse, csphase=cs)
+                for first, count in ((0, 5), (3, 4), (5, 7), (11, 1), (0, 12)):
+                    assert torch.equal(_precompute_legpoly(12, 14, t, norm=norm, inverse=inverse, csphase=cs, m_first=first, m_count=count), full[first:first + count])
+                    assert torch.equal(_precompute_dlegpoly(12, 14, t, norm=norm, inverse=inverse, csphase=cs, m_first=first, m_count=count), dfull[:, first:first + count])

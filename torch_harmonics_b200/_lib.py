@@ -41,6 +41,8 @@ def load():
         lib.shtb200_last_error.restype = ctypes.c_char_p
         lib.shtb200_plan_create.argtypes = [ctypes.POINTER(vp), ci, ci, ci, ci, ci, vp, ci, ci]
         lib.shtb200_plan_create.restype = ci
+        lib.shtb200_plan_create_orders.argtypes = [ctypes.POINTER(vp), ci, ci, ci, ci, ci, ci, vp, ci, ci]
+        lib.shtb200_plan_create_orders.restype = ci
         lib.shtb200_plan_destroy.argtypes = [vp]
         lib.shtb200_plan_destroy.restype = ci
         lib.shtb200_workspace_bytes.argtypes = [vp, ci]
@@ -109,7 +111,9 @@ def quadrature(x, lat_weights, out, nfields, nlat, nlon, stream):
 class Plan:
     """Owner of one ``shtb200_plan``."""
 
-    def __init__(self, kind, nlat, nlon, lmax, mmax, table_f32_cuda, engine="auto"):
+    def __init__(self, kind, nlat, nlon, lmax, mmax, table_f32_cuda, engine="auto", orders=None):
+        """``orders = (m_first, m_count)`` builds a plan for that window of orders from a table that holds them only
+        (``shtb200_plan_create_orders``); such a plan serves :meth:`legendre` alone."""
         import torch
 
         lib = load()
@@ -119,9 +123,14 @@ class Plan:
         self.device = table_f32_cuda.device
         self.handle = ctypes.c_void_p()
         torch.cuda.synchronize(self.device)
-        rc = lib.shtb200_plan_create(
-            ctypes.byref(self.handle), kind, nlat, nlon, lmax, mmax, ctypes.c_void_p(table_f32_cuda.data_ptr()), self.device.index or 0, ENGINES[engine]
-        )
+        if orders is None:
+            rc = lib.shtb200_plan_create(
+                ctypes.byref(self.handle), kind, nlat, nlon, lmax, mmax, ctypes.c_void_p(table_f32_cuda.data_ptr()), self.device.index or 0, ENGINES[engine]
+            )
+        else:
+            rc = lib.shtb200_plan_create_orders(
+                ctypes.byref(self.handle), kind, nlat, nlon, lmax, int(orders[0]), int(orders[1]), ctypes.c_void_p(table_f32_cuda.data_ptr()), self.device.index or 0, ENGINES[engine]
+            )
         check(rc, "shtb200_plan_create")
 
     def workspace_bytes(self, nfields):

@@ -53,8 +53,10 @@ struct WsLayout {
     size_t total() const { return align256(op_bytes) + align256(y_bytes) + align256(extra_bytes); }
 };
 
+// (m0 = first order of the call, an actual order inside the plan's window)
 WsLayout ws_layout(const Plan &pl, int nfields, int m0, int mloc) {
     WsLayout w;
+    m0 -= pl.m_base;
     const size_t ncols = (size_t)(pl.vector ? 4 : 2) * nfields;
     const size_t ncp = (size_t)col_pitch((long long)ncols);  // row pitch of the column-contiguous operands
     if (pl.analysis) {
@@ -82,6 +84,8 @@ GemmParams gemm_params(const Plan &pl, int nfields, int m0, int mloc, const floa
     gp.lmax = pl.lmax;
     gp.mmax_out = mloc;
     gp.m0 = m0;
+    gp.m_base = pl.m_base;
+    const int ml = m0 - pl.m_base;  // first order of the call inside the plan's window
     if (pl.analysis) {
         gp.b_mn = 1;
         gp.b_krows = pl.Ka;
@@ -89,15 +93,15 @@ GemmParams gemm_params(const Plan &pl, int nfields, int m0, int mloc, const floa
         gp.b_pitch = col_pitch(gp.ncols);
         gp.b_dx = kBK;
         gp.b_kext = pl.Ka;
-        gp.b_unit0 = 2 * m0;
+        gp.b_unit0 = 2 * ml;
         gp.mode = pl.vector ? EPI_COEFFS : EPI_SLABS;
         gp.slab0 = pl.d_gb0;
-        gp.slab_unit0 = pl.group_b0[2 * m0];
+        gp.slab_unit0 = pl.group_b0[2 * ml];
     } else {
         gp.b_pitch = kBK;
         gp.b_dx = 0;
         gp.b_kext = kBK;
-        gp.b_unit0 = pl.group_b0[2 * m0];
+        gp.b_unit0 = pl.group_b0[2 * ml];
         gp.mode = EPI_LATROWS;
         gp.out_ld = col_pitch(gp.ncols);
         gp.out_groups = 2 * mloc;
@@ -125,6 +129,7 @@ int run_gemm(Plan &pl, const GemmParams &gp, cudaStream_t st) {
 
 // Y slices of groups that contain no degree at all are never produced by the contraction.
 int clear_empty_groups(const Plan &pl, float *Y, int ncols, int m0, int mloc, cudaStream_t st) {
+    m0 -= pl.m_base;
     for (int g = 2 * m0; g < 2 * (m0 + mloc); ++g) {
         if (pl.group_kblocks[g] == 0) {
             const size_t ncp = (size_t)col_pitch(ncols);
@@ -136,6 +141,7 @@ int clear_empty_groups(const Plan &pl, float *Y, int ncols, int m0, int mloc, cu
 }
 
 int execute_full(Plan &pl, const void *in, void *out, int nfields, void *ws, size_t ws_bytes, cudaStream_t st) {
+    if (pl.window) return fail(SHTB200_EINVAL, "a plan created for a window of orders serves shtb200_legendre only");
     if (nfields < 0) return fail(SHTB200_EINVAL, "nfields must be >= 0");
     pl.last_launches = 0;
     if (nfields == 0) return SHTB200_OK;
@@ -202,13 +208,17 @@ int shtb200_version(void) { return 100; }
 
 const char *shtb200_last_error(void) { return g_last_error.c_str(); }
 
-int shtb200_plan_create(shtb200_plan **plan_out, int kind, int nlat, int nlon, int lmax, int mmax, const float *table_dev, int device, int engine) {
+}  // extern "C"
+
+// `mmax` orders starting at `m_base`; `window` marks a plan that serves the Legendre stage only
+static int plan_create_impl(shtb200_plan **plan_out, int kind, int nlat, int nlon, int lmax, int m_base, int mmax, bool window, const float *table_dev, int device,
+                            int engine) {
     if (!plan_out) return fail(SHTB200_EINVAL, "plan_out is null");
     *plan_out = nullptr;
     if (kind < SHTB200_SHT || kind > SHTB200_IVSHT_ADJOINT) return fail(SHTB200_EINVAL, "unknown plan kind");
     if (engine < SHTB200_ENGINE_AUTO || engine > SHTB200_ENGINE_TCGEN05) return fail(SHTB200_EINVAL, "unknown engine");
     if (nlat < 2 || nlon < 2 || lmax < 1 || mmax < 1) return fail(SHTB200_EINVAL, "nlat, nlon >= 2 and lmax, mmax >= 1 required");
-    if (mmax > lmax) return fail(SHTB200_EINVAL, "mmax must not exceed lmax (triangular truncation)");
+    if (m_base < 0 || m_base + mmax > lmax) return fail(SHTB200_EINVAL, "mmax must not exceed lmax (triangular truncation)");
     if (!table_dev) return fail(SHTB200_EINVAL, "table_dev is null");
     int ndev = 0;
     if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0) return fail(SHTB200_ECUDA, "no CUDA device available: this library has no CPU path");
@@ -224,6 +234,8 @@ int shtb200_plan_create(shtb200_plan **plan_out, int kind, int nlat, int nlon, i
     pl->nlon = nlon;
     pl->lmax = lmax;
     pl->mmax = mmax;
+    pl->m_base = m_base;
+    pl->window = window;
     pl->analysis = is_analysis(kind);
     pl->vector = is_vector(kind);
     pl->ncomp = pl->vector ? 2 : 1;
@@ -241,7 +253,8 @@ int shtb200_plan_create(shtb200_plan **plan_out, int kind, int nlat, int nlon, i
     // per-order scale applied inside the FFT kernels
     std::vector<float> ms(mmax);
     {
-        for (int m = 0; m < mmax; ++m) {
+        for (int ml = 0; ml < mmax; ++ml) {
+            const int m = m_base + ml;
             const bool edge = (m == 0) || (2 * m == nlon);
             double s = 1.0;
             switch (kind) {
@@ -250,7 +263,7 @@ int shtb200_plan_create(shtb200_plan **plan_out, int kind, int nlat, int nlon, i
                 case SHTB200_SHT_ADJOINT: case SHTB200_VSHT_ADJOINT: s = (2.0 * M_PI / nlon) * (edge ? 1.0 : 0.5); break;
                 case SHTB200_ISHT_ADJOINT: case SHTB200_IVSHT_ADJOINT: s = edge ? 1.0 : 2.0; break;
             }
-            ms[m] = (float)s;
+            ms[ml] = (float)s;
         }
         if ((rc = upload(&pl->d_mscale, ms))) { shtb200_plan_destroy(pl); return rc; }
         pl->zero_imag_edges = (kind == SHTB200_ISHT_ADJOINT || kind == SHTB200_IVSHT_ADJOINT) ? 1 : 0;
@@ -261,7 +274,7 @@ int shtb200_plan_create(shtb200_plan **plan_out, int kind, int nlat, int nlon, i
     pl->group_rows.assign(ngroups, 0);
     for (int m = 0; m < mmax; ++m)
         for (int p = 0; p < 2; ++p) {
-            int cnt = lmax - m - p;
+            int cnt = lmax - (m_base + m) - p;
             pl->group_rows[2 * m + p] = cnt > 0 ? (cnt + 1) / 2 : 0;
         }
     // Polar extent of every group, in whole 32-row blocks.  The cut-off is far below what fp32 keeps next to the
@@ -274,8 +287,9 @@ int shtb200_plan_create(shtb200_plan **plan_out, int kind, int nlat, int nlon, i
         // fewer rows is always correct; the contraction and the FFT kernels read the same clamped value).
         for (int g = 0; g < ngroups; ++g) pl->group_krow0[g] = std::min(std::min(first[g], std::max(pl->Kh - 1, 0)) / kBK, kMaxPolarBlock) * kBK;
     }
-    if ((rc = build_fft_plan(nlon, mmax, pl->analysis ? kFftSplit : kFftPacked, pl->group_krow0.data(), &pl->fft, &pl->d_tw, &pl->d_perm)) ||
-        (rc = build_twopass_tables(*pl, ms))) {
+    // (a window plan never runs a longitude transform)
+    if (!window && ((rc = build_fft_plan(nlon, mmax, pl->analysis ? kFftSplit : kFftPacked, pl->group_krow0.data(), &pl->fft, &pl->d_tw, &pl->d_perm)) ||
+                    (rc = build_twopass_tables(*pl, ms)))) {
         shtb200_plan_destroy(pl);
         return rc;
     }
@@ -306,7 +320,7 @@ int shtb200_plan_create(shtb200_plan **plan_out, int kind, int nlat, int nlon, i
                 it.kfirst = pl->group_krow0[g] / kBK;
                 it.kblocks = kblocks - it.kfirst;
                 it.rows = std::min(kItemRowsMax, pl->group_rows[g] - r0);
-                it.m = g >> 1;
+                it.m = m_base + (g >> 1);
                 it.p = g & 1;
                 it.r0 = r0;
                 pl->items.push_back(it);
@@ -337,7 +351,7 @@ int shtb200_plan_create(shtb200_plan **plan_out, int kind, int nlat, int nlon, i
                 it.b_dy = 1;
                 it.kblocks = pl->group_kblocks[g];
                 it.rows = std::min(kItemRowsMax, pl->Kh - r0);
-                it.m = g >> 1;
+                it.m = m_base + (g >> 1);
                 it.p = g & 1;
                 it.r0 = r0;
                 pl->items.push_back(it);
@@ -349,9 +363,9 @@ int shtb200_plan_create(shtb200_plan **plan_out, int kind, int nlat, int nlon, i
     // time share the group's operand through L2 instead of fetching it from HBM again later.
     {
         std::vector<long long> gwork(ngroups, 0);
-        for (const GemmItem &it : pl->items) gwork[2 * it.m + it.p] += (long long)it.kblocks * it.rows;
-        std::stable_sort(pl->items.begin(), pl->items.end(), [&gwork](const GemmItem &a, const GemmItem &b) {
-            const int ga = 2 * a.m + a.p, gb = 2 * b.m + b.p;
+        for (const GemmItem &it : pl->items) gwork[2 * (it.m - m_base) + it.p] += (long long)it.kblocks * it.rows;
+        std::stable_sort(pl->items.begin(), pl->items.end(), [&gwork, m_base](const GemmItem &a, const GemmItem &b) {
+            const int ga = 2 * (a.m - m_base) + a.p, gb = 2 * (b.m - m_base) + b.p;
             if (gwork[ga] != gwork[gb]) return gwork[ga] > gwork[gb];
             if (ga != gb) return ga < gb;
             return a.r0 < b.r0;
@@ -374,6 +388,17 @@ int shtb200_plan_create(shtb200_plan **plan_out, int kind, int nlat, int nlon, i
     if ((rc = launch_pack_table(*pl, table_dev, 0))) { shtb200_plan_destroy(pl); return rc; }
     *plan_out = pl;
     return SHTB200_OK;
+}
+
+extern "C" {
+
+int shtb200_plan_create(shtb200_plan **plan_out, int kind, int nlat, int nlon, int lmax, int mmax, const float *table_dev, int device, int engine) {
+    if (mmax > lmax) return fail(SHTB200_EINVAL, "mmax must not exceed lmax (triangular truncation)");
+    return plan_create_impl(plan_out, kind, nlat, nlon, lmax, 0, mmax, false, table_dev, device, engine);
+}
+
+int shtb200_plan_create_orders(shtb200_plan **plan_out, int kind, int nlat, int nlon, int lmax, int m_first, int m_count, const float *table_dev, int device, int engine) {
+    return plan_create_impl(plan_out, kind, nlat, nlon, lmax, m_first, m_count, true, table_dev, device, engine);
 }
 
 int shtb200_plan_destroy(shtb200_plan *pl) {
@@ -406,7 +431,7 @@ int shtb200_plan_destroy(shtb200_plan *pl) {
 }
 
 size_t shtb200_workspace_bytes(const shtb200_plan *pl, int nfields) {
-    if (!pl || nfields <= 0) return 0;
+    if (!pl || nfields <= 0 || pl->window) return 0;
     return ws_layout(*pl, nfields, 0, pl->mmax).total();
 }
 
@@ -419,6 +444,7 @@ int shtb200_execute(shtb200_plan *pl, const void *in_dev, void *out_dev, int nfi
 
 int shtb200_execute_host(shtb200_plan *pl, const void *in_host, void *out_host, int nfields, void *stream) {
     if (!pl) return fail(SHTB200_EINVAL, "plan is null");
+    if (pl->window) return fail(SHTB200_EINVAL, "a plan created for a window of orders serves shtb200_legendre only");
     if (nfields < 0) return fail(SHTB200_EINVAL, "nfields must be >= 0");
     if (nfields == 0) return SHTB200_OK;
     if (!in_host || !out_host) return fail(SHTB200_EINVAL, "null host pointer");
@@ -488,6 +514,7 @@ struct ConvLayout {
     size_t total() const { return align256(op) + align256(zin) + align256(zout) + align256(wsplit); }
 };
 int conv_layout(const Plan &pa, const Plan &ps, int batch, int cin, int cout, int ngroups, ConvLayout *out) {
+    if (pa.window || ps.window) return fail(SHTB200_EINVAL, "a plan created for a window of orders serves shtb200_legendre only");
     if (pa.vector || ps.vector || !pa.analysis || ps.analysis) return fail(SHTB200_EINVAL, "spectral convolution needs a scalar analysis plan and a scalar synthesis plan");
     if (pa.lmax != ps.lmax || pa.mmax != ps.mmax) return fail(SHTB200_EINVAL, "the two plans of a spectral convolution must share lmax and mmax");
     if (pa.device != ps.device) return fail(SHTB200_EINVAL, "the two plans of a spectral convolution must live on the same device");
@@ -617,13 +644,13 @@ int shtb200_irfft_modes(const void *in_dev, float *out_dev, long long nrows, int
 
 size_t shtb200_legendre_workspace_bytes(const shtb200_plan *pl, int nfields, int mloc) {
     if (!pl || nfields <= 0 || mloc <= 0) return 0;
-    // sized for the worst first order (m0 = 0 holds the longest groups)
-    return ws_layout(*pl, nfields, 0, std::min(mloc, pl->mmax)).total();
+    // sized for the worst first order (the plan's first order holds the longest groups)
+    return ws_layout(*pl, nfields, pl->m_base, std::min(mloc, pl->mmax)).total();
 }
 
 int shtb200_legendre(shtb200_plan *pl, const void *in_dev, void *out_dev, int nfields, int m0, int mloc, void *workspace_dev, size_t workspace_bytes, void *stream) {
     if (!pl) return fail(SHTB200_EINVAL, "plan is null");
-    if (nfields < 0 || m0 < 0 || mloc < 0 || m0 + mloc > pl->mmax) return fail(SHTB200_EINVAL, "bad (nfields, m0, mloc)");
+    if (nfields < 0 || mloc < 0 || m0 < pl->m_base || m0 + mloc > pl->m_base + pl->mmax) return fail(SHTB200_EINVAL, "bad (nfields, m0, mloc): the orders must lie inside the plan");
     pl->last_launches = 0;
     if (nfields == 0 || mloc == 0) return SHTB200_OK;
     if (!in_dev || !out_dev) return fail(SHTB200_EINVAL, "null pointer");

@@ -109,6 +109,7 @@ struct GemmParams {
     float *out;           // destination
     int lmax, mmax_out;   // EPI_COEFFS: out dims (mmax_out = number of orders stored = mloc)
     int m0;               // first order stored in out (orders outside [m0, m0 + mmax_out) are skipped)
+    int m_base;           // first order the plan holds: slab0 is indexed by 2 (m - m_base) + p
     long long out_ld;     // EPI_LATROWS: floats per row of Y
     int out_groups;       // EPI_LATROWS: groups held in Y
     const long long *slab0;  // EPI_SLABS: first slab of every group (device array, 2 * mmax + 1 entries)
@@ -122,6 +123,11 @@ struct Plan {
     int kind = 0, engine = 0, device = 0;
     int sm_count = 0;  // multiprocessors of `device` (grid size of the persistent contraction kernel)
     int nlat = 0, nlon = 0, lmax = 0, mmax = 0;
+    // A plan may hold a window of orders only (the spatially distributed transforms contract the orders of one azimuth
+    // rank): m_base = first order of the window, mmax = number of orders in it.  Group arrays are indexed by the local
+    // group 2 (m - m_base) + p; GemmItem::m and every degree computation use the actual order m.
+    int m_base = 0;
+    bool window = false;  // created for a window: only the Legendre stage entry point accepts the plan
     int Kh = 0;   // folded latitude count, (nlat + 1) / 2
     int Ka = 0;   // contraction length of the analysis kinds, ncomp * Kh
     int Lh = 0;   // largest number of degrees of one parity, (lmax + 1) / 2
@@ -209,6 +215,7 @@ int launch_pack_table(Plan &pl, const float *table, cudaStream_t st);
 // first_row[2 m + p] = first folded latitude k' at which any degree l = m + p + 2 r of the dense table reaches `rel` times
 // that degree's largest magnitude over all latitudes (Kh if none does)
 int launch_polar_extent(const Plan &pl, const float *table, float rel, std::vector<int> *first_row);
+// (m0 = first order of the call, an actual order: m_base <= m0, m0 + mloc <= m_base + mmax)
 int launch_pack_coeffs(const Plan &pl, const float2 *c, float *Ct, int nfields, int m0, int mloc, cudaStream_t st);
 int launch_unpack_coeffs(const Plan &pl, const float *Z, float2 *c, int nfields, int m0, int mloc, cudaStream_t st);
 int launch_zero_upper(const Plan &pl, float2 *c, int nfields, int m0, int mloc, cudaStream_t st);

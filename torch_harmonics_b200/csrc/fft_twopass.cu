@@ -252,7 +252,7 @@ template <int R1, int R2>
 __global__ void __launch_bounds__(TwoPass<R1, R2>::THREADS, 2) fft_synthesis_twopass_kernel(const TwoPassArgs a) {
     using TP = TwoPass<R1, R2>;
     constexpr int N = TP::N, TS = TP::TS, TS2 = TP::TS / 2;
-    constexpr int CH = 5;  // orders whose loads are in flight together
+    constexpr int CH = 5;  // orders whose loads are in flight together (measured: more in flight, or asking the next item's rows into L2 ahead of time, is slower)
     extern __shared__ __align__(16) float smem_tp[];
     unsigned char *blob_s = reinterpret_cast<unsigned char *>(smem_tp + kNT * TS);
     const uint32_t bar_tab = ptx::smem_u32(blob_s + a.blob_bytes);
@@ -271,8 +271,6 @@ __global__ void __launch_bounds__(TwoPass<R1, R2>::THREADS, 2) fft_synthesis_two
     for (int it = blockIdx.x; it < nitems; it += gridDim.x) {
         // ---- gather the even / odd parts of the retained orders, rebuild the Hermitian spectrum of north + i south ----
         float2 u[R2];
-#pragma unroll
-        for (int r = 0; r < R2; ++r) u[r] = make_float2(0.f, 0.f);
         {
             const int tid = tid_now();
             const int t = tid & 7, q = q_of<R1>(tid >> 5, (tid >> 3) & 3);
@@ -285,11 +283,14 @@ __global__ void __launch_bounds__(TwoPass<R1, R2>::THREADS, 2) fft_synthesis_two
             const unsigned char *kf_s = reinterpret_cast<const unsigned char *>(ms_s + a.mpad);
             const float *yb = a.op + ((size_t)(kn >> 5) * ngroups * 32 + (kn & 31)) * a.ncp + 2 * (f0 + t);
             const size_t gstride = (size_t)32 * a.ncp;
+            // the loads of CH orders are issued before the first of them is used
+#pragma unroll
+            for (int r = 0; r < R2; ++r) u[r] = make_float2(0.f, 0.f);
 #pragma unroll
             for (int i0 = 0; i0 <= R2 / 2; i0 += CH) {
                 float2 ev[CH], ov[CH];
 #pragma unroll
-                for (int c = 0; c < CH; ++c) {  // the loads of a chunk are issued before the first of them is used
+                for (int c = 0; c < CH; ++c) {
                     const int i = i0 + c, m = q + R1 * i;
                     ev[c] = ov[c] = make_float2(0.f, 0.f);
                     if (i <= R2 / 2 && active && m < mtop) {
@@ -299,28 +300,32 @@ __global__ void __launch_bounds__(TwoPass<R1, R2>::THREADS, 2) fft_synthesis_two
                         if (kn >= (kf >> 4) * kBK) ov[c] = __ldg(reinterpret_cast<const float2 *>(pe + gstride));
                     }
                 }
+                // bin m -> register i.  Bin n - m -> register R2 - 1 - i of the thread that owns R1 - q, i.e. of the partner
+                // lane (of this thread itself for q = R1 / 2); for q = 0 it is this thread's register R2 - i.  DC and Nyquist
+                // have no mirror bin.  Orders that are not retained contribute zeros.
 #pragma unroll
                 for (int c = 0; c < CH; ++c) {
                     const int i = i0 + c, m = q + R1 * i;
                     if (i > R2 / 2) continue;
-                    const bool have = active && m < mtop;
-                    const float sc = have ? ms_s[m] : 0.f;
+                    const float sc = (active && m < mtop) ? ms_s[m] : 0.f;
                     // north row spectrum A = even + odd, south row spectrum B = even - odd; Z_m = A + i B, Z_{n-m} = conj A + i conj B
                     const float ar = sc * (ev[c].x + ov[c].x), ai = sc * (ev[c].y + ov[c].y);
                     const float br = sc * (ev[c].x - ov[c].x), bi = sc * (ev[c].y - ov[c].y);
-                    const bool edge = (m == 0) || (2 * m == N);  // imaginary parts of DC / Nyquist are dropped, no mirror bin
+                    const bool edge = (m == 0) || (2 * m == N);  // imaginary parts of DC / Nyquist are dropped
                     const float2 zm = edge ? make_float2(ar, br) : make_float2(ar - bi, ai + br);
                     const float2 zn = edge ? make_float2(0.f, 0.f) : make_float2(ar + bi, br - ai);
                     float2 got;
                     got.x = __shfl_xor_sync(0xffffffffu, zn.x, 16);
                     got.y = __shfl_xor_sync(0xffffffffu, zn.y, 16);
-                    // bin m -> register i.  Bin n - m -> register R2 - 1 - i of the thread that owns R1 - q, i.e. of the
-                    // partner lane (of this thread itself for q = R1 / 2); for q = 0 it is this thread's register R2 - i.
-                    // DC and Nyquist have no mirror bin.  Every assignment is unconditional with the old value as the
-                    // alternative, so that the register array never looks conditionally initialised.
-                    u[i] = have ? zm : u[i];
-                    if (i < R2 / 2) u[R2 - 1 - i] = (q == 0) ? u[R2 - 1 - i] : (q == R1 / 2) ? (have ? zn : u[R2 - 1 - i]) : got;
-                    if (i >= 1 && i < R2 / 2) u[R2 - i] = (q == 0 && have) ? zn : u[R2 - i];
+                    // every assignment is unconditional (a select with the old value), so that the register array never looks
+                    // conditionally initialised; for q = 0 register R2 - 1 - i first takes a placeholder and the next order fills it
+                    if (i < R2 / 2) {
+                        u[i] = zm;
+                        u[R2 - 1 - i] = (q == R1 / 2) ? zn : got;
+                        if (i >= 1) u[R2 - i] = (q == 0) ? zn : u[R2 - i];
+                    } else {
+                        u[i] = (q == 0) ? zm : u[i];  // order R1 R2 / 2 = n / 2 exists for q = 0 only
+                    }
                 }
             }
         }

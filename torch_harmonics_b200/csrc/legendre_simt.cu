@@ -91,7 +91,7 @@ __global__ void __launch_bounds__(256) legendre_simt_kernel(GemmParams gp) {
                 *o = make_float2(acc[i][j], acc[i][j + 1]);
             }
         } else if (gp.mode == EPI_SLABS) {
-            const long long slab = gp.slab0[2 * it.m + it.p] - gp.slab_unit0 + (rg >> 5);
+            const long long slab = gp.slab0[2 * (it.m - gp.m_base) + it.p] - gp.slab_unit0 + (rg >> 5);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const int c = col0 + tx * 4 + j;

@@ -364,7 +364,7 @@ legendre_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                         if (col < gp.ncols) o[(size_t)(col >> 1) * fstride] = make_float2(v[j], v[j + 1]);
                     }
                 } else if (gp.mode == EPI_SLABS) {
-                    const long long slab = gp.slab0[2 * w.it.m + w.it.p] - gp.slab_unit0 + (rg >> 5);
+                    const long long slab = gp.slab0[2 * (w.it.m - gp.m_base) + w.it.p] - gp.slab_unit0 + (rg >> 5);
                     float *o = gp.out + (size_t)slab * gp.ncols * kBK + (rg & 31);
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
@@ -463,7 +463,7 @@ int launch_gemm_tc(const Plan &pl, const GemmParams &gp, cudaStream_t st) {
         a_inner = kBK;
         a_rows = pl.group_a0.back() + kItemRowsMax;
         b_inner = kBK;
-        b_rows = (pl.group_b0[2 * (gp.m0 + gp.mmax_out)] - pl.group_b0[2 * gp.m0]) * (long long)gp.ncols;
+        b_rows = (pl.group_b0[2 * (gp.m0 - pl.m_base + gp.mmax_out)] - pl.group_b0[2 * (gp.m0 - pl.m_base)]) * (long long)gp.ncols;
     }
     CUtensorMap tmA, tmB;
     int rc;

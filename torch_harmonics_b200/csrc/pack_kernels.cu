@@ -21,7 +21,9 @@ namespace {
 struct TableView {
     const float *t;
     int mmax, lmax, nlat;
-    int mkl;  // 0: (.., m, l, k)   1: (.., m, k, l)
+    int mkl;    // 0: (.., m, l, k)   1: (.., m, k, l)
+    int mbase;  // order of the table's first row block (the table holds orders mbase .. mbase + mmax - 1)
+    // m: index into the table (order minus mbase)
     __device__ float at(int seg, int m, int l, int k) const {
         size_t base = (size_t)seg * mmax * lmax * nlat;
         return mkl ? t[base + ((size_t)m * nlat + k) * lmax + l] : t[base + ((size_t)m * lmax + l) * nlat + k];
@@ -31,12 +33,12 @@ struct TableView {
 // One CTA per order m, one warp per degree l at a time: the degree's largest magnitude over the northern latitudes, then
 // the first latitude that reaches rel times it; the minimum over the degrees of each parity is the group's answer.
 __global__ void polar_extent_kernel(TableView tv, int Kh, float rel, int *first_row) {
-    const int m = blockIdx.x;
+    const int m = blockIdx.x;  // index inside the plan's window of orders
     __shared__ int s_first[2];
     if (threadIdx.x < 2) s_first[threadIdx.x] = Kh;
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-    for (int l = m + warp; l < tv.lmax; l += nwarps) {
+    for (int l = m + tv.mbase + warp; l < tv.lmax; l += nwarps) {
         float mx = 0.f;
         for (int k = lane; k < Kh; k += 32) mx = fmaxf(mx, fabsf(tv.at(0, m, l, k)));
         for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
@@ -45,7 +47,7 @@ __global__ void polar_extent_kernel(TableView tv, int Kh, float rel, int *first_
             for (int k = lane; k < Kh && first == Kh; k += 32)
                 if (fabsf(tv.at(0, m, l, k)) >= rel * mx) first = k;
         for (int o = 16; o; o >>= 1) first = min(first, __shfl_xor_sync(0xffffffffu, first, o));
-        if (lane == 0) atomicMin(&s_first[(l - m) & 1], first);
+        if (lane == 0) atomicMin(&s_first[(l - m - tv.mbase) & 1], first);
     }
     __syncthreads();
     if (threadIdx.x < 2) first_row[2 * m + threadIdx.x] = s_first[threadIdx.x];
@@ -60,7 +62,7 @@ __global__ void pack_table_rows_kernel(TableView tv, float *A, const long long *
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         const int r = (int)(i / pitch), c = (int)(i - (long long)r * pitch);
         const int seg = c / Kh, k = c - seg * Kh;
-        const int l = m + p + 2 * r;
+        const int l = m + tv.mbase + p + 2 * r;
         // scalar and the m/sin(theta) table share parity p with the rows; the d/dtheta table (seg 0 of a
         // vector plan) has the opposite parity but is addressed the same way: the fold is chosen by the FFT kernel
         float v = 0.f;
@@ -88,7 +90,7 @@ __global__ void pack_table_blocks_kernel(TableView tv, float *A, const long long
         int seg, r, par;
         if (ncomp == 2 && kb < nkb0) { seg = 0; r = kb * kBK + kk; par = 1 - p; }
         else { seg = ncomp == 2 ? 1 : 0; r = (kb - nkb0) * kBK + kk; par = p; }
-        const int l = m + par + 2 * r;
+        const int l = m + tv.mbase + par + 2 * r;
         float v = 0.f;
         if (l < lmax) v = tv.at(seg, m, l, k);
         if (negate_seg1 && seg == 1) v = -v;
@@ -98,12 +100,12 @@ __global__ void pack_table_blocks_kernel(TableView tv, float *A, const long long
 
 // Ct[((b0[g] - b0[2 m0]) + kb) * ncols + col][kk]
 __global__ void pack_coeffs_kernel(const float2 *__restrict__ c, float *__restrict__ Ct, const long long *b0, const int *gkb, const int *gkb0, int ncols,
-                                   int lmax, int mloc, int m0, int vector) {
-    const int gl = blockIdx.y;             // local group
-    const int g = gl + 2 * m0;
-    const int m = g >> 1, p = g & 1;
+                                   int lmax, int mloc, int m0, int mbase, int vector) {
+    const int gl = blockIdx.y;             // group inside the call's orders
+    const int m = m0 + (gl >> 1), p = gl & 1;
+    const int g = gl + 2 * (m0 - mbase);   // group inside the plan
     const int nkb = gkb[g], nkb0 = gkb0[g];
-    const long long base = (b0[g] - b0[2 * m0]) * ncols;
+    const long long base = (b0[g] - b0[2 * (m0 - mbase)]) * ncols;
     const long long total = (long long)nkb * ncols * kBK;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         const int kk = (int)(i % kBK);
@@ -157,7 +159,7 @@ __device__ __forceinline__ int tile_swz(int ll) { return 2 * ((ll >> 3) & 7) + (
 
 template <bool TO_SLABS>
 __global__ void __launch_bounds__(256) coeff_slab_transpose_kernel(float2 *__restrict__ c, float *__restrict__ S, const long long *__restrict__ slab0,
-                                                                   const int *__restrict__ gkb, int ncols, int lmax, int mloc, int m0, int nsb) {
+                                                                   const int *__restrict__ gkb, int ncols, int lmax, int mloc, int m0, int nsb, int mbase) {
     __shared__ float2 T[kTileRows][32];
     const int mb0 = blockIdx.x * 32, f = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -174,7 +176,7 @@ __global__ void __launch_bounds__(256) coeff_slab_transpose_kernel(float2 *__res
     }
     const int sb = blockIdx.y;
     // the first order of the tile has the longest groups: nothing to do beyond them (except the zeros next to the diagonal)
-    if (sb > 0 && sb >= gkb[2 * (m0 + mb0)]) return;
+    if (sb > 0 && sb >= gkb[2 * (m0 - mbase + mb0)]) return;
     const int lbase = m0 + mb0 + 64 * sb;  // degree of tile row 0
 
     if (TO_SLABS) {
@@ -208,9 +210,9 @@ __global__ void __launch_bounds__(256) coeff_slab_transpose_kernel(float2 *__res
             have[it] = false;
             srow[it] = S;
             if (mi < mloc) {
-                const int g = 2 * (m0 + mi) + p;
+                const int g = 2 * (m0 - mbase + mi) + p;  // group inside the plan
                 have[it] = sb < gkb[g];
-                srow[it] = S + ((size_t)(slab0[g] - slab0[2 * m0] + sb) * ncols + 2 * f + ri) * kBK + 4 * q;
+                srow[it] = S + ((size_t)(slab0[g] - slab0[2 * (m0 - mbase)] + sb) * ncols + 2 * f + ri) * kBK + 4 * q;
             }
         }
         if (!TO_SLABS) {
@@ -337,6 +339,7 @@ __global__ void fold_modes_vec_kernel(const float2 *__restrict__ Xc, float *__re
 // Y[blocked_row(2 mi + p, k')][2 f + ri] -> Xc (field, k, mloc) complex
 // (rows above krow0[2 (m0 + mi) + p] were not produced by the contraction: they count as zeros)
 __global__ void unfold_modes_kernel(const float *__restrict__ Y, float2 *__restrict__ Xc, int nfields, int nlat, int Kh, int ncp, int mloc, const int *__restrict__ krow0, int m0) {
+    // (m0 here = first order of the call relative to the plan's first order)
     const long long total = (long long)nfields * Kh * mloc;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         const int mi = (int)(i % mloc);
@@ -363,7 +366,7 @@ static int grid_x_for(long long total) {
 
 int launch_pack_table(Plan &pl, const float *table, cudaStream_t st) {
     const int ngroups = 2 * pl.mmax;
-    TableView tv{table, pl.mmax, pl.lmax, pl.nlat, 0};
+    TableView tv{table, pl.mmax, pl.lmax, pl.nlat, 0, pl.m_base};
     // dense layout handed over by the caller: (.., m, k, l) for the tables of the inverse modules
     tv.mkl = (pl.kind == SHTB200_ISHT || pl.kind == SHTB200_ISHT_ADJOINT || pl.kind == SHTB200_IVSHT || pl.kind == SHTB200_IVSHT_ADJOINT) ? 1 : 0;
     dim3 grid(64, ngroups);
@@ -381,7 +384,7 @@ int launch_polar_extent(const Plan &pl, const float *table, float rel, std::vect
     const int ngroups = 2 * pl.mmax;
     first_row->assign(ngroups, 0);
     if (pl.mmax == 0) return SHTB200_OK;
-    TableView tv{table, pl.mmax, pl.lmax, pl.nlat, 0};
+    TableView tv{table, pl.mmax, pl.lmax, pl.nlat, 0, pl.m_base};
     tv.mkl = (pl.kind == SHTB200_ISHT || pl.kind == SHTB200_ISHT_ADJOINT || pl.kind == SHTB200_IVSHT || pl.kind == SHTB200_IVSHT_ADJOINT) ? 1 : 0;
     int *d = nullptr;
     SHT_CUDA_CHECK(cudaMalloc(&d, sizeof(int) * ngroups));
@@ -399,13 +402,13 @@ int launch_pack_coeffs(const Plan &pl, const float2 *c, float *Ct, int nfields, 
     if (!pl.vector && nfields <= 65535) {
         const int nsb = ceil_div(pl.Lh, kBK);  // slabs of the longest group
         dim3 grid(ceil_div(mloc, 32), nsb, nfields);
-        coeff_slab_transpose_kernel<true><<<grid, 256, 0, st>>>(const_cast<float2 *>(c), Ct, pl.d_gb0, pl.d_gkb, ncols, pl.lmax, mloc, m0, nsb);
+        coeff_slab_transpose_kernel<true><<<grid, 256, 0, st>>>(const_cast<float2 *>(c), Ct, pl.d_gb0, pl.d_gkb, ncols, pl.lmax, mloc, m0, nsb, pl.m_base);
         SHT_CUDA_CHECK(cudaGetLastError());
         return SHTB200_OK;
     }
     const long long per_group = (long long)ceil_div(pl.Lh, kBK) * pl.ncomp * ncols * kBK;
     dim3 grid(grid_x_for(per_group), 2 * mloc);
-    pack_coeffs_kernel<<<grid, 256, 0, st>>>(c, Ct, pl.d_gb0, pl.d_gkb, pl.d_gkb0, ncols, pl.lmax, mloc, m0, pl.vector ? 1 : 0);
+    pack_coeffs_kernel<<<grid, 256, 0, st>>>(c, Ct, pl.d_gb0, pl.d_gkb, pl.d_gkb0, ncols, pl.lmax, mloc, m0, pl.m_base, pl.vector ? 1 : 0);
     SHT_CUDA_CHECK(cudaGetLastError());
     return SHTB200_OK;
 }
@@ -418,7 +421,7 @@ int launch_unpack_coeffs(const Plan &pl, const float *Z, float2 *c, int nfields,
     // extra tile rows for the degrees above the diagonal of the last order block: l < m0 + 32 (blocks - 1)
     const int nzero = ceil_div(std::min(m0 + 32 * (ceil_div(mloc, 32) - 1), pl.lmax), 64);
     dim3 grid(ceil_div(mloc, 32), nsb + nzero, nfields);
-    coeff_slab_transpose_kernel<false><<<grid, 256, 0, st>>>(c, const_cast<float *>(Z), pl.d_gb0, pl.d_gkb, 2 * nfields, pl.lmax, mloc, m0, nsb);
+    coeff_slab_transpose_kernel<false><<<grid, 256, 0, st>>>(c, const_cast<float *>(Z), pl.d_gb0, pl.d_gkb, 2 * nfields, pl.lmax, mloc, m0, nsb, pl.m_base);
     SHT_CUDA_CHECK(cudaGetLastError());
     return SHTB200_OK;
 }
@@ -453,7 +456,7 @@ int launch_unfold_modes(const Plan &pl, const float *Y, float2 *Xc, int nfields,
     const int nf = pl.vector ? 2 * nfields : nfields;
     const long long total = (long long)nf * pl.Kh * mloc;
     if (total == 0) return SHTB200_OK;
-    unfold_modes_kernel<<<grid_x_for(total), 256, 0, st>>>(Y, Xc, nf, pl.nlat, pl.Kh, (int)col_pitch(2 * nf), mloc, pl.d_krow0, m0);
+    unfold_modes_kernel<<<grid_x_for(total), 256, 0, st>>>(Y, Xc, nf, pl.nlat, pl.Kh, (int)col_pitch(2 * nf), mloc, pl.d_krow0, m0 - pl.m_base);
     SHT_CUDA_CHECK(cudaGetLastError());
     return SHTB200_OK;
 }

@@ -26,7 +26,6 @@ from .primitives import (
     distributed_transpose_azimuth,
     distributed_transpose_polar,
     flatten_and_pad_leading_dims,
-    split_tensor_along_dim,
     unpad_and_unflatten_leading_dims,
 )
 from .utils import azimuth_group_rank, azimuth_group_size, polar_group_rank, polar_group_size
@@ -143,35 +142,44 @@ class _DistributedBase(nn.Module):
     def extra_repr(self):
         return f"nlat={self.nlat}, nlon={self.nlon},\n lmax={self.lmax}, mmax={self.mmax},\n grid={self.grid}, csphase={self.csphase}"
 
-    def _full_table(self):
+    def _local_table(self):
+        """float64 table of this rank's orders [_m0, _m0 + mmax_local) in the reference's layout (built once, in the constructor)."""
         raise NotImplementedError
 
     def _plan(self, device, adjoint):
+        """Plan over this rank's window of orders, packed from the module's own buffer."""
         key = (device.index, adjoint, self.engine)
         pl = self._plans.get(key)
         if pl is None:
             with torch.cuda.device(device):
-                t32 = self._full_table().to(device=device, dtype=torch.float32).contiguous()
-                pl = _lib.Plan(self._adj_kind if adjoint else self._kind, self.nlat, self.nlon, self.lmax, self.mmax, t32, engine=self.engine)
+                t32 = getattr(self, self._table_name).detach().to(device=device, dtype=torch.float32).contiguous()
+                pl = _lib.Plan(self._adj_kind if adjoint else self._kind, self.nlat, self.nlon, self.lmax, self.mmax, t32, engine=self.engine,
+                               orders=(self._m0, self.mmax_local))
                 del t32
             self._plans[key] = pl
         return pl
+
+    def _apply(self, fn, *args, **kwargs):
+        # buffers may move or change dtype: plans built from the old table are dropped
+        out = super()._apply(fn, *args, **kwargs)
+        for pl in self._plans.values():
+            pl.close()
+        self._plans.clear()
+        return out
 
 
 class DistributedRealSHT(_DistributedBase):
     """Forward SHT on a local tile: ``(..., nlat_local, nlon_local)`` float32 -> ``(..., lmax_local, mmax_local)`` complex64."""
 
-    _kind, _adj_kind = _lib.SHT, _lib.SHT_ADJOINT
+    _kind, _adj_kind, _table_name = _lib.SHT, _lib.SHT_ADJOINT, "weights"
 
     def __init__(self, nlat, nlon, lmax=None, mmax=None, grid="equiangular", norm="ortho", csphase=True):
         super().__init__(nlat, nlon, lmax, mmax, grid, norm, csphase)
-        weights = self._full_table()
-        # the module keeps this rank's orders only, like the reference (distributed_sht.py:164)
-        weights = split_tensor_along_dim(weights, dim=0, num_chunks=self.comm_size_azimuth)[self.comm_rank_azimuth].contiguous()
-        self.register_buffer("weights", weights, persistent=False)
+        # the module keeps this rank's orders only, like the reference (distributed_sht.py:164); only they are computed
+        self.register_buffer("weights", self._local_table(), persistent=False)
 
-    def _full_table(self):
-        pct = _precompute_legpoly(self.mmax, self.lmax, self._tq, norm=self.norm, csphase=self.csphase)
+    def _local_table(self):
+        pct = _precompute_legpoly(self.mmax, self.lmax, self._tq, norm=self.norm, csphase=self.csphase, m_first=self._m0, m_count=self.mmax_local)
         return (pct * self._quad_w.to(pct.device)[None, None, :]).contiguous()
 
     def forward(self, x: torch.Tensor):
@@ -202,16 +210,14 @@ class DistributedRealSHT(_DistributedBase):
 class DistributedInverseRealSHT(_DistributedBase):
     """Inverse SHT on a local tile: ``(..., lmax_local, mmax_local)`` complex64 -> ``(..., nlat_local, nlon_local)`` float32."""
 
-    _kind, _adj_kind = _lib.ISHT, _lib.ISHT_ADJOINT
+    _kind, _adj_kind, _table_name = _lib.ISHT, _lib.ISHT_ADJOINT, "pct"
 
     def __init__(self, nlat, nlon, lmax=None, mmax=None, grid="equiangular", norm="ortho", csphase=True):
         super().__init__(nlat, nlon, lmax, mmax, grid, norm, csphase)
-        pct = self._full_table()
-        pct = split_tensor_along_dim(pct, dim=0, num_chunks=self.comm_size_azimuth)[self.comm_rank_azimuth].contiguous()
-        self.register_buffer("pct", pct, persistent=False)
+        self.register_buffer("pct", self._local_table(), persistent=False)  # this rank's orders (distributed_sht.py:333)
 
-    def _full_table(self):
-        pct = _precompute_legpoly(self.mmax, self.lmax, self._tq, norm=self.norm, inverse=True, csphase=self.csphase)
+    def _local_table(self):
+        pct = _precompute_legpoly(self.mmax, self.lmax, self._tq, norm=self.norm, inverse=True, csphase=self.csphase, m_first=self._m0, m_count=self.mmax_local)
         return pct.permute(0, 2, 1).contiguous()
 
     def forward(self, x: torch.Tensor):
@@ -239,17 +245,14 @@ class DistributedRealVectorSHT(_DistributedBase):
     """Forward vector SHT on a local tile: ``(..., 2, nlat_local, nlon_local)`` float32 ->
     ``(..., 2, lmax_local, mmax_local)`` complex64 (spheroidal, toroidal)."""
 
-    _kind, _adj_kind = _lib.VSHT, _lib.VSHT_ADJOINT
+    _kind, _adj_kind, _table_name = _lib.VSHT, _lib.VSHT_ADJOINT, "weights"
 
     def __init__(self, nlat, nlon, lmax=None, mmax=None, grid="equiangular", norm="ortho", csphase=True):
         super().__init__(nlat, nlon, lmax, mmax, grid, norm, csphase)
-        weights = self._full_table()
-        # this rank's orders only (distributed_sht.py:490)
-        weights = split_tensor_along_dim(weights, dim=1, num_chunks=self.comm_size_azimuth)[self.comm_rank_azimuth].contiguous()
-        self.register_buffer("weights", weights, persistent=False)
+        self.register_buffer("weights", self._local_table(), persistent=False)  # this rank's orders only (distributed_sht.py:490)
 
-    def _full_table(self):
-        dpct = _precompute_dlegpoly(self.mmax, self.lmax, self._tq, norm=self.norm, csphase=self.csphase)
+    def _local_table(self):
+        dpct = _precompute_dlegpoly(self.mmax, self.lmax, self._tq, norm=self.norm, csphase=self.csphase, m_first=self._m0, m_count=self.mmax_local)
         # 1 / (l (l + 1)) in float32, like the serial module (torch_harmonics/sht.py:439-441)
         l = torch.arange(0, self.lmax)
         norm_factor = 1.0 / l / (l + 1)
@@ -284,16 +287,14 @@ class DistributedInverseRealVectorSHT(_DistributedBase):
     """Inverse vector SHT on a local tile: ``(..., 2, lmax_local, mmax_local)`` complex64 ->
     ``(..., 2, nlat_local, nlon_local)`` float32."""
 
-    _kind, _adj_kind = _lib.IVSHT, _lib.IVSHT_ADJOINT
+    _kind, _adj_kind, _table_name = _lib.IVSHT, _lib.IVSHT_ADJOINT, "dpct"
 
     def __init__(self, nlat, nlon, lmax=None, mmax=None, grid="equiangular", norm="ortho", csphase=True):
         super().__init__(nlat, nlon, lmax, mmax, grid, norm, csphase)
-        dpct = self._full_table()
-        dpct = split_tensor_along_dim(dpct, dim=1, num_chunks=self.comm_size_azimuth)[self.comm_rank_azimuth].contiguous()
-        self.register_buffer("dpct", dpct, persistent=False)
+        self.register_buffer("dpct", self._local_table(), persistent=False)  # this rank's orders only (distributed_sht.py:645)
 
-    def _full_table(self):
-        dpct = _precompute_dlegpoly(self.mmax, self.lmax, self._tq, norm=self.norm, inverse=True, csphase=self.csphase)
+    def _local_table(self):
+        dpct = _precompute_dlegpoly(self.mmax, self.lmax, self._tq, norm=self.norm, inverse=True, csphase=self.csphase, m_first=self._m0, m_count=self.mmax_local)
         return dpct.permute(0, 1, 3, 2).contiguous()
 
     def forward(self, x: torch.Tensor):

@@ -94,7 +94,11 @@ GemmParams gemm_params(const Plan &pl, int nfields, int m0, int mloc, const floa
         gp.b_dx = kBK;
         gp.b_kext = pl.Ka;
         gp.b_unit0 = 2 * ml;
+#ifdef SHTB200_DIRECT_EPI  // build-time switch for A/B measurements: scalar analysis writes (field, l, m) from the contraction's epilogue
+        gp.mode = EPI_COEFFS;
+#else
         gp.mode = pl.vector ? EPI_COEFFS : EPI_SLABS;
+#endif
         gp.slab0 = pl.d_gb0;
         gp.slab_unit0 = pl.group_b0[2 * ml];
     } else {
@@ -155,17 +159,21 @@ int execute_full(Plan &pl, const void *in, void *out, int nfields, void *ws, siz
     if (pl.analysis) {
         float *X = reinterpret_cast<float *>(ws);
         float *Z = reinterpret_cast<float *>(reinterpret_cast<char *>(ws) + align256(w.op_bytes));
-        if (pl.vector) {
-            if ((rc = launch_zero_upper(pl, reinterpret_cast<float2 *>(out), nfields, 0, pl.mmax, st))) return rc;
-            pl.last_launches += 1;
-        }
+#ifdef SHTB200_DIRECT_EPI
+        const bool direct = true;
+#else
+        const bool direct = pl.vector;
+#endif
         if ((rc = launch_fft_analysis(pl, reinterpret_cast<const float *>(in), X, nfields, st))) return rc;
         mark(pl, st);
         pl.last_launches += 1;
-        GemmParams gp = gemm_params(pl, nfields, 0, pl.mmax, X, pl.vector ? reinterpret_cast<float *>(out) : Z);
+        GemmParams gp = gemm_params(pl, nfields, 0, pl.mmax, X, direct ? reinterpret_cast<float *>(out) : Z);
         if ((rc = run_gemm(pl, gp, st))) return rc;
         mark(pl, st);
-        if (!pl.vector) {
+        if (direct) {  // exact zeros above the diagonal (the epilogue writes l >= m only)
+            if ((rc = launch_zero_upper(pl, reinterpret_cast<float2 *>(out), nfields, 0, pl.mmax, st))) return rc;
+            pl.last_launches += 1;
+        } else {
             if ((rc = launch_unpack_coeffs(pl, Z, reinterpret_cast<float2 *>(out), nfields, 0, pl.mmax, st))) return rc;
             pl.last_launches += 1;
         }

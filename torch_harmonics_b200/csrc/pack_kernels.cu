@@ -273,26 +273,40 @@ __global__ void zero_upper_kernel(float2 *c, long long nfl, int lmax, int mloc, 
 }
 
 // Xc (field, k, mloc) complex -> X[blocked_row(2 mi + p, k')][2 f + ri] (row pitch ncp); rows k' >= Kh of the last
-// 32-row block are written as zeros
-__global__ void fold_modes_kernel(const float2 *__restrict__ Xc, float *__restrict__ X, int nfields, int nlat, int Kh, int ncp, int mloc) {
-    const int Kr = (Kh + kBK - 1) / kBK * kBK;
-    const long long total = (long long)mloc * Kr * nfields;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-        const int f = (int)(i % nfields);
-        const long long t = i / nfields;
-        const int k = (int)(t % Kr);
-        const int mi = (int)(t / Kr);
-        float2 e = make_float2(0.f, 0.f), o = e;
-        if (k < Kh) {
-            const int ks = nlat - 1 - k;
-            float2 a = Xc[((size_t)f * nlat + k) * mloc + mi];
-            e = a;
-            if (ks != k) {
-                float2 b = Xc[((size_t)f * nlat + ks) * mloc + mi];
-                e = make_float2(a.x + b.x, a.y + b.y);
-                o = make_float2(a.x - b.x, a.y - b.y);
+// 32-row block are written as zeros.  The input is contiguous along the orders, the output along the fields: a CTA moves
+// a 32 (orders) x 32 (fields) tile of one folded latitude through shared memory, so that both sides see 256-byte runs.
+__global__ void __launch_bounds__(256) fold_modes_kernel(const float2 *__restrict__ Xc, float *__restrict__ X, int nfields, int nlat, int Kh, int ncp, int mloc) {
+    __shared__ float2 E[32][33], O[32][33];
+    const int mi0 = blockIdx.x * 32, k = blockIdx.y, f0 = blockIdx.z * 32;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    if (k < Kh) {
+        const int ks = nlat - 1 - k;
+        const int mi = mi0 + tx;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int f = f0 + ty + 8 * i;
+            float2 e = make_float2(0.f, 0.f), o = e;
+            if (f < nfields && mi < mloc) {
+                const float2 a = __ldg(Xc + ((size_t)f * nlat + k) * mloc + mi);
+                e = a;
+                if (ks != k) {
+                    const float2 b = __ldg(Xc + ((size_t)f * nlat + ks) * mloc + mi);
+                    e = make_float2(a.x + b.x, a.y + b.y);
+                    o = make_float2(a.x - b.x, a.y - b.y);
+                }
             }
+            E[ty + 8 * i][tx] = e;
+            O[ty + 8 * i][tx] = o;
         }
+    }
+    __syncthreads();
+    const int f = f0 + tx;
+    if (f >= nfields) return;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int mi = mi0 + ty + 8 * i;
+        if (mi >= mloc) continue;
+        const float2 e = k < Kh ? E[tx][ty + 8 * i] : make_float2(0.f, 0.f), o = k < Kh ? O[tx][ty + 8 * i] : make_float2(0.f, 0.f);
         *reinterpret_cast<float2 *>(X + (size_t)blocked_row(2 * mi, k, 2 * mloc) * ncp + 2 * f) = e;
         *reinterpret_cast<float2 *>(X + (size_t)blocked_row(2 * mi + 1, k, 2 * mloc) * ncp + 2 * f) = o;
     }
@@ -336,20 +350,37 @@ __global__ void fold_modes_vec_kernel(const float2 *__restrict__ Xc, float *__re
     }
 }
 
-// Y[blocked_row(2 mi + p, k')][2 f + ri] -> Xc (field, k, mloc) complex
-// (rows above krow0[2 (m0 + mi) + p] were not produced by the contraction: they count as zeros)
-__global__ void unfold_modes_kernel(const float *__restrict__ Y, float2 *__restrict__ Xc, int nfields, int nlat, int Kh, int ncp, int mloc, const int *__restrict__ krow0, int m0) {
-    // (m0 here = first order of the call relative to the plan's first order)
-    const long long total = (long long)nfields * Kh * mloc;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-        const int mi = (int)(i % mloc);
-        const long long t = i / mloc;
-        const int k = (int)(t % Kh);
-        const int f = (int)(t / Kh);
-        float2 e = make_float2(0.f, 0.f), o = e;
-        if (k >= krow0[2 * (m0 + mi)]) e = *reinterpret_cast<const float2 *>(Y + (size_t)blocked_row(2 * mi, k, 2 * mloc) * ncp + 2 * f);
-        if (k >= krow0[2 * (m0 + mi) + 1]) o = *reinterpret_cast<const float2 *>(Y + (size_t)blocked_row(2 * mi + 1, k, 2 * mloc) * ncp + 2 * f);
-        const int ks = nlat - 1 - k;
+// Y[blocked_row(2 mi + p, k')][2 f + ri] -> Xc (field, k, mloc) complex, the same tiling the other way round
+// (rows above krow0[2 (m0 + mi) + p] were not produced by the contraction: they count as zeros; m0 here = first order of
+// the call relative to the plan's first order)
+__global__ void __launch_bounds__(256) unfold_modes_kernel(const float *__restrict__ Y, float2 *__restrict__ Xc, int nfields, int nlat, int Kh, int ncp, int mloc,
+                                                           const int *__restrict__ krow0, int m0) {
+    __shared__ float2 E[32][33], O[32][33];
+    const int mi0 = blockIdx.x * 32, k = blockIdx.y, f0 = blockIdx.z * 32;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    {
+        const int f = f0 + tx;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int mi = mi0 + ty + 8 * i;
+            float2 e = make_float2(0.f, 0.f), o = e;
+            if (f < nfields && mi < mloc) {
+                if (k >= krow0[2 * (m0 + mi)]) e = __ldg(reinterpret_cast<const float2 *>(Y + (size_t)blocked_row(2 * mi, k, 2 * mloc) * ncp + 2 * f));
+                if (k >= krow0[2 * (m0 + mi) + 1]) o = __ldg(reinterpret_cast<const float2 *>(Y + (size_t)blocked_row(2 * mi + 1, k, 2 * mloc) * ncp + 2 * f));
+            }
+            E[ty + 8 * i][tx] = e;
+            O[ty + 8 * i][tx] = o;
+        }
+    }
+    __syncthreads();
+    const int mi = mi0 + tx;
+    if (mi >= mloc) return;
+    const int ks = nlat - 1 - k;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int f = f0 + ty + 8 * i;
+        if (f >= nfields) continue;
+        const float2 e = E[tx][ty + 8 * i], o = O[tx][ty + 8 * i];
         Xc[((size_t)f * nlat + k) * mloc + mi] = make_float2(e.x + o.x, e.y + o.y);
         if (ks != k) Xc[((size_t)f * nlat + ks) * mloc + mi] = make_float2(e.x - o.x, e.y - o.y);
     }
@@ -444,9 +475,10 @@ int launch_fold_modes(const Plan &pl, const float2 *Xc, float *X, int nfields, i
         SHT_CUDA_CHECK(cudaGetLastError());
         return SHTB200_OK;
     }
-    const long long total = (long long)mloc * nfields * round_up(pl.Kh, kBK);
-    if (total == 0) return SHTB200_OK;
-    fold_modes_kernel<<<grid_x_for(total), 256, 0, st>>>(Xc, X, nfields, pl.nlat, pl.Kh, (int)col_pitch(2 * nfields), mloc);
+    if (mloc == 0 || nfields == 0) return SHTB200_OK;
+    if (ceil_div(nfields, 32) > 65535) return fail(SHTB200_EINVAL, "too many fields in one call");
+    dim3 grid(ceil_div(mloc, 32), (unsigned)round_up(pl.Kh, kBK), ceil_div(nfields, 32));
+    fold_modes_kernel<<<grid, 256, 0, st>>>(Xc, X, nfields, pl.nlat, pl.Kh, (int)col_pitch(2 * nfields), mloc);
     SHT_CUDA_CHECK(cudaGetLastError());
     return SHTB200_OK;
 }
@@ -454,9 +486,10 @@ int launch_fold_modes(const Plan &pl, const float2 *Xc, float *X, int nfields, i
 int launch_unfold_modes(const Plan &pl, const float *Y, float2 *Xc, int nfields, int m0, int mloc, cudaStream_t st) {
     // a vector pair is two complex fields side by side (theta, phi): same kernel on 2 x nfields fields
     const int nf = pl.vector ? 2 * nfields : nfields;
-    const long long total = (long long)nf * pl.Kh * mloc;
-    if (total == 0) return SHTB200_OK;
-    unfold_modes_kernel<<<grid_x_for(total), 256, 0, st>>>(Y, Xc, nf, pl.nlat, pl.Kh, (int)col_pitch(2 * nf), mloc, pl.d_krow0, m0 - pl.m_base);
+    if (nf == 0 || mloc == 0) return SHTB200_OK;
+    if (ceil_div(nf, 32) > 65535) return fail(SHTB200_EINVAL, "too many fields in one call");
+    dim3 grid(ceil_div(mloc, 32), pl.Kh, ceil_div(nf, 32));
+    unfold_modes_kernel<<<grid, 256, 0, st>>>(Y, Xc, nf, pl.nlat, pl.Kh, (int)col_pitch(2 * nf), mloc, pl.d_krow0, m0 - pl.m_base);
     SHT_CUDA_CHECK(cudaGetLastError());
     return SHTB200_OK;
 }

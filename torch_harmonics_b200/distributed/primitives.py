@@ -5,9 +5,10 @@ axis for a shard of another one: the tensor arrives sharded along ``dims[1]`` (e
 all of ``dims[0]``) and leaves sharded along ``dims[0]`` with ``dims[1]`` complete.  Chunks are balanced and may be
 uneven (``compute_split_shapes``).
 
-The exchange itself is ONE ``all_to_all_single`` over NCCL on a send buffer packed peer-major by a single
-``movedim(...).contiguous()`` (the reference copies every chunk separately and uses the list form).  Backends
-without all-to-all (gloo, used by the CPU tests) go through point-to-point sends.
+The exchange itself is ONE ``all_to_all_single`` over NCCL.  Pieces travel in the tensor's own axis order, so that
+a transpose costs at most one copy on each side and none on the side whose axis leads (the reference copies every
+chunk separately, uses the list form and concatenates).  Backends without all-to-all (gloo, used by the CPU tests)
+go through point-to-point sends.
 """
 
 from typing import List
@@ -126,7 +127,12 @@ def _exchange(send: torch.Tensor, send_counts, recv_counts, group):
 
 
 def _transpose(x: torch.Tensor, dim0: int, dim1: int, dim1_split_sizes, group):
-    """Scatter ``dim0``, gather ``dim1`` across ``group``; returns the redistributed contiguous tensor."""
+    """Scatter ``dim0``, gather ``dim1`` across ``group``; returns the redistributed contiguous tensor.
+
+    On the wire every piece keeps the tensor's own axis order: peer j receives this rank's slice ``dim0 in chunk j`` and
+    this rank receives from peer j the slice that carries ``dim1`` chunk j.  The send buffer is therefore one gather of the
+    chunks (no copy at all when ``dim0`` is the leading axis: the chunks already lie one after the other) and the result is
+    one concatenation along ``dim1`` (no copy when ``dim1`` is the leading axis: the received pieces already are the result)."""
     size = dist.get_world_size(group)
     rank = dist.get_rank(group)
     if size == 1:
@@ -138,28 +144,31 @@ def _transpose(x: torch.Tensor, dim0: int, dim1: int, dim1_split_sizes, group):
         _verify("_transpose: error, dim1_split_sizes", x.shape[dim1], list(dim1_split_sizes), group)
     is_complex = x.is_complex()
     xr = torch.view_as_real(x) if is_complex else x  # trailing (re, im) axis does not move
-    # peer-major send buffer: dim0 first
-    send = xr.movedim(dim0, 0).contiguous()
+    xr = xr.contiguous()
     d0 = compute_split_shapes(x.shape[dim0], size)
-    per_row = send[0].numel() if send.shape[0] > 0 else 0
-    send_counts = [c * per_row for c in d0]
+    per0 = xr.numel() // x.shape[dim0] if x.shape[dim0] else 0   # elements per index of dim0
+    send_counts = [c * per0 for c in d0]
+    if dim0 == 0:
+        send = xr.reshape(-1)
+    else:
+        send = torch.cat([p.reshape(-1) for p in torch.split(xr, d0, dim=dim0)])
     # what arrives from peer j: my dim0 chunk, with dim1 of length dim1_split_sizes[j]
-    rest = per_row // x.shape[dim1]
+    rest = per0 // x.shape[dim1] if x.shape[dim1] else 0         # elements per (dim0 index, dim1 index)
     recv_counts = [d0[rank] * rest * s for s in dim1_split_sizes]
-    recv = _exchange(send.reshape(-1), send_counts, recv_counts, group)
-    # unpack: piece j has the send layout (dim0 first) with dim1 -> split j
-    shape_moved = list(send.shape)
-    d1_moved = dim1 + 1 if dim1 < dim0 else dim1  # position of dim1 after dim0 moved to the front
-    pieces = []
-    off = 0
-    for j, s in enumerate(dim1_split_sizes):
-        shp = list(shape_moved)
-        shp[0] = d0[rank]
-        shp[d1_moved] = s
-        n = recv_counts[j]
-        pieces.append(recv[off:off + n].view(shp))
-        off += n
-    out = torch.cat(pieces, dim=d1_moved).movedim(0, dim0).contiguous()
+    recv = _exchange(send, send_counts, recv_counts, group)
+    shape = list(xr.shape)
+    shape[dim0] = d0[rank]
+    if dim1 == 0:
+        shape[dim1] = sum(dim1_split_sizes)
+        out = recv.view(shape)
+    else:
+        pieces, off = [], 0
+        for j, s_ in enumerate(dim1_split_sizes):
+            shp = list(shape)
+            shp[dim1] = s_
+            pieces.append(recv[off:off + recv_counts[j]].view(shp))
+            off += recv_counts[j]
+        out = torch.cat(pieces, dim=dim1)
     return torch.view_as_complex(out) if is_complex else out
 
 

@@ -137,8 +137,8 @@ int clear_empty_groups(const Plan &pl, float *Y, int ncols, int m0, int mloc, cu
     for (int g = 2 * m0; g < 2 * (m0 + mloc); ++g) {
         if (pl.group_kblocks[g] == 0) {
             const size_t ncp = (size_t)col_pitch(ncols);
-            for (int k0 = 0; k0 < pl.Kh; k0 += kBK)  // the group's rows come in 32-row blocks
-                SHT_CUDA_CHECK(cudaMemsetAsync(Y + (size_t)blocked_row(g - 2 * m0, k0, 2 * mloc) * ncp, 0, sizeof(float) * kBK * ncp, st));
+            // one row per latitude, a whole latitude (2 mloc rows) apart
+            SHT_CUDA_CHECK(cudaMemset2DAsync(Y + (size_t)y_row(g - 2 * m0, 0, 2 * mloc) * ncp, sizeof(float) * 2 * mloc * ncp, 0, sizeof(float) * ncp, (size_t)pl.Kh, st));
         }
     }
     return SHTB200_OK;

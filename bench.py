@@ -17,6 +17,8 @@ independent replicas, no data-path collective).  Prints ONE JSON line (rank 0).
                  the kernels this library replaces (1 GPU only)
   configs        fields/s and roofline fractions of the other single-GPU workloads: 256x512 legendre-gauss with 1024
                  fields, the vector transforms with 104 (u, v) pairs, 2048 fields on one GPU (1 GPU only)
+  spectral_conv  SpectralConvS2 at the benchmark grid: the fused library call against the composed layer (1 GPU only)
+  setup          seconds to build the modules' tables on the GPU and to pack them into plans
   spatial        N > 1 only: DistributedRealSHT / DistributedInverseRealSHT on a polar x azimuth process grid
                  (1x2, 2x2, 2x4) at 721x1440: per-rank parity against the serial transform and the reference's rows,
                  forward / inverse / round-trip fields/s, all-to-all bytes and GB/s
@@ -285,6 +287,18 @@ def config_record(dev, name, engine, barrier):
     t_step, nb = timed_blocks(step, k, barrier, 0.25)
     t_fwd, _ = timed_blocks(fwd_fn, k, barrier, 0.15)
     t_inv, _ = timed_blocks(inv_fn, k, barrier, 0.15)
+    p_f.set_profiling(True)
+    p_i.set_profiling(True)
+    kt = {}
+    for _ in range(3):
+        fwd_fn()
+        for n, t in zip(["fft_analysis", "legendre_analysis", "unpack_coeffs"], p_f.last_kernel_times()):
+            kt[n] = kt.get(n, 0.0) + t / 3
+        inv_fn()
+        for n, t in zip(["pack_coeffs", "legendre_synthesis", "fft_synthesis"], p_i.last_kernel_times()):
+            kt[n] = kt.get(n, 0.0) + t / 3
+    p_f.set_profiling(False)
+    p_i.set_profiling(False)
     t_mem, t_tc, src = transform_bound(nf, nlat, nlon, lmax, mmax, vector)
     bound = max(t_mem, t_tc)
     rec = {
@@ -295,9 +309,42 @@ def config_record(dev, name, engine, barrier):
             "t_mem_ms_per_direction": 1e3 * t_mem, "t_tc_ms_per_direction": 1e3 * t_tc, "bound": "hbm" if t_mem >= t_tc else "tensor",
             "fwd_frac": bound / (t_fwd / k), "inv_frac": bound / (t_inv / k), "roundtrip_frac": 2 * bound / (t_step / k), "peak_source": src,
         },
-        "launches_per_step": p_f.last_launch_count + p_i.last_launch_count,
+        "kernel_ms": kt, "launches_per_step": p_f.last_launch_count + p_i.last_launch_count,
     }
     del p_f, p_i, fwd, inv, c, c2, x, x2, ws
+    torch.cuda.empty_cache()
+    return rec
+
+
+def spectral_conv_record(dev, engine, barrier):
+    """SpectralConvS2 at the benchmark grid (73 -> 73 channels, default truncation lmax = 361): the single fused library call
+    against the same layer composed of the transform modules and a torch einsum, as the reference composes it."""
+    import torch_harmonics_b200 as th
+
+    C = 73
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        with torch.device(dev):
+            layer = th.SpectralConvS2((NLAT, NLON), (NLAT, NLON), C, C)
+    layer.sht.engine = layer.isht.engine = engine
+    x = torch.randn(1, C, NLAT, NLON, device=dev, generator=torch.Generator(device=dev).manual_seed(5))
+
+    def composed():
+        c = layer.sht(x).reshape(1, 1, C, layer.lmax, layer.mmax)
+        return layer.isht(torch.einsum("bgixy,giox->bgoxy", c, layer.weight).reshape(1, C, layer.lmax, layer.mmax).contiguous())
+
+    with torch.no_grad():
+        y, yc = layer(x), composed()
+        diff = float((y - yc).abs().max() / yc.abs().max())
+        t_f, _ = timed_blocks(lambda: layer(x), 10, barrier, 0.2)
+        t_c, _ = timed_blocks(composed, 10, barrier, 0.2)
+    rec = {
+        "workload": f"SpectralConvS2 {NLAT}x{NLON} -> {NLAT}x{NLON}, {C} -> {C} channels, 1 group, lmax = mmax = {layer.lmax}, batch 1, no bias",
+        "fused_ms": 1e3 * t_f / 10, "composed_ms": 1e3 * t_c / 10, "fused_fields_per_s": C * 10 / t_f, "composed_fields_per_s": C * 10 / t_c,
+        "fused_vs_composed_diff": diff, "fused_launches": 6,
+        "note": "fused = one library call, coefficients stay in the degree-slab layout (no (.., l, m) tensor, no transposes); composed = RealSHT, torch.einsum, InverseRealSHT",
+    }
+    del layer, x, y, yc
     torch.cuda.empty_cache()
     return rec
 
@@ -511,9 +558,17 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=240))
 
     nf = args.nfields
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
     sht, isht = build_scalar(dev, NLAT, NLON, LMAX, MMAX, "equiangular", args.engine)
+    torch.cuda.synchronize()
+    t1 = time.perf_counter()
     p_f = sht._op.plan(dev, False)
     p_i = isht._op.plan(dev, False)
+    torch.cuda.synchronize()
+    t2 = time.perf_counter()
+    # construction: float64 tables of both modules built on the device (torch ops), then packed into the two plans
+    setup = {"tables_s": t1 - t0, "plans_s": t2 - t1, "note": "RealSHT + InverseRealSHT constructors on the GPU, then table packing and polar-extent scan of both plans"}
 
     coeffs = synthetic_coeffs(nf, seed=2 + rank).to(dev)
     stream = torch.cuda.current_stream().cuda_stream
@@ -644,6 +699,11 @@ def run_ours(args):
                 cfgs[name] = {"error": repr(e)[:300]}
                 torch.cuda.empty_cache()
         extras["configs"] = cfgs
+        try:
+            extras["spectral_conv"] = spectral_conv_record(dev, args.engine, barrier)
+        except Exception as e:
+            extras["spectral_conv"] = {"error": repr(e)[:300]}
+            torch.cuda.empty_cache()
     if world > 1 and not args.no_spatial:
         try:
             extras["spatial"] = spatial_record(dev, rank, world, args.engine, args.spatial_fields, p_f, p_i)
@@ -704,6 +764,7 @@ def run_ours(args):
             },
             "module_api": {"value": nf * world * k / t_mod, "unit": "fields/s", "ms_per_step": 1e3 * t_mod / k,
                            "note": "RealSHT.forward then InverseRealSHT.forward on device tensors: output and workspace allocation and operator dispatch included"},
+            "setup": setup,
             "gpu_launches": 6 * k * nblocks,
             "clocks": clocks,
         }

@@ -226,8 +226,27 @@ def _dist_worker(rank, world, port, gh, gw):
             if max(e1, e2, e3, e4) > 3e-6 or max(e0, e5) > TOL:
                 ok = False
                 msgs.append(f"rank {rank} {'vector ' if vector else ''}{nlat}x{nlon} lmax={lmax} {lead} {grid}: oracle {e0:.2e} {e5:.2e} serial {e1:.2e} {e2:.2e} {e3:.2e} {e4:.2e}")
+    # inference path: without a gradient to record, large batches are cut into chunks whose all-to-alls and kernels overlap on
+    # streams of their own; the result must be the one of the plain path, bit for bit (forced here by dropping the size limit)
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        dsht, disht = thd.DistributedRealSHT(33, 64, lmax=17).cuda(), thd.DistributedInverseRealSHT(33, 64, lmax=17).cuda()
+    x = torch.randn(37, 3, 33, 64, device="cuda", generator=torch.Generator(device="cuda").manual_seed(5))
+    xl = tile(x)
+    with torch.no_grad():
+        dsht.pipeline_chunks = disht.pipeline_chunks = 0
+        c_plain = dsht(xl)
+        y_plain = disht(c_plain)
+        dsht.pipeline_chunks, dsht.pipeline_min_bytes = 4, 0
+        disht.pipeline_chunks, disht.pipeline_min_bytes = 3, 0
+        c_pipe = dsht(xl)
+        y_pipe = disht(c_pipe)
+    torch.cuda.synchronize()
+    if not (torch.equal(c_plain, c_pipe) and torch.equal(y_plain, y_pipe)):
+        ok = False
+        msgs.append(f"rank {rank}: pipelined inference path differs from the plain path")
     if rank == 0:
-        print(f"distributed parity {gh}x{gw}: {len(SCALAR_CASES)} scalar + {len(VECTOR_CASES)} vector cases, ok={ok}", flush=True)
+        print(f"distributed parity {gh}x{gw}: {len(SCALAR_CASES)} scalar + {len(VECTOR_CASES)} vector cases + pipelined path, ok={ok}", flush=True)
     _finish(ok, msgs)
 
 

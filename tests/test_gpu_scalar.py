@@ -30,6 +30,10 @@ SHAPES = [
     (8, 16, 12, 9, "legendre-gauss", 2),
     (91, 180, 90, 90, "equiangular", 9),
     (2, 4, 2, 2, "legendre-gauss", 1),
+    # longitudes with a register-resident two-pass FFT (1440 = 40 x 36, 720 = 36 x 20, 512 = 32 x 16), ragged field counts
+    (45, 1440, 40, 40, "legendre-gauss", 11),
+    (91, 720, 90, 90, "equiangular", 10),
+    (40, 512, 40, 40, "legendre-gauss", 9),
 ]
 
 

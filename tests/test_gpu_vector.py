@@ -77,3 +77,25 @@ def test_vector_module_shapes_and_errors():
     assert ivs(c).shape == x.shape
     with pytest.raises(RuntimeError, match="vector field"):
         vs(torch.zeros(3, 32, 64, device="cuda"))
+
+
+@pytest.mark.parametrize("engine", ["simt", "tcgen05"])
+@pytest.mark.parametrize("nlat,nlon,lmax,grid,npairs", [(24, 512, 20, "legendre-gauss", 5), (25, 720, 22, "equiangular", 3), (23, 1440, 16, "legendre-gauss", 6)])
+def test_vector_two_pass_longitudes_match_oracle(nlat, nlon, lmax, grid, npairs, engine):
+    """Vector transforms on longitudes that take the register-resident two-pass FFT kernels (their emit carries the
+    component sign pattern), with pair counts that leave the last block of eight component fields ragged."""
+    import torch
+
+    from torch_harmonics_b200 import _lib
+
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        vw, L, M = orc.vsht_weights(nlat, nlon, lmax=lmax, grid=grid)
+        vp, _, _ = orc.ivsht_dpct(nlat, nlon, lmax=L, mmax=M, grid=grid)
+    rng = np.random.default_rng(nlon)
+    x = rng.standard_normal((npairs, 2, nlat, nlon)).astype(np.float32)
+    c = run_plan(make_plan(_lib.VSHT, nlat, nlon, L, M, vw, engine), x, (npairs, 2, L, M), torch.complex64, npairs)
+    assert err(c, orc.vsht_forward(x.astype(np.float64), vw)) <= TOL
+    a = (rng.standard_normal((npairs, 2, L, M)) + 1j * rng.standard_normal((npairs, 2, L, M))).astype(np.complex64)
+    v = run_plan(make_plan(_lib.IVSHT, nlat, nlon, L, M, vp, engine), a, (npairs, 2, nlat, nlon), torch.float32, npairs)
+    assert err(v, orc.vsht_inverse(a.astype(np.complex128), vp, nlon)) <= TOL

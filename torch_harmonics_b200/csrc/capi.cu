@@ -61,7 +61,7 @@ WsLayout ws_layout(const Plan &pl, int nfields, int m0, int mloc) {
     const size_t ncp = (size_t)col_pitch((long long)ncols);  // row pitch of the column-contiguous operands
     if (pl.analysis) {
         w.op_bytes = (size_t)2 * mloc * round_up(pl.Ka, kBK) * ncp * sizeof(float);
-        if (!pl.vector) w.y_bytes = (size_t)(pl.group_b0[2 * (m0 + mloc)] - pl.group_b0[2 * m0]) * ncols * kBK * sizeof(float);
+        w.y_bytes = (size_t)(pl.group_b0[2 * (m0 + mloc)] - pl.group_b0[2 * m0]) * ncols * kBK * sizeof(float);  // degree slabs
     } else {
         const long long slabs = pl.group_b0[2 * (m0 + mloc)] - pl.group_b0[2 * m0];
         w.op_bytes = (size_t)slabs * ncols * kBK * sizeof(float);
@@ -94,11 +94,10 @@ GemmParams gemm_params(const Plan &pl, int nfields, int m0, int mloc, const floa
         gp.b_dx = kBK;
         gp.b_kext = pl.Ka;
         gp.b_unit0 = 2 * ml;
-#ifdef SHTB200_DIRECT_EPI  // build-time switch for A/B measurements: scalar analysis writes (field, l, m) from the contraction's epilogue
-        gp.mode = EPI_COEFFS;
-#else
-        gp.mode = pl.vector ? EPI_COEFFS : EPI_SLABS;
-#endif
+        // The contraction leaves degree slabs; a tiled transpose turns them into (field, l, m).  Writing (field, l, m) from
+        // the epilogue instead (8-byte stores, a whole coefficient array apart per column) was measured on the
+        // scalar transform at 73 fields: contraction 0.30 ms instead of 0.16 + 0.08 ms.
+        gp.mode = EPI_SLABS;
         gp.slab0 = pl.d_gb0;
         gp.slab_unit0 = pl.group_b0[2 * ml];
     } else {
@@ -159,24 +158,15 @@ int execute_full(Plan &pl, const void *in, void *out, int nfields, void *ws, siz
     if (pl.analysis) {
         float *X = reinterpret_cast<float *>(ws);
         float *Z = reinterpret_cast<float *>(reinterpret_cast<char *>(ws) + align256(w.op_bytes));
-#ifdef SHTB200_DIRECT_EPI
-        const bool direct = true;
-#else
-        const bool direct = pl.vector;
-#endif
         if ((rc = launch_fft_analysis(pl, reinterpret_cast<const float *>(in), X, nfields, st))) return rc;
         mark(pl, st);
         pl.last_launches += 1;
-        GemmParams gp = gemm_params(pl, nfields, 0, pl.mmax, X, direct ? reinterpret_cast<float *>(out) : Z);
+        GemmParams gp = gemm_params(pl, nfields, 0, pl.mmax, X, Z);
         if ((rc = run_gemm(pl, gp, st))) return rc;
         mark(pl, st);
-        if (direct) {  // exact zeros above the diagonal (the epilogue writes l >= m only)
-            if ((rc = launch_zero_upper(pl, reinterpret_cast<float2 *>(out), nfields, 0, pl.mmax, st))) return rc;
-            pl.last_launches += 1;
-        } else {
-            if ((rc = launch_unpack_coeffs(pl, Z, reinterpret_cast<float2 *>(out), nfields, 0, pl.mmax, st))) return rc;
-            pl.last_launches += 1;
-        }
+        // (a vector pair's four columns are the (re, im) pairs of its two output fields: the same slab layout with twice the fields)
+        if ((rc = launch_unpack_coeffs(pl, Z, reinterpret_cast<float2 *>(out), nfields, 0, pl.mmax, st))) return rc;
+        pl.last_launches += 1;
         mark(pl, st);
     } else {
         float *Ct = reinterpret_cast<float *>(ws);
@@ -673,11 +663,7 @@ int shtb200_legendre(shtb200_plan *pl, const void *in_dev, void *out_dev, int nf
         float *X = reinterpret_cast<float *>(workspace_dev);
         float *Z = reinterpret_cast<float *>(reinterpret_cast<char *>(workspace_dev) + align256(w.op_bytes));
         if ((rc = launch_fold_modes(*pl, reinterpret_cast<const float2 *>(in_dev), X, nfields, m0, mloc, st))) return rc;
-        if (pl->vector) {  // the contraction writes the coefficients itself; the l < m triangle is zeroed first
-            if ((rc = launch_zero_upper(*pl, reinterpret_cast<float2 *>(out_dev), nfields, m0, mloc, st))) return rc;
-            GemmParams gp = gemm_params(*pl, nfields, m0, mloc, X, reinterpret_cast<float *>(out_dev));
-            if ((rc = run_gemm(*pl, gp, st))) return rc;
-        } else {
+        {
             GemmParams gp = gemm_params(*pl, nfields, m0, mloc, X, Z);
             if ((rc = run_gemm(*pl, gp, st))) return rc;
             if ((rc = launch_unpack_coeffs(*pl, Z, reinterpret_cast<float2 *>(out_dev), nfields, m0, mloc, st))) return rc;

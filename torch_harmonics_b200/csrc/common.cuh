@@ -85,7 +85,6 @@ constexpr int kItemRowsMax = 128;  // one 128-row tensor-core tile
 
 // How a finished tile leaves the contraction kernel.
 enum EpilogueMode : int {
-    EPI_COEFFS = 0,   // analysis: rows are degrees l = m + p + 2 r  -> complex64 out[n][l][m - m0]
     EPI_LATROWS = 1,  // synthesis: rows are folded latitudes k'      -> float Y[y_row(group, k')][col] (row pitch ld)
     EPI_SLABS = 2,    // analysis: rows are degrees -> float Z[(slab0[g] + r / 32) * ncols + col][r % 32], the same
                       // degree-slab layout the synthesis contraction reads its coefficients from
@@ -107,7 +106,7 @@ struct GemmParams {
     int nitems;
     int mode;             // EpilogueMode
     float *out;           // destination
-    int lmax, mmax_out;   // EPI_COEFFS: out dims (mmax_out = number of orders stored = mloc)
+    int lmax, mmax_out;   // degrees; number of orders of the call (mloc)
     int m0;               // first order stored in out (orders outside [m0, m0 + mmax_out) are skipped)
     int m_base;           // first order the plan holds: slab0 is indexed by 2 (m - m_base) + p
     long long out_ld;     // EPI_LATROWS: floats per row of Y
@@ -218,7 +217,6 @@ int launch_polar_extent(const Plan &pl, const float *table, float rel, std::vect
 // (m0 = first order of the call, an actual order: m_base <= m0, m0 + mloc <= m_base + mmax)
 int launch_pack_coeffs(const Plan &pl, const float2 *c, float *Ct, int nfields, int m0, int mloc, cudaStream_t st);
 int launch_unpack_coeffs(const Plan &pl, const float *Z, float2 *c, int nfields, int m0, int mloc, cudaStream_t st);
-int launch_zero_upper(const Plan &pl, float2 *c, int nfields, int m0, int mloc, cudaStream_t st);
 int launch_fold_modes(const Plan &pl, const float2 *Xc, float *X, int nfields, int m0, int mloc, cudaStream_t st);
 int launch_unfold_modes(const Plan &pl, const float *Y, float2 *Xc, int nfields, int m0, int mloc, cudaStream_t st);  // honours group_krow0
 

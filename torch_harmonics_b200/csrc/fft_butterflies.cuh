@@ -128,6 +128,8 @@ template <bool INV> struct Dft<12, INV> : DftComposite<3, 4, INV> {};
 template <bool INV> struct Dft<15, INV> : DftComposite<3, 5, INV> {};
 template <bool INV> struct Dft<16, INV> : DftComposite<4, 4, INV> {};
 
+template <bool INV> struct Dft<20, INV> : DftComposite<4, 5, INV> {};
+template <bool INV> struct Dft<32, INV> : DftComposite<4, 8, INV> {};
 template <bool INV> struct Dft<36, INV> : DftComposite<4, 9, INV> {};
 template <bool INV> struct Dft<40, INV> : DftComposite<8, 5, INV> {};
 

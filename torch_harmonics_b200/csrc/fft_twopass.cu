@@ -1,4 +1,5 @@
-// Longitude transforms of the scalar SHT for nlon = R1 * R2 (1440 = 40 * 36): register-resident two-pass FFT kernels.
+// Longitude transforms of the SHT for nlon = R1 * R2 (1440 = 40 * 36, 720 = 36 * 20, 512 = 32 * 16): register-resident
+// two-pass FFT kernels.
 //
 // A persistent CTA (two per SM) works through (field block, latitude pair) items.  An item = eight fields x one
 // pair of rows (k', nlat-1-k'), i.e. eight complex transforms of z = north + i south.  R1 threads carry one transform,
@@ -111,7 +112,13 @@ __device__ __forceinline__ void decode_item(int it, int Kh, int nfields, int *kn
 // Register arrays are filled unconditionally (idle lanes read valid but meaningless addresses and only their stores are
 // predicated): an array that is initialised under a condition counts as live around the whole item loop, and the two
 // passes' arrays would then not share registers.  Thread coordinates are re-derived in every phase for the same reason.
-template <int R1, int R2>
+// VEC = 2: the transforms of an item are the (theta, phi) components of four vector fields; a.nfields counts component
+// fields (2 per pair).  The operand then has two row segments per group, k' against the d/dtheta table with the fold of
+// parity 1 - p and Kh + k' against the m / sin(theta) table with the fold of parity p, and four columns per pair that
+// carry the sign pattern of torch_harmonics/sht.py:488-493:
+//     rows k'     : ( Re X0,  Im X0, -Re X1, -Im X1)        rows Kh + k' : (-Im X1,  Re X1, -Im X0,  Re X0)
+// (X0 = theta component, X1 = phi component): every thread still writes 8-byte pieces of its own transform only.
+template <int R1, int R2, int VEC>
 __global__ void __launch_bounds__(TwoPass<R1, R2>::THREADS, 2) fft_analysis_twopass_kernel(const TwoPassArgs a) {
     using TP = TwoPass<R1, R2>;
     constexpr int N = TP::N, TS = TP::TS, TS2 = TP::TS / 2;
@@ -123,7 +130,7 @@ __global__ void __launch_bounds__(TwoPass<R1, R2>::THREADS, 2) fft_analysis_twop
 
     // rows of the last 32-row block beyond the contraction length: the contraction reads them, they must be zeros
     for (int z = blockIdx.x; z < a.kpad * nfb; z += gridDim.x) {
-        const int kk = a.Kh + z / nfb, f0 = (z % nfb) * kNT, ngroups = 2 * a.mmax;
+        const int kk = VEC * a.Kh + z / nfb, f0 = (z % nfb) * kNT, ngroups = 2 * a.mmax;
         for (int i = threadIdx.x; i < ngroups * 4; i += blockDim.x) {
             const int g = i >> 2, c = 2 * f0 + 4 * (i & 3);
             if (c < 2 * a.nfields) *reinterpret_cast<float4 *>(a.op + (size_t)blocked_row(g, kk, ngroups) * a.ncp + c) = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -213,6 +220,8 @@ __global__ void __launch_bounds__(TwoPass<R1, R2>::THREADS, 2) fft_analysis_twop
             const unsigned char *kf_s = reinterpret_cast<const unsigned char *>(ms_s + a.mpad);
             const float sc0 = (a.nlat - 1 - kn == kn) ? 0.25f : 0.5f;  // odd nlat: the equator row is its own mirror image and counts once
             float *xb = a.op + ((size_t)(kn >> 5) * ngroups * 32 + (kn & 31)) * a.ncp + 2 * (f0 + t);
+            const int k2 = a.Kh + kn;  // VEC = 2: row of the second segment
+            float *xb2 = a.op + ((size_t)(k2 >> 5) * ngroups * 32 + (k2 & 31)) * a.ncp + 2 * (f0 + t);
             const size_t gstride = (size_t)32 * a.ncp;  // floats between the rows of consecutive groups
 #pragma unroll
             for (int i = 0; i <= R2 / 2; ++i) {
@@ -231,10 +240,23 @@ __global__ void __launch_bounds__(TwoPass<R1, R2>::THREADS, 2) fft_analysis_twop
                 const bool edge = a.zero_imag_edges && (m == 0 || 2 * m == N);
                 const float2 e = make_float2(sc * (ar + br), edge ? 0.f : sc * (ai + bi));
                 const float2 o = make_float2(sc * (ar - br), edge ? 0.f : sc * (ai - bi));
-                const int kf = kf_s[m];  // (the contraction does not read rows above the group's polar extent)
-                float *pe = xb + (size_t)(2 * m) * gstride;
-                if (kn >= (kf & 15) * kBK) *reinterpret_cast<float2 *>(pe) = e;
-                if (kn >= (kf >> 4) * kBK) *reinterpret_cast<float2 *>(pe + gstride) = o;
+                if (VEC == 1) {
+                    const int kf = kf_s[m];  // (the contraction does not read rows above the group's polar extent)
+                    float *pe = xb + (size_t)(2 * m) * gstride;
+                    if (kn >= (kf & 15) * kBK) *reinterpret_cast<float2 *>(pe) = e;
+                    if (kn >= (kf >> 4) * kBK) *reinterpret_cast<float2 *>(pe + gstride) = o;
+                } else {
+                    const int comp = t & 1;
+                    const float sg = comp ? -1.f : 1.f;
+                    // own columns inside the pair's four: the first segment at 2 comp, the second at 2 (1 - comp)
+                    float *p0 = xb + (size_t)(2 * m) * gstride;                    // rows k'
+                    float *p1 = xb2 + (2 - 4 * comp) + (size_t)(2 * m) * gstride;  // rows Kh + k'
+                    // group 2 m (p = 0): first segment takes the odd fold, second the even one; group 2 m + 1 the other way
+                    *reinterpret_cast<float2 *>(p0) = make_float2(sg * o.x, sg * o.y);
+                    *reinterpret_cast<float2 *>(p1) = make_float2(-e.y, e.x);
+                    *reinterpret_cast<float2 *>(p0 + gstride) = make_float2(sg * e.x, sg * e.y);
+                    *reinterpret_cast<float2 *>(p1 + gstride) = make_float2(-o.y, o.x);
+                }
             }
             // orders beyond the Nyquist frequency (mmax > n / 2 + 1) are zeros
             for (int m = mtop + (tid >> 3); m < a.mmax; m += TP::THREADS >> 3) {
@@ -242,6 +264,11 @@ __global__ void __launch_bounds__(TwoPass<R1, R2>::THREADS, 2) fft_analysis_twop
                     float *pe = xb + (size_t)(2 * m) * gstride;
                     *reinterpret_cast<float2 *>(pe) = make_float2(0.f, 0.f);
                     *reinterpret_cast<float2 *>(pe + gstride) = make_float2(0.f, 0.f);
+                    if (VEC == 2) {
+                        pe = xb2 + (size_t)(2 * m) * gstride;
+                        *reinterpret_cast<float2 *>(pe) = make_float2(0.f, 0.f);
+                        *reinterpret_cast<float2 *>(pe + gstride) = make_float2(0.f, 0.f);
+                    }
                 }
             }
         }
@@ -388,9 +415,12 @@ __global__ void __launch_bounds__(TwoPass<R1, R2>::THREADS, 2) fft_synthesis_two
     if (tid_now() == 0) ptx::bulk_wait_read_all();  // shared memory stays allocated until the last rows have been read
 }
 
+// nfields: scalar fields, or (theta, phi) pairs of a vector plan (two component fields each)
 template <int R1, int R2>
 int launch_twopass(const Plan &pl, bool analysis, const float *in, float *out, int nfields, cudaStream_t st) {
     using TP = TwoPass<R1, R2>;
+    const int vec = pl.vector ? 2 : 1;
+    nfields *= vec;  // component fields from here on
     TwoPassArgs a{};
     a.blob = pl.d_tp_blob;
     a.blob_bytes = pl.tp_blob_bytes;
@@ -410,8 +440,13 @@ int launch_twopass(const Plan &pl, bool analysis, const float *in, float *out, i
         a.grid_in = in;
         a.op = out;
         a.kpad = (int)(round_up(pl.Ka, kBK) - pl.Ka);
-        SHT_CUDA_CHECK(cudaFuncSetAttribute(fft_analysis_twopass_kernel<R1, R2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        fft_analysis_twopass_kernel<R1, R2><<<grid, TP::THREADS, smem, st>>>(a);
+        if (vec == 2) {
+            SHT_CUDA_CHECK(cudaFuncSetAttribute(fft_analysis_twopass_kernel<R1, R2, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            fft_analysis_twopass_kernel<R1, R2, 2><<<grid, TP::THREADS, smem, st>>>(a);
+        } else {
+            SHT_CUDA_CHECK(cudaFuncSetAttribute(fft_analysis_twopass_kernel<R1, R2, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            fft_analysis_twopass_kernel<R1, R2, 1><<<grid, TP::THREADS, smem, st>>>(a);
+        }
     } else {
         a.op = const_cast<float *>(in);
         a.grid_out = out;
@@ -429,11 +464,14 @@ bool twopass_supported(int nlon, int *r1, int *r2) {
 #ifdef SHTB200_DISABLE_TWOPASS  // build-time switch for A/B measurements against the general kernels
     return false;
 #endif
-    if (nlon == 1440) {
-        *r1 = 40;
-        *r2 = 36;
-        return true;
-    }
+    // nlon = R1 * R2 with R2 <= R1 <= 40 (the radices are carried in registers), R1 a multiple of 4, R2 even
+    static const int splits[][3] = {{1440, 40, 36}, {720, 36, 20}, {512, 32, 16}};
+    for (const auto &sp : splits)
+        if (nlon == sp[0]) {
+            *r1 = sp[1];
+            *r2 = sp[2];
+            return true;
+        }
     return false;
 }
 
@@ -442,7 +480,7 @@ bool twopass_supported(int nlon, int *r1, int *r2) {
 int build_twopass_tables(Plan &pl, const std::vector<float> &mscale) {
     int r1 = 0, r2 = 0;
     pl.twopass = false;
-    if (pl.vector || !twopass_supported(pl.nlon, &r1, &r2)) return SHTB200_OK;
+    if (!twopass_supported(pl.nlon, &r1, &r2)) return SHTB200_OK;
     const int n = pl.nlon, ntw = (r1 - 1) * r2;
     const int mpad = (int)round_up(pl.mmax, 16);
     std::vector<unsigned char> blob(sizeof(float2) * ntw + sizeof(float) * mpad + mpad, 0);
@@ -468,12 +506,17 @@ int build_twopass_tables(Plan &pl, const std::vector<float> &mscale) {
 }
 
 // Both need 16-byte aligned rows (bulk copies): the caller falls back to the general kernels otherwise.
-int launch_fft_analysis_twopass(const Plan &pl, const float *x, float *X, int nfields, cudaStream_t st) {
-    return launch_twopass<40, 36>(pl, true, x, X, nfields, st);
+static int dispatch_twopass(const Plan &pl, bool analysis, const float *in, float *out, int nfields, cudaStream_t st) {
+    switch (pl.nlon) {
+        case 1440: return launch_twopass<40, 36>(pl, analysis, in, out, nfields, st);
+        case 720: return launch_twopass<36, 20>(pl, analysis, in, out, nfields, st);
+        case 512: return launch_twopass<32, 16>(pl, analysis, in, out, nfields, st);
+    }
+    return fail(SHTB200_EINVAL, "no two-pass FFT kernel for this nlon");
 }
 
-int launch_fft_synthesis_twopass(const Plan &pl, const float *Y, float *x, int nfields, cudaStream_t st) {
-    return launch_twopass<40, 36>(pl, false, Y, x, nfields, st);
-}
+int launch_fft_analysis_twopass(const Plan &pl, const float *x, float *X, int nfields, cudaStream_t st) { return dispatch_twopass(pl, true, x, X, nfields, st); }
+
+int launch_fft_synthesis_twopass(const Plan &pl, const float *Y, float *x, int nfields, cudaStream_t st) { return dispatch_twopass(pl, false, Y, x, nfields, st); }
 
 }  // namespace shtb200

@@ -80,17 +80,7 @@ __global__ void __launch_bounds__(256) legendre_simt_kernel(GemmParams gp) {
         const int r = row0 + ty * 4 + i;
         if (r >= it.rows) continue;
         const int rg = it.r0 + r;  // row index inside the group
-        if (gp.mode == EPI_COEFFS) {
-            const int l = it.m + it.p + 2 * rg;
-#pragma unroll
-            for (int j = 0; j < 4; j += 2) {
-                const int c = col0 + tx * 4 + j;
-                if (c >= gp.ncols) continue;
-                // columns come in (re, im) pairs of one output field
-                float2 *o = reinterpret_cast<float2 *>(gp.out) + ((size_t)(c >> 1) * gp.lmax + l) * gp.mmax_out + (it.m - gp.m0);
-                *o = make_float2(acc[i][j], acc[i][j + 1]);
-            }
-        } else if (gp.mode == EPI_SLABS) {
+        if (gp.mode == EPI_SLABS) {
             const long long slab = gp.slab0[2 * (it.m - gp.m_base) + it.p] - gp.slab_unit0 + (rg >> 5);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {

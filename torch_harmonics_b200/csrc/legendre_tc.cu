@@ -17,8 +17,7 @@
 //               tensor-memory accumulators.  It waits on ONE barrier per k-step (both splitters done) and commits to
 //               ONE barrier per k-step (MMAs done), which everybody who recycles a stage or an A slot watches.
 //   warps 10-17 epilogue: tcgen05.ld of a finished accumulator while the next units are being multiplied,
-//               stores to the degree-slab array / coefficient array (analysis) or the latitude-row operand of the
-//               synthesis FFT.
+//               stores to the degree-slab array (analysis) or the latitude-row operand of the synthesis FFT.
 //
 // Every mbarrier wait is bounded: when one runs out the CTA raises a device error word and unwinds.
 // Replaces torch.einsum -> aten::bmm at torch_harmonics/sht.py:180-181, :333-334 (vector :488-493, :638-643).
@@ -354,16 +353,7 @@ legendre_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                     continue;
                 }
                 if (!rvalid) continue;
-                if (gp.mode == EPI_COEFFS) {
-                    const int l = w.it.m + w.it.p + 2 * rg;
-                    float2 *o = reinterpret_cast<float2 *>(gp.out) + (size_t)l * gp.mmax_out + (w.it.m - gp.m0);
-                    const size_t fstride = (size_t)gp.lmax * gp.mmax_out;
-#pragma unroll
-                    for (int j = 0; j < 16; j += 2) {
-                        const int col = col0 + cc + j;
-                        if (col < gp.ncols) o[(size_t)(col >> 1) * fstride] = make_float2(v[j], v[j + 1]);
-                    }
-                } else if (gp.mode == EPI_SLABS) {
+                if (gp.mode == EPI_SLABS) {
                     const long long slab = gp.slab0[2 * (w.it.m - gp.m_base) + w.it.p] - gp.slab_unit0 + (rg >> 5);
                     float *o = gp.out + (size_t)slab * gp.ncols * kBK + (rg & 31);
 #pragma unroll

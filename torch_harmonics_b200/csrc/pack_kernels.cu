@@ -5,8 +5,6 @@
 //  * pack_coeffs    : synthesis, per call: coefficients (field, l, m) -> order-major operand with the
 //                     degree index contiguous (replaces the transpose + real/imag split copies of
 //                     torch_harmonics/sht.py:326-328 and :630-633).
-//  * zero_upper     : analysis: exact zeros for l < m (the reference gets them from the zero half of its
-//                     dense table, torch_harmonics/legendre.py:77-78).
 //  * fold / unfold  : distributed stages: plain complex (field, k, m) <-> folded order-major operand.
 
 #include <algorithm>
@@ -262,13 +260,63 @@ __global__ void __launch_bounds__(256) coeff_slab_transpose_kernel(float2 *__res
     }
 }
 
-__global__ void zero_upper_kernel(float2 *c, long long nfl, int lmax, int mloc, int m0) {
-    // one thread per (field * l, m) element; only the l < m ones are written
-    const long long total = nfl * mloc;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-        const int mi = (int)(i % mloc);
-        const int l = (int)((i / mloc) % lmax);
-        if (l < mi + m0) c[i] = make_float2(0.f, 0.f);
+// Vector synthesis: the same tiled transpose from c[(pair, component)][l][mi] into the two-segment slabs the vector
+// contraction reads, Ct[(b0[g] + kb) * ncols + 4 pair + cc][kk].  For group g = 2 m + p the first kb0[g] slabs (segment 0,
+// contracted with the d/dtheta table) hold the degrees of parity 1 - p, the others (segment 1, m / sin(theta) table) the
+// degrees of parity p.  A degree l = m + pi + 2 r of component `comp` therefore lands in
+//     segment 0 of group 2 m + (1 - pi):  columns 2 comp + (re, im),            sign - for the phi component,
+//     segment 1 of group 2 m + pi:        columns 2 (1 - comp) + (im, re),      sign - for the imaginary part
+// (component / part / sign pattern of torch_harmonics/sht.py:638-643).  One CTA: 32 orders x one slab index x one component field.
+__global__ void __launch_bounds__(256) coeff_slab_transpose_vec_kernel(const float2 *__restrict__ c, float *__restrict__ S, const long long *__restrict__ b0,
+                                                                       const int *__restrict__ gkb, const int *__restrict__ gkb0, int ncols, int lmax, int mloc,
+                                                                       int m0, int mbase) {
+    __shared__ float2 T[kTileRows][32];
+    const int mb0 = blockIdx.x * 32, sb = blockIdx.y, cf = blockIdx.z;  // cf = 2 pair + component
+    const int pair = cf >> 1, comp = cf & 1;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int mi_l = mb0 + lane;
+    const int lbase = m0 + mb0 + 64 * sb;
+    if (lbase >= lmax) return;  // no degree of this band exists for any order of the tile
+    {
+        float2 v[kTileRows / 8];
+        const float2 *crow = c + ((size_t)cf * lmax + lbase + warp) * mloc + mi_l;
+        const int d0 = warp - lane, lrem = lmax - lbase - warp;
+        const bool colok = mi_l < mloc;
+#pragma unroll
+        for (int it = 0; it < kTileRows / 8; ++it) {
+            const int d = d0 + 8 * it;
+            v[it] = make_float2(0.f, 0.f);
+            if (colok && d >= 0 && d < 64 && 8 * it < lrem) v[it] = __ldg(crow + (size_t)(8 * it) * mloc);
+        }
+#pragma unroll
+        for (int it = 0; it < kTileRows / 8; ++it) {
+            const int ll = warp + 8 * it;
+            T[ll][lane ^ tile_swz(ll)] = v[it];
+        }
+        __syncthreads();
+    }
+    // lane = (parity pi of l - m, re / im, quad of r): four consecutive r per store, two destinations
+    const int q = lane & 7, ri = (lane >> 3) & 1, pi = lane >> 4;
+    const float sa = comp ? -1.f : 1.f, sbn = ri ? -1.f : 1.f;
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+        const int ml = warp + 8 * it, mi = mb0 + ml;
+        if (mi >= mloc) continue;
+        const int gm = 2 * (m0 - mbase + mi);  // group of parity 0 of this order inside the plan
+        const int ga = gm + (1 - pi), gb = gm + pi;
+        float v[4];
+        const int ll0 = ml + pi + 8 * q;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int ll = ll0 + 2 * i;
+            v[i] = reinterpret_cast<const float *>(&T[ll][ml ^ tile_swz(ll)])[ri];
+        }
+        const long long base = b0[2 * (m0 - mbase)];
+        if (sb < gkb0[ga])  // segment 0 of group ga
+            *reinterpret_cast<float4 *>(S + ((size_t)(b0[ga] - base + sb) * ncols + 4 * pair + 2 * comp + ri) * kBK + 4 * q) = make_float4(sa * v[0], sa * v[1], sa * v[2], sa * v[3]);
+        if (sb < gkb[gb] - gkb0[gb])  // segment 1 of group gb
+            *reinterpret_cast<float4 *>(S + ((size_t)(b0[gb] - base + gkb0[gb] + sb) * ncols + 4 * pair + 2 * (1 - comp) + (1 - ri)) * kBK + 4 * q) =
+                make_float4(sbn * v[0], sbn * v[1], sbn * v[2], sbn * v[3]);
     }
 }
 
@@ -437,6 +485,12 @@ int launch_pack_coeffs(const Plan &pl, const float2 *c, float *Ct, int nfields, 
         SHT_CUDA_CHECK(cudaGetLastError());
         return SHTB200_OK;
     }
+    if (pl.vector && 2 * nfields <= 65535) {
+        dim3 grid(ceil_div(mloc, 32), ceil_div(pl.Lh, kBK), 2 * nfields);
+        coeff_slab_transpose_vec_kernel<<<grid, 256, 0, st>>>(c, Ct, pl.d_gb0, pl.d_gkb, pl.d_gkb0, ncols, pl.lmax, mloc, m0, pl.m_base);
+        SHT_CUDA_CHECK(cudaGetLastError());
+        return SHTB200_OK;
+    }
     const long long per_group = (long long)ceil_div(pl.Lh, kBK) * pl.ncomp * ncols * kBK;
     dim3 grid(grid_x_for(per_group), 2 * mloc);
     pack_coeffs_kernel<<<grid, 256, 0, st>>>(c, Ct, pl.d_gb0, pl.d_gkb, pl.d_gkb0, ncols, pl.lmax, mloc, m0, pl.m_base, pl.vector ? 1 : 0);
@@ -445,22 +499,14 @@ int launch_pack_coeffs(const Plan &pl, const float2 *c, float *Ct, int nfields, 
 }
 
 int launch_unpack_coeffs(const Plan &pl, const float *Z, float2 *c, int nfields, int m0, int mloc, cudaStream_t st) {
-    if (pl.vector) return fail(SHTB200_EINVAL, "slab output is implemented for the scalar kinds only");
     if (mloc == 0 || nfields == 0) return SHTB200_OK;
+    if (pl.vector) nfields *= 2;  // a vector pair is two output fields (spheroidal, toroidal) side by side
     if (nfields > 65535) return fail(SHTB200_EINVAL, "too many fields in one call (limit 65535)");
     const int nsb = ceil_div(pl.Lh, kBK);
     // extra tile rows for the degrees above the diagonal of the last order block: l < m0 + 32 (blocks - 1)
     const int nzero = ceil_div(std::min(m0 + 32 * (ceil_div(mloc, 32) - 1), pl.lmax), 64);
     dim3 grid(ceil_div(mloc, 32), nsb + nzero, nfields);
     coeff_slab_transpose_kernel<false><<<grid, 256, 0, st>>>(c, const_cast<float *>(Z), pl.d_gb0, pl.d_gkb, 2 * nfields, pl.lmax, mloc, m0, nsb, pl.m_base);
-    SHT_CUDA_CHECK(cudaGetLastError());
-    return SHTB200_OK;
-}
-
-int launch_zero_upper(const Plan &pl, float2 *c, int nfields, int m0, int mloc, cudaStream_t st) {
-    const long long nfl = (long long)nfields * (pl.vector ? 2 : 1) * pl.lmax;
-    if (nfl == 0 || mloc == 0) return SHTB200_OK;
-    zero_upper_kernel<<<grid_x_for(nfl * mloc), 256, 0, st>>>(c, nfl, pl.lmax, mloc, m0);
     SHT_CUDA_CHECK(cudaGetLastError());
     return SHTB200_OK;
 }

@@ -159,6 +159,47 @@ class _DistributedBase(nn.Module):
             self._plans[key] = pl
         return pl
 
+    # Number of field chunks the inference path pipelines (0 / 1 switches it off) and the smallest local tensor worth it.
+    pipeline_chunks = 4
+    pipeline_min_bytes = 64 << 20
+
+    def _run_stages(self, x, stages):
+        """Apply the stage functions ``stage(tensor, nfields)`` to the flattened batch ``x`` (fields on axis 0; ``nfields`` is
+        the number of fields of the batch the tensor belongs to, which the gathering transposes need for their split sizes).
+
+        Every stage maps (fields, ...) to (fields, ...) and the fields never mix, so the batch may be cut into chunks that
+        run as independent transforms.  When no gradient is recorded and the tensor is large, the chunks are issued stage
+        by stage on streams of their own: NCCL executes the all-to-alls in issue order (chunk 0, chunk 1, ... of one
+        stage), while the FFT / Legendre kernels of a chunk run on its stream next to the other chunks' exchanges."""
+        n = x.shape[0]
+        gmax = max(self.comm_size_polar, self.comm_size_azimuth)
+        nchunks = min(self.pipeline_chunks, n // max(gmax, 1))
+        if (gmax == 1 or nchunks < 2 or torch.is_grad_enabled() and x.requires_grad or not x.is_cuda
+                or x.numel() * x.element_size() < self.pipeline_min_bytes):
+            for st in stages:
+                x = st(x, n)
+            return x
+        main = torch.cuda.current_stream(x.device)
+        if not hasattr(self, "_streams") or len(self._streams) < nchunks or self._streams[0].device != x.device:
+            self._streams = [torch.cuda.Stream(device=x.device) for _ in range(nchunks)]
+        parts = list(torch.tensor_split(x, nchunks, dim=0))
+        counts = [p.shape[0] for p in parts]
+        for c in range(nchunks):
+            self._streams[c].wait_stream(main)
+        for st in stages:
+            for c in range(nchunks):
+                with torch.cuda.stream(self._streams[c]):
+                    parts[c] = st(parts[c], counts[c])
+        out = torch.empty((n,) + tuple(parts[0].shape[1:]), dtype=parts[0].dtype, device=x.device)
+        n0 = 0
+        for c in range(nchunks):
+            with torch.cuda.stream(self._streams[c]):
+                out[n0:n0 + parts[c].shape[0]].copy_(parts[c])
+            n0 += parts[c].shape[0]
+            main.wait_stream(self._streams[c])
+        # (the chunk tensors were allocated on the chunk streams and die here; `out` belongs to the caller's stream)
+        return out
+
     def _apply(self, fn, *args, **kwargs):
         # buffers may move or change dtype: plans built from the old table are dropped
         out = super()._apply(fn, *args, **kwargs)
@@ -189,21 +230,19 @@ class DistributedRealSHT(_DistributedBase):
         _require(x, torch.float32, "DistributedRealSHT")
 
         x, lead_shape, lead_size = flatten_and_pad_leading_dims(x, max(self.comm_size_polar, self.comm_size_azimuth))
-        num_chans = x.shape[-3]
-        # fields get sharded over the azimuth group, longitudes become local
-        if self.comm_size_azimuth > 1:
-            x = distributed_transpose_azimuth(x, (-3, -1), self.lon_shapes)
-        x = _RfftStage.apply(x, self.mmax, 2.0 * math.pi)
-        # orders get sharded, fields local again
-        if self.comm_size_azimuth > 1:
-            x = distributed_transpose_azimuth(x, (-1, -3), compute_split_shapes(num_chans, self.comm_size_azimuth))
-        # fields get sharded over the polar group, latitudes become local
-        if self.comm_size_polar > 1:
-            x = distributed_transpose_polar(x, (-3, -2), self.lat_shapes)
-        x = _LegendreStage.apply(x, self, False, self.lmax)
-        # degrees get sharded, fields local again
-        if self.comm_size_polar > 1:
-            x = distributed_transpose_polar(x, (-2, -3), compute_split_shapes(num_chans, self.comm_size_polar))
+        A, P = self.comm_size_azimuth, self.comm_size_polar
+        stages = []
+        if A > 1:  # fields get sharded over the azimuth group, longitudes become local
+            stages.append(lambda t, n: distributed_transpose_azimuth(t, (-3, -1), self.lon_shapes))
+        stages.append(lambda t, n: _RfftStage.apply(t, self.mmax, 2.0 * math.pi))
+        if A > 1:  # orders get sharded, fields local again
+            stages.append(lambda t, n: distributed_transpose_azimuth(t, (-1, -3), compute_split_shapes(n, A)))
+        if P > 1:  # fields get sharded over the polar group, latitudes become local
+            stages.append(lambda t, n: distributed_transpose_polar(t, (-3, -2), self.lat_shapes))
+        stages.append(lambda t, n: _LegendreStage.apply(t, self, False, self.lmax))
+        if P > 1:  # degrees get sharded, fields local again
+            stages.append(lambda t, n: distributed_transpose_polar(t, (-2, -3), compute_split_shapes(n, P)))
+        x = self._run_stages(x, stages)
         return unpad_and_unflatten_leading_dims(x, lead_shape, lead_size)
 
 
@@ -227,17 +266,19 @@ class DistributedInverseRealSHT(_DistributedBase):
         _require(x, torch.complex64, "DistributedInverseRealSHT")
 
         x, lead_shape, lead_size = flatten_and_pad_leading_dims(x, max(self.comm_size_polar, self.comm_size_azimuth))
-        num_chans = x.shape[-3]
-        if self.comm_size_polar > 1:
-            x = distributed_transpose_polar(x, (-3, -2), self.l_shapes)
-        x = _LegendreStage.apply(x, self, False, self.nlat)
-        if self.comm_size_polar > 1:
-            x = distributed_transpose_polar(x, (-2, -3), compute_split_shapes(num_chans, self.comm_size_polar))
-        if self.comm_size_azimuth > 1:
-            x = distributed_transpose_azimuth(x, (-3, -1), self.m_shapes)
-        x = _IrfftStage.apply(x, self.nlon)
-        if self.comm_size_azimuth > 1:
-            x = distributed_transpose_azimuth(x, (-1, -3), compute_split_shapes(num_chans, self.comm_size_azimuth))
+        A, P = self.comm_size_azimuth, self.comm_size_polar
+        stages = []
+        if P > 1:
+            stages.append(lambda t, n: distributed_transpose_polar(t, (-3, -2), self.l_shapes))
+        stages.append(lambda t, n: _LegendreStage.apply(t, self, False, self.nlat))
+        if P > 1:
+            stages.append(lambda t, n: distributed_transpose_polar(t, (-2, -3), compute_split_shapes(n, P)))
+        if A > 1:
+            stages.append(lambda t, n: distributed_transpose_azimuth(t, (-3, -1), self.m_shapes))
+        stages.append(lambda t, n: _IrfftStage.apply(t, self.nlon))
+        if A > 1:
+            stages.append(lambda t, n: distributed_transpose_azimuth(t, (-1, -3), compute_split_shapes(n, A)))
+        x = self._run_stages(x, stages)
         return unpad_and_unflatten_leading_dims(x, lead_shape, lead_size)
 
 
@@ -269,17 +310,19 @@ class DistributedRealVectorSHT(_DistributedBase):
         _require(x, torch.float32, "DistributedRealVectorSHT")
 
         x, lead_shape, lead_size = flatten_and_pad_leading_dims(x, max(self.comm_size_polar, self.comm_size_azimuth), num_trailing_dims=3)
-        num_chans = x.shape[-4]
-        if self.comm_size_azimuth > 1:
-            x = distributed_transpose_azimuth(x, (-4, -1), self.lon_shapes)
-        x = _RfftStage.apply(x, self.mmax, 2.0 * math.pi)
-        if self.comm_size_azimuth > 1:
-            x = distributed_transpose_azimuth(x, (-1, -4), compute_split_shapes(num_chans, self.comm_size_azimuth))
-        if self.comm_size_polar > 1:
-            x = distributed_transpose_polar(x, (-4, -2), self.lat_shapes)
-        x = _LegendreStage.apply(x, self, False, self.lmax)
-        if self.comm_size_polar > 1:
-            x = distributed_transpose_polar(x, (-2, -4), compute_split_shapes(num_chans, self.comm_size_polar))
+        A, P = self.comm_size_azimuth, self.comm_size_polar
+        stages = []
+        if A > 1:
+            stages.append(lambda t, n: distributed_transpose_azimuth(t, (-4, -1), self.lon_shapes))
+        stages.append(lambda t, n: _RfftStage.apply(t, self.mmax, 2.0 * math.pi))
+        if A > 1:
+            stages.append(lambda t, n: distributed_transpose_azimuth(t, (-1, -4), compute_split_shapes(n, A)))
+        if P > 1:
+            stages.append(lambda t, n: distributed_transpose_polar(t, (-4, -2), self.lat_shapes))
+        stages.append(lambda t, n: _LegendreStage.apply(t, self, False, self.lmax))
+        if P > 1:
+            stages.append(lambda t, n: distributed_transpose_polar(t, (-2, -4), compute_split_shapes(n, P)))
+        x = self._run_stages(x, stages)
         return unpad_and_unflatten_leading_dims(x, lead_shape, lead_size, num_trailing_dims=3)
 
 
@@ -305,15 +348,17 @@ class DistributedInverseRealVectorSHT(_DistributedBase):
         _require(x, torch.complex64, "DistributedInverseRealVectorSHT")
 
         x, lead_shape, lead_size = flatten_and_pad_leading_dims(x, max(self.comm_size_polar, self.comm_size_azimuth), num_trailing_dims=3)
-        num_chans = x.shape[-4]
-        if self.comm_size_polar > 1:
-            x = distributed_transpose_polar(x, (-4, -2), self.l_shapes)
-        x = _LegendreStage.apply(x, self, False, self.nlat)
-        if self.comm_size_polar > 1:
-            x = distributed_transpose_polar(x, (-2, -4), compute_split_shapes(num_chans, self.comm_size_polar))
-        if self.comm_size_azimuth > 1:
-            x = distributed_transpose_azimuth(x, (-4, -1), self.m_shapes)
-        x = _IrfftStage.apply(x, self.nlon)
-        if self.comm_size_azimuth > 1:
-            x = distributed_transpose_azimuth(x, (-1, -4), compute_split_shapes(num_chans, self.comm_size_azimuth))
+        A, P = self.comm_size_azimuth, self.comm_size_polar
+        stages = []
+        if P > 1:
+            stages.append(lambda t, n: distributed_transpose_polar(t, (-4, -2), self.l_shapes))
+        stages.append(lambda t, n: _LegendreStage.apply(t, self, False, self.nlat))
+        if P > 1:
+            stages.append(lambda t, n: distributed_transpose_polar(t, (-2, -4), compute_split_shapes(n, P)))
+        if A > 1:
+            stages.append(lambda t, n: distributed_transpose_azimuth(t, (-4, -1), self.m_shapes))
+        stages.append(lambda t, n: _IrfftStage.apply(t, self.nlon))
+        if A > 1:
+            stages.append(lambda t, n: distributed_transpose_azimuth(t, (-1, -4), compute_split_shapes(n, A)))
+        x = self._run_stages(x, stages)
         return unpad_and_unflatten_leading_dims(x, lead_shape, lead_size, num_trailing_dims=3)

@@ -504,7 +504,12 @@ def spatial_record(dev, rank, world, engine, nfields, p_f, p_i):
     t_fwd, _ = timed_blocks(fwd, k, barrier, 0.2, 40, agree=allmax)
     t_inv, _ = timed_blocks(inv, k, barrier, 0.2, 40, agree=allmax)
     t_step, t_fwd, t_inv = allmax(t_step), allmax(t_fwd), allmax(t_inv)
-    # all-to-all volume and time of one forward and one inverse call
+    # all-to-all volume and time of one forward and one inverse call (unpipelined, so that the events bracket the exchanges only)
+    chunks = dsht.pipeline_chunks
+    dsht.pipeline_chunks = disht.pipeline_chunks = 0
+    t_fwd_plain, _ = timed_blocks(fwd, k, barrier, 0.0, 1, agree=allmax)
+    t_inv_plain, _ = timed_blocks(inv, k, barrier, 0.0, 1, agree=allmax)
+    t_fwd_plain, t_inv_plain = allmax(t_fwd_plain), allmax(t_inv_plain)
     barrier()
     prim.exchange_log_start()
     fwd()
@@ -513,6 +518,7 @@ def spatial_record(dev, rank, world, engine, nfields, p_f, p_i):
     prim.exchange_log_start()
     inv()
     log_i = prim.exchange_log_stop()
+    dsht.pipeline_chunks = disht.pipeline_chunks = chunks
 
     def a2a(log):
         sent, recv, ms = sum(v[0] for v in log), sum(v[1] for v in log), sum(v[2] for v in log)
@@ -533,6 +539,8 @@ def spatial_record(dev, rank, world, engine, nfields, p_f, p_i):
         "tolerance": 1e-5, "parity_ok": bool(max(err_fwd, err_rt, err_fix_c or 0.0, err_fix_rt or 0.0) <= 1e-5),
         "fwd_fields_per_s": nf * k / t_fwd, "inv_fields_per_s": nf * k / t_inv, "roundtrip_fields_per_s": nf * k / t_step,
         "fwd_ms": 1e3 * t_fwd / k, "inv_ms": 1e3 * t_inv / k, "roundtrip_ms": 1e3 * t_step / k,
+        "fwd_ms_unpipelined": 1e3 * t_fwd_plain / k, "inv_ms_unpipelined": 1e3 * t_inv_plain / k,
+        "pipelined": bool(min(gh, gw) == 1 and chunks >= 2),
         "all_to_all_forward": af, "all_to_all_inverse": ai,
         "bound": {
             "t_local_hbm_ms": 1e3 * t_local, "t_nvlink_fwd_ms": 1e3 * t_link_f, "t_nvlink_inv_ms": 1e3 * t_link_i, "nvlink_gbs_per_direction": 900.0,

@@ -227,7 +227,9 @@ def _dist_worker(rank, world, port, gh, gw):
                 ok = False
                 msgs.append(f"rank {rank} {'vector ' if vector else ''}{nlat}x{nlon} lmax={lmax} {lead} {grid}: oracle {e0:.2e} {e5:.2e} serial {e1:.2e} {e2:.2e} {e3:.2e} {e4:.2e}")
     # inference path: without a gradient to record, large batches are cut into chunks whose all-to-alls and kernels overlap on
-    # streams of their own; the result must be the one of the plain path, bit for bit (forced here by dropping the size limit)
+    # streams of their own (forced here by dropping the size limit; grids with one distributed axis only).  The chunks pair
+    # the latitude rows differently inside the row FFT (two real rows share one complex transform), so the results agree to
+    # rounding, not bit for bit.
     with warnings.catch_warnings():
         warnings.simplefilter("ignore")
         dsht, disht = thd.DistributedRealSHT(33, 64, lmax=17).cuda(), thd.DistributedInverseRealSHT(33, 64, lmax=17).cuda()
@@ -242,9 +244,10 @@ def _dist_worker(rank, world, port, gh, gw):
         c_pipe = dsht(xl)
         y_pipe = disht(c_pipe)
     torch.cuda.synchronize()
-    if not (torch.equal(c_plain, c_pipe) and torch.equal(y_plain, y_pipe)):
+    ep = max(float((c_pipe - c_plain).abs().max() / c_plain.abs().max()), float((y_pipe - y_plain).abs().max() / y_plain.abs().max()))
+    if not ep <= 2e-6:
         ok = False
-        msgs.append(f"rank {rank}: pipelined inference path differs from the plain path")
+        msgs.append(f"rank {rank}: pipelined inference path differs from the plain path by {ep:.2e}")
     if rank == 0:
         print(f"distributed parity {gh}x{gw}: {len(SCALAR_CASES)} scalar + {len(VECTOR_CASES)} vector cases + pipelined path, ok={ok}", flush=True)
     _finish(ok, msgs)

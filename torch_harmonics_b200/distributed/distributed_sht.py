@@ -170,11 +170,13 @@ class _DistributedBase(nn.Module):
         Every stage maps (fields, ...) to (fields, ...) and the fields never mix, so the batch may be cut into chunks that
         run as independent transforms.  When no gradient is recorded and the tensor is large, the chunks are issued stage
         by stage on streams of their own: NCCL executes the all-to-alls in issue order (chunk 0, chunk 1, ... of one
-        stage), while the FFT / Legendre kernels of a chunk run on its stream next to the other chunks' exchanges."""
+        stage), while the FFT / Legendre kernels of a chunk run on its stream next to the other chunks' exchanges.
+        Only grids with ONE distributed axis are pipelined: with two communicators the exchanges of different chunks would
+        sit on two NCCL streams whose relative order is not the same on every rank."""
         n = x.shape[0]
         gmax = max(self.comm_size_polar, self.comm_size_azimuth)
         nchunks = min(self.pipeline_chunks, n // max(gmax, 1))
-        if (gmax == 1 or nchunks < 2 or torch.is_grad_enabled() and x.requires_grad or not x.is_cuda
+        if (gmax == 1 or min(self.comm_size_polar, self.comm_size_azimuth) > 1 or nchunks < 2 or torch.is_grad_enabled() and x.requires_grad or not x.is_cuda
                 or x.numel() * x.element_size() < self.pipeline_min_bytes):
             for st in stages:
                 x = st(x, n)

@@ -136,8 +136,8 @@ int clear_empty_groups(const Plan &pl, float *Y, int ncols, int m0, int mloc, cu
     for (int g = 2 * m0; g < 2 * (m0 + mloc); ++g) {
         if (pl.group_kblocks[g] == 0) {
             const size_t ncp = (size_t)col_pitch(ncols);
-            // one row per latitude, a whole latitude (2 mloc rows) apart
-            SHT_CUDA_CHECK(cudaMemset2DAsync(Y + (size_t)y_row(g - 2 * m0, 0, 2 * mloc) * ncp, sizeof(float) * 2 * mloc * ncp, 0, sizeof(float) * ncp, (size_t)pl.Kh, st));
+            // the group's 64-byte pieces, one per (latitude, 16-column panel), lie a whole panel row (2 mloc pieces) apart
+            SHT_CUDA_CHECK(cudaMemset2DAsync(Y + y_off(g - 2 * m0, 0, 0, 2 * mloc, (long long)ncp), sizeof(float) * 16 * 2 * mloc, 0, sizeof(float) * 16, (size_t)pl.Kh * (ncp / 16), st));
         }
     }
     return SHTB200_OK;

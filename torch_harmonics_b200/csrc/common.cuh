@@ -85,7 +85,7 @@ constexpr int kItemRowsMax = 128;  // one 128-row tensor-core tile
 
 // How a finished tile leaves the contraction kernel.
 enum EpilogueMode : int {
-    EPI_LATROWS = 1,  // synthesis: rows are folded latitudes k'      -> float Y[y_row(group, k')][col] (row pitch ld)
+    EPI_LATROWS = 1,  // synthesis: rows are folded latitudes k'      -> float Y[y_off(group, k', col)] (out_ld = padded column count)
     EPI_SLABS = 2,    // analysis: rows are degrees -> float Z[(slab0[g] + r / 32) * ncols + col][r % 32], the same
                       // degree-slab layout the synthesis contraction reads its coefficients from
 };
@@ -109,7 +109,7 @@ struct GemmParams {
     int lmax, mmax_out;   // degrees; number of orders of the call (mloc)
     int m0;               // first order stored in out (orders outside [m0, m0 + mmax_out) are skipped)
     int m_base;           // first order the plan holds: slab0 is indexed by 2 (m - m_base) + p
-    long long out_ld;     // EPI_LATROWS: floats per row of Y
+    long long out_ld;     // EPI_LATROWS: padded column count of Y
     int out_groups;       // EPI_LATROWS: groups held in Y
     const long long *slab0;  // EPI_SLABS: first slab of every group (device array, 2 * mmax + 1 entries)
     long long slab_unit0;    // EPI_SLABS: slab0 of the first order held in the output
@@ -231,11 +231,14 @@ int launch_quadrature(const float *x, const float *w, float *out, long long nfie
 // 32 x columns tile the contraction loads per k-step is one contiguous piece.
 __host__ __device__ inline long long blocked_row(long long group, int k, int ngroups) { return (((long long)(k >> 5) * ngroups + group) << 5) + (k & 31); }
 
-// Row of (group, k') in the synthesis operand Y: latitude-major.  The synthesis FFT gathers, for one latitude, a 64-byte
-// piece of every group's row; with the rows of one latitude next to each other the CTAs that work on that latitude at the
-// same time (one per block of eight fields) read one contiguous region of HBM between them.  (Measured against the
-// 32-row blocking of X: the FFT kernel 5 % faster, the contraction's epilogue, which writes whole rows, unchanged.)
-__host__ __device__ inline long long y_row(long long group, int k, int ngroups) { return (long long)k * ngroups + group; }
+// Offset (floats) of element (group, k', column) of the synthesis operand Y, stored in panels of 16 columns (eight
+// fields): Y[k'][column / 16][group][column % 16], `ncp` = padded column count (a multiple of 32).  The synthesis FFT
+// works on one latitude pair of eight fields at a time and needs, of every group, exactly those 16 columns: with this order
+// its whole input is ONE contiguous region of ngroups x 64 bytes.  The contraction's epilogue produces 64-byte pieces
+// (16 columns of one latitude row) anyway, which it scatters into the panels.
+__host__ __device__ inline size_t y_off(long long group, int k, int col, int ngroups, long long ncp) {
+    return ((((size_t)k * (size_t)(ncp >> 4) + (size_t)(col >> 4)) * (size_t)ngroups + (size_t)group) << 4) + (size_t)(col & 15);
+}
 
 inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 // Row pitch (floats) of the column-contiguous operands: whole 128-byte lines, so that the 64-byte runs the FFT kernels

@@ -622,7 +622,7 @@ __global__ void __launch_bounds__(32 * NW * G, (NW * G >= 16) ? 2 : 1) fft_analy
 // ------------------------------------------------------------------------------------------------
 // synthesis kernel
 // ------------------------------------------------------------------------------------------------
-// Y[y_row(2 m + p, k')][col] (row pitch ncp) holds the even (p = 0) / odd (p = 1) latitude parts of order m;
+// Y[y_off(2 m + p, k', col)] (16-column panels, see y_off) holds the even (p = 0) / odd (p = 1) latitude parts of order m;
 // col = 2 f + (re, im) for scalar fields, 4 f + (theta re, theta im, phi re, phi im) for vector pairs: in both
 // cases transform u of the CTA reads columns 2 u, 2 u + 1 past the CTA's first column.
 template <int NW, int VEC, int G>
@@ -682,8 +682,8 @@ __global__ void __launch_bounds__(32 * NW * G, (NW * G >= 16) ? 2 : 1) fft_synth
                 if (m >= 0 && col < 2 * VEC * nfields) {
                     // (the contraction does not produce rows above the group's polar extent: they are zeros)
                     const int kf = kf_s ? kf_s[m] : 0;
-                    if (kn >= (kf & 15) * kBK) av[u] = __ldg(reinterpret_cast<const float4 *>(Y + (size_t)y_row(2 * m, kn, 2 * mmax) * ncp + col));
-                    if (kn >= (kf >> 4) * kBK) bv[u] = __ldg(reinterpret_cast<const float4 *>(Y + (size_t)y_row(2 * m + 1, kn, 2 * mmax) * ncp + col));
+                    if (kn >= (kf & 15) * kBK) av[u] = __ldg(reinterpret_cast<const float4 *>(Y + y_off(2 * m, kn, col, 2 * mmax, ncp)));
+                    if (kn >= (kf >> 4) * kBK) bv[u] = __ldg(reinterpret_cast<const float4 *>(Y + y_off(2 * m + 1, kn, col, 2 * mmax, ncp)));
                 }
             }
 #pragma unroll

@@ -308,9 +308,9 @@ __global__ void __launch_bounds__(TwoPass<R1, R2>::THREADS, 2) fft_synthesis_two
             const int mtop = min(a.mmax, N / 2 + 1);
             const float *ms_s = reinterpret_cast<const float *>(blob_s + sizeof(float2) * TP::NTW);
             const unsigned char *kf_s = reinterpret_cast<const unsigned char *>(ms_s + a.mpad);
-            // row of (group 0, kn) and the distance between the rows of consecutive groups
-            const float *yb = a.op + (size_t)y_row(0, kn, ngroups) * a.ncp + 2 * (f0 + t);
-            const size_t gstride = (size_t)(y_row(1, kn, ngroups) - y_row(0, kn, ngroups)) * a.ncp;
+            // this item's panel of Y (latitude kn, fields f0 .. f0 + 7): one contiguous region, 16 floats per group
+            const float *yb = a.op + y_off(0, kn, 2 * (f0 + t), ngroups, a.ncp);
+            const size_t gstride = 16;
             // the loads of CH orders are issued before the first of them is used
 #pragma unroll
             for (int r = 0; r < R2; ++r) u[r] = make_float2(0.f, 0.f);

@@ -94,7 +94,7 @@ __global__ void __launch_bounds__(256) legendre_simt_kernel(GemmParams gp) {
             for (int j = 0; j < 4; ++j) {
                 const int c = col0 + tx * 4 + j;
                 if (c >= gp.ncols) continue;
-                gp.out[(size_t)y_row(g, rg, gp.out_groups) * gp.out_ld + c] = acc[i][j];
+                gp.out[y_off(g, rg, c, gp.out_groups, gp.out_ld)] = acc[i][j];
             }
         }
     }

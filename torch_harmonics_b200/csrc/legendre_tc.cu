@@ -347,7 +347,7 @@ legendre_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                     for (int k = 0; k < 4; ++k) {
                         const int rr = (q * 32 + (lane & ~3) + k);  // row inside the tile
                         if (rr < w.it.rows && colq < gp.ncols)  // (columns past the last field pad the row pitch: nobody reads them)
-                            *reinterpret_cast<float4 *>(gp.out + (size_t)y_row(g, w.it.r0 + rr, gp.out_groups) * gp.out_ld + colq) =
+                            *reinterpret_cast<float4 *>(gp.out + y_off(g, w.it.r0 + rr, colq, gp.out_groups, gp.out_ld)) =
                                 make_float4(v[4 * k], v[4 * k + 1], v[4 * k + 2], v[4 * k + 3]);
                     }
                     continue;

@@ -398,7 +398,7 @@ __global__ void fold_modes_vec_kernel(const float2 *__restrict__ Xc, float *__re
     }
 }
 
-// Y[y_row(2 mi + p, k')][2 f + ri] -> Xc (field, k, mloc) complex, the same tiling the other way round
+// Y[y_off(2 mi + p, k', 2 f + ri)] -> Xc (field, k, mloc) complex, the same tiling the other way round
 // (rows above krow0[2 (m0 + mi) + p] were not produced by the contraction: they count as zeros; m0 here = first order of
 // the call relative to the plan's first order)
 __global__ void __launch_bounds__(256) unfold_modes_kernel(const float *__restrict__ Y, float2 *__restrict__ Xc, int nfields, int nlat, int Kh, int ncp, int mloc,
@@ -413,8 +413,8 @@ __global__ void __launch_bounds__(256) unfold_modes_kernel(const float *__restri
             const int mi = mi0 + ty + 8 * i;
             float2 e = make_float2(0.f, 0.f), o = e;
             if (f < nfields && mi < mloc) {
-                if (k >= krow0[2 * (m0 + mi)]) e = __ldg(reinterpret_cast<const float2 *>(Y + (size_t)y_row(2 * mi, k, 2 * mloc) * ncp + 2 * f));
-                if (k >= krow0[2 * (m0 + mi) + 1]) o = __ldg(reinterpret_cast<const float2 *>(Y + (size_t)y_row(2 * mi + 1, k, 2 * mloc) * ncp + 2 * f));
+                if (k >= krow0[2 * (m0 + mi)]) e = __ldg(reinterpret_cast<const float2 *>(Y + y_off(2 * mi, k, 2 * f, 2 * mloc, ncp)));
+                if (k >= krow0[2 * (m0 + mi) + 1]) o = __ldg(reinterpret_cast<const float2 *>(Y + y_off(2 * mi + 1, k, 2 * f, 2 * mloc, ncp)));
             }
             E[ty + 8 * i][tx] = e;
             O[ty + 8 * i][tx] = o;

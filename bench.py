@@ -191,8 +191,8 @@ def kernel_bytes(nf, table_fwd_bytes, table_inv_bytes, slabs):
 # The FFT and transpose kernels only stream per-field data; the Legendre kernels also read the packed table once per
 # launch, so their figure holds for the captured field count only.
 NCU_TRAFFIC = {
-    "fft_analysis": (132.96e6 + 64.42e6, 32, True, "fft_kernels_32fields"),
-    "fft_synthesis": (98.66e6 + 87.81e6, 32, True, "fft_kernels_32fields"),
+    "fft_analysis": (133.01e6 + 58.22e6, 32, True, "fft_twopass_kernels_32fields"),
+    "fft_synthesis": (98.70e6 + 83.60e6, 32, True, "fft_twopass_kernels_32fields"),
     "pack_coeffs": (67.86e6 + 26.12e6, 32, True, "coeff_slab_transpose_32fields"),
     "unpack_coeffs": (72.31e6 + 78.94e6, 32, True, "coeff_slab_transpose_32fields"),
     "legendre_analysis": (611.80e6 + 135.90e6, 73, False, "legendre_tc_kernel_73fields"),
@@ -649,7 +649,9 @@ def run_ours(args):
         module_step()
     t_mod, _ = timed_blocks(module_step, args.steps, barrier, 0.2, agree=maxr)
 
-    # end to end through the host-buffer entry point (pinned host memory, copies inside the timed region)
+    # end to end through the host-buffer entry point (pinned host memory, copies inside the timed region); this rank's
+    # thread runs on (and first-touches the pinned pages from) the CPUs NVML reports as local to its GPU
+    host_cpus, numa = bind_near_gpu(dev)
     xh = x.cpu().pin_memory()
     ch = torch.empty(nf, LMAX, MMAX, dtype=torch.complex64).pin_memory()
     xh2 = torch.empty(nf, NLAT, NLON).pin_memory()
@@ -683,6 +685,8 @@ def run_ours(args):
     copy_step()
     t_copy, _ = timed_blocks(copy_step, e2e_steps, barrier, 0.0, agree=maxr)
     del xd, cd
+    if host_cpus:
+        os.sched_setaffinity(0, host_cpus)
 
     t_step, t_fwd, t_inv, t_e2e, t_mod, t_copy_max = maxr(t_step), maxr(t_fwd), maxr(t_inv), maxr(t_e2e), maxr(t_mod), maxr(t_copy)
     xb, cb = x.numel() * 4, c.numel() * 8
@@ -765,6 +769,7 @@ def run_ours(args):
                 "value": nf * world * e2e_steps / t_e2e, "unit": "fields/s",
                 "h2d_bytes_per_step": xb + cb, "d2h_bytes_per_step": cb + xb, "steps": e2e_steps,
                 "h2d_gbs_per_rank": (xb + cb) * e2e_steps / t_e2e / 1e9, "d2h_gbs_per_rank": (xb + cb) * e2e_steps / t_e2e / 1e9,
+                "host_binding": numa,
                 "copies_only": {
                     "fields_per_s": nf * world * e2e_steps / t_copy_max, "gbs_per_direction_per_rank": (xb + cb) * e2e_steps / t_copy_max / 1e9,
                     "note": "the step's host<->device copies alone (both directions at once, no kernels), all ranks at the same time: the host-side ceiling of e2e on this box",
@@ -783,6 +788,33 @@ def run_ours(args):
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def bind_near_gpu(dev):
+    """Restrict this process to the CPUs NVML lists as local to `dev` (a query; nothing on the GPU changes).
+
+    Returns (the previous CPU set or None, a record for the bench line).  Pinned buffers allocated afterwards are first
+    touched from those CPUs, so they land on the GPU's NUMA node when the kernel's default policy applies."""
+    try:
+        import pynvml
+
+        pynvml.nvmlInit()
+        idx = dev.index if dev.index is not None else torch.cuda.current_device()
+        try:  # by UUID: NVML's index order need not be CUDA's
+            h = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + str(torch.cuda.get_device_properties(idx).uuid)).encode())
+        except Exception:
+            h = pynvml.nvmlDeviceGetHandleByIndex(idx)
+        words = -(-(os.cpu_count() or 1) // 64)
+        mask = pynvml.nvmlDeviceGetCpuAffinity(h, max(words, 1))
+        near = {64 * w + b for w, v in enumerate(mask) for b in range(64) if (int(v) >> b) & 1}
+        before = os.sched_getaffinity(0)
+        use = near & before
+        if not use:
+            return None, {"bound": False, "why": "no CPU local to the GPU is in this process's CPU set", "cpus_allowed": len(before)}
+        os.sched_setaffinity(0, use)
+        return before, {"bound": True, "cpus_local_to_gpu": len(near), "cpus_used": len(use), "cpus_allowed": len(before)}
+    except Exception as e:  # no NVML, or affinity not permitted: run unbound and say so
+        return None, {"bound": False, "why": repr(e)[:120]}
 
 
 def cpu_baseline(nfields, steps, warmup=1):

@@ -59,6 +59,47 @@ def _worker(rank, world, port, which):
             assert torch.equal(local.grad, local.detach())
 
     thd.config.debug = False
+
+    # copy-to-region / reduce-from-region: conjugate pairs (identity one way, sum over the group the other way); the group
+    # that is not distributed leaves values and gradients alone (torch-harmonics tests/test_distributed_primitives.py)
+    copy_here, reduce_here = (thd.copy_to_azimuth_region, thd.reduce_from_azimuth_region) if which == "azimuth" else (thd.copy_to_polar_region, thd.reduce_from_polar_region)
+    copy_other, reduce_other = (thd.copy_to_polar_region, thd.reduce_from_polar_region) if which == "azimuth" else (thd.copy_to_azimuth_region, thd.reduce_from_azimuth_region)
+    for dtype in (torch.float32, torch.complex64, torch.bfloat16):
+        base = torch.arange(6, dtype=torch.float32).reshape(2, 3) + 1
+        v = (base * (rank + 1)).to(dtype)
+        if dtype.is_complex:
+            v = v * (1 + 2j)
+        total = sum((base * (r + 1)) for r in range(world)).to(dtype) * ((1 + 2j) if dtype.is_complex else 1)
+        a = v.clone().requires_grad_(True)
+        out = reduce_here(a)
+        assert torch.equal(out.detach(), total) and torch.equal(a.detach(), v)  # the input is not written
+        out.backward(torch.ones_like(out) * (rank + 2))
+        assert torch.equal(a.grad, torch.ones_like(v) * (rank + 2))
+        b = v.clone().requires_grad_(True)
+        out = copy_here(b)
+        assert torch.equal(out.detach(), v)
+        out.backward(v.detach().clone())
+        assert torch.equal(b.grad, total)
+        c = v.clone().requires_grad_(True)
+        out = reduce_other(copy_other(c))
+        out.backward(torch.ones_like(out))
+        assert torch.equal(out.detach(), v) and torch.equal(c.grad, torch.ones_like(v))
+
+    # the distributed quadrature holds this rank's tile of the serial module's weights
+    import torch_harmonics_b200 as th
+
+    for grid, shape in (("equiangular", (33, 64)), ("legendre-gauss", (32, 64)), ("lobatto", (17, 30))):
+        for normalize in (False, True):
+            qs = th.QuadratureS2(shape, grid=grid, normalize=normalize)
+            qd = thd.DistributedQuadratureS2(shape, grid=grid, normalize=normalize)
+            full = qs.quad_weight
+            tile = thd.split_tensor_along_dim(full, -1 if which == "azimuth" else -2, world)[rank]
+            assert qd.quad_weight.shape == tile.shape and torch.equal(qd.quad_weight, tile)
+    with pytest.raises(ValueError):
+        thd.DistributedQuadratureS2((8, 16), grid="nonsense")
+    with pytest.raises(RuntimeError):
+        thd.DistributedQuadratureS2((8, 16))(torch.zeros(1, 8, 16))  # no CPU path
+
     with pytest.raises(RuntimeError):
         thd.compute_split_shapes(1, 2)
     thd.finalize()

@@ -244,7 +244,9 @@ def _dist_worker(rank, world, port, gh, gw):
         c_pipe = dsht(xl)
         y_pipe = disht(c_pipe)
     torch.cuda.synchronize()
-    ep = max(float((c_pipe - c_plain).abs().max() / c_plain.abs().max()), float((y_pipe - y_plain).abs().max() / y_plain.abs().max()))
+    # (a rank's tile of coefficients can lie entirely above the diagonal l >= m and be all zeros)
+    ep = max(float((c_pipe - c_plain).abs().max() / c_plain.abs().max().clamp_min(1e-30)),
+             float((y_pipe - y_plain).abs().max() / y_plain.abs().max().clamp_min(1e-30)))
     if not ep <= 2e-6:
         ok = False
         msgs.append(f"rank {rank}: pipelined inference path differs from the plain path by {ep:.2e}")
@@ -295,6 +297,82 @@ def _cfg5_worker(rank, world, port, gh, gw):
     _finish(ok, msgs)
 
 
+# (in_shape, out_shape, batch, channels, groups, grid_in, grid_out, bias): torch-harmonics
+# tests/test_distributed_spectral_convolution.py:92-121 (incl. fewer channels than the polar group), plus a grouped case
+SPECTRAL_CONV_CASES = [
+    ((64, 128), (64, 128), 4, 8, 1, "equiangular", "equiangular", False),
+    ((65, 128), (65, 128), 4, 8, 1, "equiangular", "equiangular", False),
+    ((64, 128), (32, 64), 4, 8, 1, "equiangular", "equiangular", False),
+    ((65, 128), (33, 64), 4, 8, 1, "equiangular", "equiangular", False),
+    ((33, 64), (65, 128), 4, 8, 1, "equiangular", "equiangular", False),
+    ((64, 128), (64, 128), 4, 8, 1, "equiangular", "legendre-gauss", False),
+    ((64, 128), (64, 128), 1, 1, 1, "equiangular", "equiangular", False),
+    ((64, 128), (64, 128), 1, 2, 1, "equiangular", "legendre-gauss", False),
+    ((64, 128), (64, 128), 4, 8, 1, "equiangular", "equiangular", True),
+    ((65, 128), (33, 64), 4, 8, 1, "equiangular", "equiangular", True),
+    ((33, 64), (65, 128), 4, 8, 1, "equiangular", "equiangular", True),
+    ((65, 128), (65, 128), 4, 8, 1, "equiangular", "legendre-gauss", True),
+    ((64, 128), (64, 128), 1, 2, 1, "equiangular", "equiangular", True),
+    ((64, 128), (32, 64), 2, 8, 2, "legendre-gauss", "equiangular", True),
+]
+
+
+def _spectral_conv_worker(rank, world, port, gh, gw):
+    """DistributedSpectralConvS2 and DistributedQuadratureS2 against the serial modules with the same (seeded) parameters:
+    output tile, input-gradient tile, and the weight / bias gradients (a rank's weight gradient covers its own orders only,
+    so it is summed over the azimuth group before the comparison, as training code has to)."""
+    import torch
+    import torch.distributed as dist
+
+    import torch_harmonics_b200 as th
+    import torch_harmonics_b200.distributed as thd
+
+    rh, rw = _init_grid(rank, world, port, gh, gw)
+    ok, msgs = True, []
+
+    def rel(a, b):
+        return float((a - b).abs().max()) / max(float(b.abs().max()), 1e-30)
+
+    for in_shape, out_shape, B, C, G, grid_in, grid_out, bias in SPECTRAL_CONV_CASES:
+        torch.manual_seed(333)  # same parameters and data on every rank
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore")
+            serial = th.SpectralConvS2(in_shape, out_shape, C, C, num_groups=G, grid_in=grid_in, grid_out=grid_out, bias=bias).cuda()
+            if serial.lmax < gh or serial.mmax < gw:
+                continue
+            local = thd.DistributedSpectralConvS2(in_shape, out_shape, C, C, num_groups=G, grid_in=grid_in, grid_out=grid_out, bias=bias).cuda()
+        l0, m0 = sum(local.l_shapes[:rh]), sum(local.m_shapes[:rw])
+        with torch.no_grad():
+            local.weight.copy_(serial.weight[..., l0:l0 + local.lmax_local])
+            if bias:
+                serial.spectral_bias.copy_(torch.randn(serial.spectral_bias.shape, dtype=torch.complex64, device="cuda"))
+                local.spectral_bias.copy_(serial.spectral_bias[..., l0:l0 + local.lmax_local, m0:m0 + local.mmax_local])
+        x = torch.randn(B, C, *in_shape, device="cuda")
+        xs = x.clone().requires_grad_(True)
+        ys = serial(xs)
+        gy = torch.randn_like(ys)
+        ys.backward(gy)
+        xl = _tile(x, -2, -1, gh, gw, rh, rw).clone().requires_grad_(True)
+        yl = local(xl)
+        yl.backward(_tile(gy, -2, -1, gh, gw, rh, rw).contiguous())
+        errs = {"out": rel(yl.detach(), _tile(ys.detach(), -2, -1, gh, gw, rh, rw)), "gx": rel(xl.grad, _tile(xs.grad, -2, -1, gh, gw, rh, rw))}
+        gw_loc = torch.view_as_real(local.weight.grad.contiguous()).clone()
+        if gw > 1:
+            dist.all_reduce(gw_loc, group=thd.azimuth_group())
+        errs["gweight"] = rel(torch.view_as_complex(gw_loc), serial.weight.grad[..., l0:l0 + local.lmax_local])
+        if bias:
+            errs["gbias"] = rel(local.spectral_bias.grad, serial.spectral_bias.grad[..., l0:l0 + local.lmax_local, m0:m0 + local.mmax_local])
+            q_s = th.QuadratureS2(in_shape, grid=grid_in, normalize=True).cuda()(x)
+            q_l = thd.DistributedQuadratureS2(in_shape, grid=grid_in, normalize=True).cuda()(xl.detach())
+            errs["quadrature"] = float((q_l - q_s).abs().max()) / max(float(q_s.abs().max()), 1e-30)
+        if max(errs.values()) > TOL:
+            ok = False
+            msgs.append(f"rank {rank} {in_shape}->{out_shape} B={B} C={C} G={G} {grid_in}/{grid_out} bias={bias}: " + " ".join(f"{k} {v:.2e}" for k, v in errs.items()))
+    if rank == 0:
+        print(f"distributed spectral convolution / quadrature {gh}x{gw}: {len(SPECTRAL_CONV_CASES)} cases, ok={ok}", flush=True)
+    _finish(ok, msgs)
+
+
 GRIDS = [(1, 2), (2, 1), (2, 2), (2, 4), (4, 2)]
 
 
@@ -306,6 +384,16 @@ def test_multi_gpu_equals_serial(gh, gw):
     if torch.cuda.device_count() < gh * gw:
         pytest.skip(f"needs {gh * gw} GPUs")
     mp.spawn(_dist_worker, args=(gh * gw, _free_port(), gh, gw), nprocs=gh * gw, join=True)
+
+
+@pytest.mark.parametrize("gh,gw", [(1, 2), (2, 1), (2, 2), (2, 4)])
+def test_multi_gpu_spectral_conv_equals_serial(gh, gw):
+    import torch
+    import torch.multiprocessing as mp
+
+    if torch.cuda.device_count() < gh * gw:
+        pytest.skip(f"needs {gh * gw} GPUs")
+    mp.spawn(_spectral_conv_worker, args=(gh * gw, _free_port(), gh, gw), nprocs=gh * gw, join=True)
 
 
 @pytest.mark.parametrize("gh,gw", [(1, 2), (2, 2), (2, 4)])

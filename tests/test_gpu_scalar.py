@@ -216,7 +216,10 @@ def test_stage_entry_points(engine):
 
     lib = _lib.load()
     rng = np.random.default_rng(11)
-    for nlon, nmodes, nrows in ((64, 33, 37), (30, 12, 5), (25, 13, 8), (16, 12, 3)):
+    # (the last six take the two-pass row kernels: full and ragged items of 16 rows, odd row counts, fewer and more
+    # modes than nlon / 2 + 1)
+    for nlon, nmodes, nrows in ((64, 33, 37), (30, 12, 5), (25, 13, 8), (16, 12, 3), (1440, 720, 48), (1440, 721, 37), (1440, 100, 1),
+                                (720, 361, 16), (720, 400, 21), (512, 257, 50), (512, 96, 15)):
         x = rng.standard_normal((nrows, nlon)).astype(np.float32)
         xd = torch.from_numpy(x).cuda()
         out = torch.empty((nrows, nmodes), dtype=torch.complex64, device="cuda")
@@ -231,6 +234,19 @@ def test_stage_entry_points(engine):
         assert rc == 0
         torch.cuda.synchronize()
         assert err(y.cpu().numpy(), orc.irfft_modes(c.astype(np.complex128), nlon)) <= TOL
+
+    # rows that are not 16-byte aligned take the general kernels
+    nlon, nmodes, nrows = 720, 300, 9
+    x = rng.standard_normal((nrows * nlon + 1,)).astype(np.float32)
+    xd = torch.from_numpy(x).cuda()[1:].view(nrows, nlon)
+    out = torch.empty((nrows, nmodes), dtype=torch.complex64, device="cuda")
+    assert lib.shtb200_rfft_modes(ctypes.c_void_p(xd.data_ptr()), ctypes.c_void_p(out.data_ptr()), nrows, nlon, nmodes, 1.0, None) == 0
+    torch.cuda.synchronize()
+    assert err(out.cpu().numpy(), orc.rfft_modes(x[1:].reshape(nrows, nlon).astype(np.float64), nmodes)) <= TOL
+    yd = torch.empty((nrows * nlon + 1,), dtype=torch.float32, device="cuda")[1:].view(nrows, nlon)
+    assert lib.shtb200_irfft_modes(ctypes.c_void_p(out.data_ptr()), ctypes.c_void_p(yd.data_ptr()), nrows, nlon, nmodes, None) == 0
+    torch.cuda.synchronize()
+    assert err(yd.cpu().numpy(), orc.irfft_modes(out.cpu().numpy().astype(np.complex128), nlon)) <= TOL
 
     nlat, nlon, grid = 33, 64, "equiangular"
     w, p, L, M = oracle_tables(nlat, nlon, 20, 20, grid)

@@ -201,6 +201,14 @@ bool twopass_supported(int nlon, int *r1, int *r2);
 int build_twopass_tables(Plan &pl, const std::vector<float> &mscale);
 int launch_fft_analysis_twopass(const Plan &pl, const float *x, float *X, int nfields, cudaStream_t st);
 int launch_fft_synthesis_twopass(const Plan &pl, const float *Y, float *x, int nfields, cudaStream_t st);
+// the same kernels as plain batched row transforms (stage entry points, no plan)
+struct TwoPassRows {
+    const unsigned char *blob = nullptr;  // pass twiddles (build_twopass_rows_tables)
+    int blob_bytes = 0, sm_count = 0;
+    int *d_err = nullptr;  // device error word for bounded waits that ran out
+};
+int build_twopass_rows_tables(int nlon, unsigned char **d_blob, int *bytes);
+int launch_rows_twopass(const TwoPassRows &tr, bool forward, const void *in, void *out, long long nrows, int nlon, int nmodes, float scale, cudaStream_t st);
 // plain row transforms for the distributed stages
 int launch_rfft_modes(const float *in, float2 *out, long long nrows, int nlon, int nmodes, float scale, cudaStream_t st);
 int launch_irfft_modes(const float2 *in, float *out, long long nrows, int nlon, int nmodes, cudaStream_t st);

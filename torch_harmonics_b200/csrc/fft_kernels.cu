@@ -906,36 +906,79 @@ struct CachedFft {
     FftPlanDev fp{};
     float2 *tw = nullptr;
     unsigned short *perm = nullptr;
+    TwoPassRows rows;        // two-pass kernels' tables (blob == nullptr: no such kernel for this nlon)
+    int *h_err = nullptr;    // pinned copy of rows.d_err, refreshed after every launch and looked at by the next call
 };
 static std::mutex g_cache_mutex;
 static std::vector<CachedFft> g_cache;
 
 // Tables for `nlon` on the CURRENT device (the stage calls run on the caller's current device and stream).
-static int cached_fft(int nlon, FftPlanDev *fp) {
+static int cached_fft(int nlon, FftPlanDev *fp, TwoPassRows *rows, int **h_err) {
     int dev = 0;
     SHT_CUDA_CHECK(cudaGetDevice(&dev));
     std::lock_guard<std::mutex> lock(g_cache_mutex);
     for (const CachedFft &c : g_cache)
-        if (c.n == nlon && c.device == dev) { *fp = c.fp; return SHTB200_OK; }
+        if (c.n == nlon && c.device == dev) {
+            *fp = c.fp;
+            *rows = c.rows;
+            *h_err = c.h_err;
+            return SHTB200_OK;
+        }
     CachedFft c;
     int rc = build_fft_plan(nlon, 0, kFftRows, nullptr, &c.fp, &c.tw, &c.perm);
     if (rc) return rc;
+    unsigned char *blob = nullptr;
+    if ((rc = build_twopass_rows_tables(nlon, &blob, &c.rows.blob_bytes)) != 0) return rc;
+    if (blob) {
+        c.rows.blob = blob;
+        SHT_CUDA_CHECK(cudaDeviceGetAttribute(&c.rows.sm_count, cudaDevAttrMultiProcessorCount, dev));
+        SHT_CUDA_CHECK(cudaMalloc(&c.rows.d_err, sizeof(int)));
+        SHT_CUDA_CHECK(cudaMemset(c.rows.d_err, 0, sizeof(int)));
+        SHT_CUDA_CHECK(cudaHostAlloc(&c.h_err, sizeof(int), cudaHostAllocDefault));
+        *c.h_err = 0;
+    }
     c.n = nlon;
     c.device = dev;
     g_cache.push_back(c);
     *fp = c.fp;
+    *rows = c.rows;
+    *h_err = c.h_err;
+    return SHTB200_OK;
+}
+
+// Two-pass row transforms when there is a kernel for nlon and the rows are 16-byte aligned; *done says whether it ran.
+// A bounded wait that ran out inside an earlier launch shows in the pinned copy of the error word: the next call fails.
+static int rows_twopass(const TwoPassRows &rows, int *h_err, bool forward, const void *in, void *out, long long nrows, int nlon, int nmodes, float scale,
+                        cudaStream_t st, bool *done) {
+    *done = false;
+    const void *grid = forward ? in : out;
+    if (!rows.blob || ((uintptr_t)grid & 15) != 0) return SHTB200_OK;
+    if (*reinterpret_cast<volatile int *>(h_err) != 0) {
+        const int v = *h_err;
+        *h_err = 0;
+        cudaMemsetAsync(rows.d_err, 0, sizeof(int), st);
+        return fail(SHTB200_EDEVICE, "a row-transform kernel gave up on a bounded wait (device error word " + std::to_string(v) + ")");
+    }
+    int rc = launch_rows_twopass(rows, forward, in, out, nrows, nlon, nmodes, scale, st);
+    if (rc) return rc;
+    SHT_CUDA_CHECK(cudaMemcpyAsync(h_err, rows.d_err, sizeof(int), cudaMemcpyDeviceToHost, st));
+    *done = true;
     return SHTB200_OK;
 }
 
 int launch_rfft_modes(const float *in, float2 *out, long long nrows, int nlon, int nmodes, float scale, cudaStream_t st) {
     FftPlanDev fp;
-    int rc = cached_fft(nlon, &fp);
+    TwoPassRows rows;
+    int *h_err = nullptr;
+    int rc = cached_fft(nlon, &fp, &rows, &h_err);
     if (rc) return rc;
+    if (nrows == 0) return SHTB200_OK;
+    bool done = false;
+    if ((rc = rows_twopass(rows, h_err, true, in, out, nrows, nlon, nmodes, scale / (float)nlon, st, &done)) != 0 || done) return rc;
     constexpr int NW = 4;
     size_t smem = fft_smem_bytes(NW, fp);
     if ((rc = set_smem(rfft_rows_kernel<NW>, smem)) != 0) return rc;
     long long blocks = (nrows + 2 * NW - 1) / (2 * NW);
-    if (blocks == 0) return SHTB200_OK;
     rfft_rows_kernel<NW><<<(unsigned)blocks, 32 * NW, smem, st>>>(in, out, fp, nrows, nmodes, scale / (float)nlon);  // rfft(norm="forward") carries 1/nlon
     SHT_CUDA_CHECK(cudaGetLastError());
     return SHTB200_OK;
@@ -943,13 +986,17 @@ int launch_rfft_modes(const float *in, float2 *out, long long nrows, int nlon, i
 
 int launch_irfft_modes(const float2 *in, float *out, long long nrows, int nlon, int nmodes, cudaStream_t st) {
     FftPlanDev fp;
-    int rc = cached_fft(nlon, &fp);
+    TwoPassRows rows;
+    int *h_err = nullptr;
+    int rc = cached_fft(nlon, &fp, &rows, &h_err);
     if (rc) return rc;
+    if (nrows == 0) return SHTB200_OK;
+    bool done = false;
+    if ((rc = rows_twopass(rows, h_err, false, in, out, nrows, nlon, nmodes, 1.f, st, &done)) != 0 || done) return rc;
     constexpr int NW = 4;
     size_t smem = fft_smem_bytes(NW, fp);
     if ((rc = set_smem(irfft_rows_kernel<NW>, smem)) != 0) return rc;
     long long blocks = (nrows + 2 * NW - 1) / (2 * NW);
-    if (blocks == 0) return SHTB200_OK;
     irfft_rows_kernel<NW><<<(unsigned)blocks, 32 * NW, smem, st>>>(in, out, fp, nrows, nmodes);
     SHT_CUDA_CHECK(cudaGetLastError());
     return SHTB200_OK;

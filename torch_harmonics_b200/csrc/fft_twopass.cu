@@ -91,7 +91,20 @@ struct TwoPassArgs {
     int nlat, Kh, nfields, ncp, mmax, zero_imag_edges;
     int kpad;               // analysis: zero rows appended to the operand (contraction length rounded up to 32)
     int *err;
+    // ROWS kernels (plain batched rfft / irfft of `nrows` rows, an item = 16 consecutive rows = 8 transforms of
+    // row 2 t + i row (2 t + 1)): spectra (nrows, nmodes) complex, `scale` multiplies the forward spectra
+    const float2 *rows_in;
+    float2 *rows_out;
+    long long nrows;
+    int nmodes;
+    float scale;
 };
+
+// ROWS: transforms of item `it` that have at least one row
+__device__ __forceinline__ int rows_nvalid(long long nrows, int it) {
+    const long long left = nrows - 16LL * it;
+    return left >= 16 ? kNT : (int)((left + 1) >> 1);
+}
 
 // item -> (latitude pair, first field): full field blocks first (k' slowest), the ragged last block at the end, so that
 // the CTAs' last round is made of the light items
@@ -118,7 +131,9 @@ __device__ __forceinline__ void decode_item(int it, int Kh, int nfields, int *kn
 // carry the sign pattern of torch_harmonics/sht.py:488-493:
 //     rows k'     : ( Re X0,  Im X0, -Re X1, -Im X1)        rows Kh + k' : (-Im X1,  Re X1, -Im X0,  Re X0)
 // (X0 = theta component, X1 = phi component): every thread still writes 8-byte pieces of its own transform only.
-template <int R1, int R2, int VEC>
+// ROWS: the same two passes as a plain batched rfft (distributed stage, torch_harmonics/distributed/distributed_sht.py:197):
+// the emit writes the two rows' spectra A and B instead of their folds.
+template <int R1, int R2, int VEC, bool ROWS>
 __global__ void __launch_bounds__(TwoPass<R1, R2>::THREADS, 2) fft_analysis_twopass_kernel(const TwoPassArgs a) {
     using TP = TwoPass<R1, R2>;
     constexpr int N = TP::N, TS = TP::TS, TS2 = TP::TS / 2;
@@ -126,7 +141,7 @@ __global__ void __launch_bounds__(TwoPass<R1, R2>::THREADS, 2) fft_analysis_twop
     unsigned char *blob_s = reinterpret_cast<unsigned char *>(smem_tp + kNT * TS);
     const uint32_t bar_tab = ptx::smem_u32(blob_s + a.blob_bytes), bar_rows = bar_tab + 8;
     const int nfb = (a.nfields + kNT - 1) / kNT;
-    const int nitems = a.Kh * nfb;
+    const int nitems = ROWS ? (int)((a.nrows + 15) >> 4) : a.Kh * nfb;
 
     // rows of the last 32-row block beyond the contraction length: the contraction reads them, they must be zeros
     for (int z = blockIdx.x; z < a.kpad * nfb; z += gridDim.x) {
@@ -139,6 +154,14 @@ __global__ void __launch_bounds__(TwoPass<R1, R2>::THREADS, 2) fft_analysis_twop
     if ((int)blockIdx.x >= nitems) return;
 
     auto issue_rows = [&](int it) {  // thread 0: the rows of item `it` (row k' -> real array, its mirror -> imaginary array)
+        if (ROWS) {
+            const long long r0 = 16LL * it;
+            const int nr = (int)min(16LL, a.nrows - r0);
+            ptx::mbar_arrive_expect_tx(bar_rows, N * 4u * (uint32_t)nr);
+            for (int u = 0; u < nr; ++u)
+                ptx::bulk_load(ptx::smem_u32(smem_tp + (u >> 1) * TS + (u & 1) * N), a.grid_in + (size_t)(r0 + u) * N, N * 4u, bar_rows);
+            return;
+        }
         int kn, f0, nvalid;
         decode_item(it, a.Kh, a.nfields, &kn, &f0, &nvalid);
         const int ks = a.nlat - 1 - kn;
@@ -164,13 +187,19 @@ __global__ void __launch_bounds__(TwoPass<R1, R2>::THREADS, 2) fft_analysis_twop
     for (int it = blockIdx.x; it < nitems; it += gridDim.x) {
         if (!cta_wait(bar_rows, phase, a.err, 0x0F7F0012)) return;
         phase ^= 1u;
+        if (ROWS && 16LL * it + 16 > a.nrows && (a.nrows & 1)) {  // odd row count: the last transform's second row is zeros
+            float *im = smem_tp + (rows_nvalid(a.nrows, it) - 1) * TS + N;
+            for (int i = threadIdx.x; i < N; i += blockDim.x) im[i] = 0.f;
+            __syncthreads();
+        }
 
         // ---- pass 1: R2 butterflies of radix R1 per transform (lane = 8 slot + transform, butterfly j = 4 warp + slot) ----
         {
             const int tid = tid_now();
             const int t = tid & 7, j = 4 * (tid >> 5) + ((tid >> 3) & 3);
             int kn, f0, nvalid;
-            decode_item(it, a.Kh, a.nfields, &kn, &f0, &nvalid);
+            if (ROWS) nvalid = rows_nvalid(a.nrows, it);
+            else decode_item(it, a.Kh, a.nfields, &kn, &f0, &nvalid);
             const bool work = t < nvalid && j < R2;
             float2 v[R1];
             {
@@ -207,8 +236,35 @@ __global__ void __launch_bounds__(TwoPass<R1, R2>::THREADS, 2) fft_analysis_twop
         if (tid_now() == 0 && it + (int)gridDim.x < nitems) issue_rows(it + gridDim.x);  // lands while this item is emitted
         Dft<R2, false>::run(u);
 
-        // ---- emit: bins q + R1 i, i <= R2 / 2, are the retained orders; their mirrors come from the partner lane ----
-        {
+        if (ROWS) {
+            // ---- emit: spectra of the two real rows packed in z = row a + i row b: A = (z_m + conj z_{n-m}) / 2,
+            // B = (z_m - conj z_{n-m}) / (2 i) ----
+            const int tid = tid_now();
+            const int t = tid & 7, q = q_of<R1>(tid >> 5, (tid >> 3) & 3);
+            const long long ra = 16LL * it + 2 * t;
+            const bool va = ra < a.nrows, vb = ra + 1 < a.nrows;
+            const int mtop = min(a.nmodes, N / 2 + 1);
+            float2 *oa = a.rows_out + (size_t)ra * a.nmodes, *ob = oa + a.nmodes;
+            const float sc = 0.5f * a.scale;
+#pragma unroll
+            for (int i = 0; i <= R2 / 2; ++i) {
+                const int m = q + R1 * i;
+                const float2 give = u[R2 - 1 - i];
+                float2 got;
+                got.x = __shfl_xor_sync(0xffffffffu, give.x, 16);
+                got.y = __shfl_xor_sync(0xffffffffu, give.y, 16);
+                if (m >= mtop) continue;
+                const float2 zm = u[i];
+                const float2 zn = (q == 0) ? u[(R2 - i) % R2] : (q == R1 / 2) ? give : got;
+                if (va) oa[m] = make_float2(sc * (zm.x + zn.x), sc * (zm.y - zn.y));
+                if (vb) ob[m] = make_float2(sc * (zm.y + zn.y), sc * (zn.x - zm.x));
+            }
+            for (int m = mtop + (tid >> 3); m < a.nmodes; m += TP::THREADS >> 3) {  // beyond the Nyquist frequency: zeros
+                if (va) oa[m] = make_float2(0.f, 0.f);
+                if (vb) ob[m] = make_float2(0.f, 0.f);
+            }
+        } else {
+            // ---- emit: bins q + R1 i, i <= R2 / 2, are the retained orders; their mirrors come from the partner lane ----
             const int tid = tid_now();
             const int t = tid & 7, q = q_of<R1>(tid >> 5, (tid >> 3) & 3);
             int kn, f0, nvalid;
@@ -275,7 +331,8 @@ __global__ void __launch_bounds__(TwoPass<R1, R2>::THREADS, 2) fft_analysis_twop
     }
 }
 
-template <int R1, int R2>
+// ROWS: plain batched irfft of (nrows, nmodes) spectra (distributed stage, torch_harmonics/distributed/distributed_sht.py:385).
+template <int R1, int R2, bool ROWS>
 __global__ void __launch_bounds__(TwoPass<R1, R2>::THREADS, 2) fft_synthesis_twopass_kernel(const TwoPassArgs a) {
     using TP = TwoPass<R1, R2>;
     constexpr int N = TP::N, TS = TP::TS, TS2 = TP::TS / 2;
@@ -283,7 +340,7 @@ __global__ void __launch_bounds__(TwoPass<R1, R2>::THREADS, 2) fft_synthesis_two
     extern __shared__ __align__(16) float smem_tp[];
     unsigned char *blob_s = reinterpret_cast<unsigned char *>(smem_tp + kNT * TS);
     const uint32_t bar_tab = ptx::smem_u32(blob_s + a.blob_bytes);
-    const int nitems = a.Kh * ((a.nfields + kNT - 1) / kNT);
+    const int nitems = ROWS ? (int)((a.nrows + 15) >> 4) : a.Kh * ((a.nfields + kNT - 1) / kNT);
     if ((int)blockIdx.x >= nitems) return;
 
     if (threadIdx.x == 0) {
@@ -301,16 +358,20 @@ __global__ void __launch_bounds__(TwoPass<R1, R2>::THREADS, 2) fft_synthesis_two
         {
             const int tid = tid_now();
             const int t = tid & 7, q = q_of<R1>(tid >> 5, (tid >> 3) & 3);
-            int kn, f0, nvalid;
-            decode_item(it, a.Kh, a.nfields, &kn, &f0, &nvalid);
-            const bool active = t < nvalid;
+            int kn = 0, f0 = 0, nvalid = 0;
+            if (!ROWS) decode_item(it, a.Kh, a.nfields, &kn, &f0, &nvalid);
+            const bool active = ROWS || t < nvalid;
             const int ngroups = 2 * a.mmax;
-            const int mtop = min(a.mmax, N / 2 + 1);
+            const int mtop = min(ROWS ? a.nmodes : a.mmax, N / 2 + 1);
             const float *ms_s = reinterpret_cast<const float *>(blob_s + sizeof(float2) * TP::NTW);
             const unsigned char *kf_s = reinterpret_cast<const unsigned char *>(ms_s + a.mpad);
             // this item's panel of Y (latitude kn, fields f0 .. f0 + 7): one contiguous region, 16 floats per group
-            const float *yb = a.op + y_off(0, kn, 2 * (f0 + t), ngroups, a.ncp);
+            const float *yb = ROWS ? nullptr : a.op + y_off(0, kn, 2 * (f0 + t), ngroups, a.ncp);
             const size_t gstride = 16;
+            // ROWS: the spectra of rows 2 t and 2 t + 1 of the item
+            const long long ra = 16LL * it + 2 * t;
+            const bool va = ROWS && ra < a.nrows, vb = ROWS && ra + 1 < a.nrows;
+            const float2 *ia = ROWS ? a.rows_in + (size_t)ra * a.nmodes : nullptr, *ib = ia + (ROWS ? a.nmodes : 0);
             // the loads of CH orders are issued before the first of them is used
 #pragma unroll
             for (int r = 0; r < R2; ++r) u[r] = make_float2(0.f, 0.f);
@@ -322,10 +383,15 @@ __global__ void __launch_bounds__(TwoPass<R1, R2>::THREADS, 2) fft_synthesis_two
                     const int i = i0 + c, m = q + R1 * i;
                     ev[c] = ov[c] = make_float2(0.f, 0.f);
                     if (i <= R2 / 2 && active && m < mtop) {
-                        const int kf = kf_s[m];  // (rows above the group's polar extent were not produced: zeros)
-                        const float *pe = yb + (size_t)(2 * m) * gstride;
-                        if (kn >= (kf & 15) * kBK) ev[c] = __ldg(reinterpret_cast<const float2 *>(pe));
-                        if (kn >= (kf >> 4) * kBK) ov[c] = __ldg(reinterpret_cast<const float2 *>(pe + gstride));
+                        if (ROWS) {
+                            if (va) ev[c] = __ldg(ia + m);
+                            if (vb) ov[c] = __ldg(ib + m);
+                        } else {
+                            const int kf = kf_s[m];  // (rows above the group's polar extent were not produced: zeros)
+                            const float *pe = yb + (size_t)(2 * m) * gstride;
+                            if (kn >= (kf & 15) * kBK) ev[c] = __ldg(reinterpret_cast<const float2 *>(pe));
+                            if (kn >= (kf >> 4) * kBK) ov[c] = __ldg(reinterpret_cast<const float2 *>(pe + gstride));
+                        }
                     }
                 }
                 // bin m -> register i.  Bin n - m -> register R2 - 1 - i of the thread that owns R1 - q, i.e. of the partner
@@ -335,10 +401,11 @@ __global__ void __launch_bounds__(TwoPass<R1, R2>::THREADS, 2) fft_synthesis_two
                 for (int c = 0; c < CH; ++c) {
                     const int i = i0 + c, m = q + R1 * i;
                     if (i > R2 / 2) continue;
-                    const float sc = (active && m < mtop) ? ms_s[m] : 0.f;
                     // north row spectrum A = even + odd, south row spectrum B = even - odd; Z_m = A + i B, Z_{n-m} = conj A + i conj B
-                    const float ar = sc * (ev[c].x + ov[c].x), ai = sc * (ev[c].y + ov[c].y);
-                    const float br = sc * (ev[c].x - ov[c].x), bi = sc * (ev[c].y - ov[c].y);
+                    // (ROWS: the two loads are A and B themselves, unscaled)
+                    const float sc = ROWS ? 1.f : (active && m < mtop) ? ms_s[m] : 0.f;
+                    const float ar = ROWS ? ev[c].x : sc * (ev[c].x + ov[c].x), ai = ROWS ? ev[c].y : sc * (ev[c].y + ov[c].y);
+                    const float br = ROWS ? ov[c].x : sc * (ev[c].x - ov[c].x), bi = ROWS ? ov[c].y : sc * (ev[c].y - ov[c].y);
                     const bool edge = (m == 0) || (2 * m == N);  // imaginary parts of DC / Nyquist are dropped
                     const float2 zm = edge ? make_float2(ar, br) : make_float2(ar - bi, ai + br);
                     const float2 zn = edge ? make_float2(0.f, 0.f) : make_float2(ar + bi, br - ai);
@@ -400,7 +467,15 @@ __global__ void __launch_bounds__(TwoPass<R1, R2>::THREADS, 2) fft_synthesis_two
         }
         ptx::fence_proxy_async_smem();  // the rows are visible to the bulk copies that follow
         __syncthreads();
-        if (tid_now() == 0) {
+        if (ROWS) {
+            if (tid_now() == 0) {
+                const long long r0 = 16LL * it;
+                const int nr = (int)min(16LL, a.nrows - r0);
+                for (int w = 0; w < nr; ++w)
+                    ptx::bulk_store(a.grid_out + (size_t)(r0 + w) * N, ptx::smem_u32(smem_tp + (w >> 1) * TS + (w & 1) * N), N * 4u);
+                ptx::bulk_commit();
+            }
+        } else if (tid_now() == 0) {
             int kn, f0, nvalid;
             decode_item(it, a.Kh, a.nfields, &kn, &f0, &nvalid);
             const int ks = a.nlat - 1 - kn;
@@ -441,17 +516,17 @@ int launch_twopass(const Plan &pl, bool analysis, const float *in, float *out, i
         a.op = out;
         a.kpad = (int)(round_up(pl.Ka, kBK) - pl.Ka);
         if (vec == 2) {
-            SHT_CUDA_CHECK(cudaFuncSetAttribute(fft_analysis_twopass_kernel<R1, R2, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            fft_analysis_twopass_kernel<R1, R2, 2><<<grid, TP::THREADS, smem, st>>>(a);
+            SHT_CUDA_CHECK(cudaFuncSetAttribute(fft_analysis_twopass_kernel<R1, R2, 2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            fft_analysis_twopass_kernel<R1, R2, 2, false><<<grid, TP::THREADS, smem, st>>>(a);
         } else {
-            SHT_CUDA_CHECK(cudaFuncSetAttribute(fft_analysis_twopass_kernel<R1, R2, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            fft_analysis_twopass_kernel<R1, R2, 1><<<grid, TP::THREADS, smem, st>>>(a);
+            SHT_CUDA_CHECK(cudaFuncSetAttribute(fft_analysis_twopass_kernel<R1, R2, 1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            fft_analysis_twopass_kernel<R1, R2, 1, false><<<grid, TP::THREADS, smem, st>>>(a);
         }
     } else {
         a.op = const_cast<float *>(in);
         a.grid_out = out;
-        SHT_CUDA_CHECK(cudaFuncSetAttribute(fft_synthesis_twopass_kernel<R1, R2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        fft_synthesis_twopass_kernel<R1, R2><<<grid, TP::THREADS, smem, st>>>(a);
+        SHT_CUDA_CHECK(cudaFuncSetAttribute(fft_synthesis_twopass_kernel<R1, R2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        fft_synthesis_twopass_kernel<R1, R2, false><<<grid, TP::THREADS, smem, st>>>(a);
     }
     SHT_CUDA_CHECK(cudaGetLastError());
     return SHTB200_OK;
@@ -518,5 +593,65 @@ static int dispatch_twopass(const Plan &pl, bool analysis, const float *in, floa
 int launch_fft_analysis_twopass(const Plan &pl, const float *x, float *X, int nfields, cudaStream_t st) { return dispatch_twopass(pl, true, x, X, nfields, st); }
 
 int launch_fft_synthesis_twopass(const Plan &pl, const float *Y, float *x, int nfields, cudaStream_t st) { return dispatch_twopass(pl, false, Y, x, nfields, st); }
+
+// ---- plain batched row transforms (stage entry points) ----
+
+// Pass twiddles alone, as a device blob for the ROWS kernels.
+int build_twopass_rows_tables(int nlon, unsigned char **d_blob, int *bytes) {
+    int r1 = 0, r2 = 0;
+    *d_blob = nullptr;
+    *bytes = 0;
+    if (!twopass_supported(nlon, &r1, &r2)) return SHTB200_OK;
+    std::vector<float2> tw((size_t)(r1 - 1) * r2 + 1);  // (+1: keeps the blob a multiple of 16 bytes for odd counts)
+    for (int q = 1; q < r1; ++q)
+        for (int j = 0; j < r2; ++j) {
+            const double ang = -2.0 * M_PI * (double)((long long)q * j % nlon) / (double)nlon;
+            tw[(size_t)(q - 1) * r2 + j] = make_float2((float)cos(ang), (float)sin(ang));
+        }
+    const size_t nbytes = (size_t)round_up((long long)(sizeof(float2) * (size_t)(r1 - 1) * r2), 16);
+    SHT_CUDA_CHECK(cudaMalloc(d_blob, nbytes));
+    SHT_CUDA_CHECK(cudaMemcpy(*d_blob, tw.data(), nbytes, cudaMemcpyHostToDevice));
+    *bytes = (int)nbytes;
+    return SHTB200_OK;
+}
+
+template <int R1, int R2>
+static int launch_rows(const TwoPassRows &tr, bool forward, const void *in, void *out, long long nrows, int nmodes, float scale, cudaStream_t st) {
+    using TP = TwoPass<R1, R2>;
+    TwoPassArgs a{};
+    a.blob = tr.blob;
+    a.blob_bytes = tr.blob_bytes;
+    a.err = tr.d_err;
+    a.nrows = nrows;
+    a.nmodes = nmodes;
+    a.scale = scale;
+    const size_t smem = sizeof(float) * kNT * TP::TS + (size_t)tr.blob_bytes + 32;
+    const long long nitems = (nrows + 15) / 16;
+    if (nitems > 0x7fffffffLL) return fail(SHTB200_EINVAL, "too many rows");
+    const int grid = (int)std::min<long long>(2LL * tr.sm_count, nitems);
+    if (forward) {
+        a.grid_in = static_cast<const float *>(in);
+        a.rows_out = static_cast<float2 *>(out);
+        SHT_CUDA_CHECK(cudaFuncSetAttribute(fft_analysis_twopass_kernel<R1, R2, 1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        fft_analysis_twopass_kernel<R1, R2, 1, true><<<grid, TP::THREADS, smem, st>>>(a);
+    } else {
+        a.rows_in = static_cast<const float2 *>(in);
+        a.grid_out = static_cast<float *>(out);
+        SHT_CUDA_CHECK(cudaFuncSetAttribute(fft_synthesis_twopass_kernel<R1, R2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        fft_synthesis_twopass_kernel<R1, R2, true><<<grid, TP::THREADS, smem, st>>>(a);
+    }
+    SHT_CUDA_CHECK(cudaGetLastError());
+    return SHTB200_OK;
+}
+
+// forward: in = (nrows, nlon) real, out = (nrows, nmodes) complex; else the other way round.  Rows must be 16-byte aligned.
+int launch_rows_twopass(const TwoPassRows &tr, bool forward, const void *in, void *out, long long nrows, int nlon, int nmodes, float scale, cudaStream_t st) {
+    switch (nlon) {
+        case 1440: return launch_rows<40, 36>(tr, forward, in, out, nrows, nmodes, scale, st);
+        case 720: return launch_rows<36, 20>(tr, forward, in, out, nrows, nmodes, scale, st);
+        case 512: return launch_rows<32, 16>(tr, forward, in, out, nrows, nmodes, scale, st);
+    }
+    return fail(SHTB200_EINVAL, "no two-pass FFT kernel for this nlon");
+}
 
 }  // namespace shtb200

@@ -212,3 +212,71 @@ def distributed_transpose_azimuth(input_, dims_, shapes_):
 def distributed_transpose_polar(input_, dims_, shapes_):
     """Same across the polar group."""
     return _Transpose.apply(input_, dims_, shapes_, "polar")
+
+
+def _all_reduce_sum(t: torch.Tensor, group) -> torch.Tensor:
+    """Sum over the ranks of ``group`` in a fresh buffer (the caller's tensor is never written); complex tensors travel
+    as (re, im) pairs, half precision is summed in float32 (torch_harmonics/distributed/primitives.py:351-369)."""
+    if dist.get_world_size(group=group) == 1:
+        return t
+    dtype = t.dtype
+    if t.is_complex():
+        buf = torch.view_as_real(t.contiguous()).clone()
+    elif dtype in (torch.float16, torch.bfloat16):
+        buf = t.float().contiguous()  # (a conversion: always a fresh buffer)
+    else:
+        buf = t.contiguous().clone()
+    dist.all_reduce(buf, group=group)
+    return torch.view_as_complex(buf) if t.is_complex() else buf.to(dtype)
+
+
+class _Region(torch.autograd.Function):
+    """The two conjugate halves of a replicated-versus-partial bookkeeping across one communicator:
+
+    * ``reduce=False`` ("copy to region"): identity forward, all-reduce of the gradient backward - for a value that is
+      the same on every rank of the group and feeds rank-local partial computations;
+    * ``reduce=True`` ("reduce from region"): all-reduce forward, identity backward - for partial results that are
+      summed into a value every rank then holds.
+
+    torch_harmonics/distributed/primitives.py:506-553 and :616-669."""
+
+    @staticmethod
+    @torch.amp.custom_fwd(device_type="cuda")
+    def forward(ctx, x, which, reduce):
+        ctx.which, ctx.reduce = which, reduce
+        active = is_distributed_azimuth() if which == "azimuth" else is_distributed_polar()
+        if reduce and active:
+            return _all_reduce_sum(x, azimuth_group() if which == "azimuth" else polar_group())
+        return x.view_as(x)
+
+    @staticmethod
+    @torch.amp.custom_bwd(device_type="cuda")
+    def backward(ctx, g):
+        active = is_distributed_azimuth() if ctx.which == "azimuth" else is_distributed_polar()
+        if not ctx.reduce and active:
+            g = _all_reduce_sum(g, azimuth_group() if ctx.which == "azimuth" else polar_group())
+        return g, None, None
+
+
+@torch.compiler.disable()
+def copy_to_polar_region(input_):
+    """Identity forward, sum of the gradients over the polar group backward."""
+    return _Region.apply(input_, "polar", False)
+
+
+@torch.compiler.disable()
+def copy_to_azimuth_region(input_):
+    """Identity forward, sum of the gradients over the azimuth group backward."""
+    return _Region.apply(input_, "azimuth", False)
+
+
+@torch.compiler.disable()
+def reduce_from_polar_region(input_):
+    """Sum over the polar group forward, identity backward."""
+    return _Region.apply(input_, "polar", True)
+
+
+@torch.compiler.disable()
+def reduce_from_azimuth_region(input_):
+    """Sum over the azimuth group forward, identity backward."""
+    return _Region.apply(input_, "azimuth", True)

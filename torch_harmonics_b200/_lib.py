@@ -87,6 +87,13 @@ def check(rc, what):
         raise ShtLibraryError(f"{what} failed (code {rc}): {msg}")
 
 
+def dense(t):
+    """``t`` as plain contiguous memory, ready for ``data_ptr()``: ``contiguous()`` alone keeps the lazy conjugate / negative
+    bits of a tensor that already is contiguous (``w.conj()``, ``z.conj().imag``), and the raw memory then holds the
+    unconjugated values."""
+    return t.contiguous().resolve_conj().resolve_neg()
+
+
 def spectral_conv(analysis, synthesis, x, weight, y, batch, cin, cout, groups, stream):
     """SHT -> per-degree channel mixing -> inverse SHT on device tensors (``shtb200_spectral_conv``)."""
     import torch

@@ -59,7 +59,7 @@ class _RfftStage(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, nmodes, scale):
         ctx.nlon, ctx.nmodes, ctx.scale = x.shape[-1], nmodes, scale
-        xc = x.contiguous()
+        xc = _lib.dense(x)
         out = torch.empty(xc.shape[:-1] + (nmodes,), dtype=torch.complex64, device=x.device)
         rows = xc.numel() // xc.shape[-1] if xc.numel() else 0
         with torch.cuda.device(x.device):
@@ -79,7 +79,7 @@ class _IrfftStage(torch.autograd.Function):
     @staticmethod
     def forward(ctx, c, nlon):
         ctx.nlon, ctx.nmodes = nlon, c.shape[-1]
-        cc = c.contiguous()
+        cc = _lib.dense(c)
         out = torch.empty(cc.shape[:-1] + (nlon,), dtype=torch.float32, device=c.device)
         rows = cc.numel() // cc.shape[-1] if cc.numel() else 0
         with torch.cuda.device(c.device):
@@ -101,7 +101,7 @@ class _LegendreStage(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, owner, adjoint, out_rows):
         ctx.owner, ctx.adjoint, ctx.in_rows = owner, adjoint, x.shape[-2]
-        xc = x.contiguous()
+        xc = _lib.dense(x)
         n, mloc = xc.shape[0], xc.shape[-1]
         out = torch.empty(xc.shape[:-2] + (out_rows, mloc), dtype=torch.complex64, device=x.device)
         if n == 0 or mloc == 0:

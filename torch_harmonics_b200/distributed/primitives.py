@@ -143,7 +143,7 @@ def _transpose(x: torch.Tensor, dim0: int, dim1: int, dim1_split_sizes, group):
     if config.debug:
         _verify("_transpose: error, dim1_split_sizes", x.shape[dim1], list(dim1_split_sizes), group)
     is_complex = x.is_complex()
-    xr = torch.view_as_real(x) if is_complex else x  # trailing (re, im) axis does not move
+    xr = torch.view_as_real(x.resolve_conj()) if is_complex else x  # trailing (re, im) axis does not move
     xr = xr.contiguous()
     d0 = compute_split_shapes(x.shape[dim0], size)
     per0 = xr.numel() // x.shape[dim0] if x.shape[dim0] else 0   # elements per index of dim0
@@ -221,7 +221,7 @@ def _all_reduce_sum(t: torch.Tensor, group) -> torch.Tensor:
         return t
     dtype = t.dtype
     if t.is_complex():
-        buf = torch.view_as_real(t.contiguous()).clone()
+        buf = torch.view_as_real(t.contiguous().resolve_conj()).clone()
     elif dtype in (torch.float16, torch.bfloat16):
         buf = t.float().contiguous()  # (a conversion: always a fresh buffer)
     else:

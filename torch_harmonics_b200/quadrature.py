@@ -110,7 +110,7 @@ class _Quadrature(torch.autograd.Function):
     def forward(ctx, x, w):
         from . import _lib
 
-        xc = x.contiguous()
+        xc = _lib.dense(x)
         nlat, nlon = xc.shape[-2], xc.shape[-1]
         out = torch.empty(xc.shape[:-2], dtype=torch.float32, device=x.device)
         n = out.numel()

@@ -98,7 +98,7 @@ def _register_op(op):
 def _linear_transform(x: torch.Tensor, handle: int, adjoint: bool, out_tail: List[int], out_complex: bool, lead_dims: int) -> torch.Tensor:
     """y = A x for the real-linear map A of plan pair `handle` (its transpose when `adjoint`)."""
     op = _OPS[handle]
-    xc = x.contiguous()
+    xc = _lib.dense(x)
     nfields = 1
     for s in xc.shape[:lead_dims]:
         nfields *= s

@@ -30,7 +30,7 @@ class _FusedSpectralConv(torch.autograd.Function):
         B, Cin = x.shape[0], x.shape[1]
         G, _, Cog, _ = weight.shape
         Cout = G * Cog
-        xc, wc = x.contiguous(), weight.contiguous()
+        xc, wc = _lib.dense(x), _lib.dense(weight)
         y = torch.empty(B, Cout, layer.isht.nlat, layer.isht.nlon, dtype=torch.float32, device=x.device)
         with torch.cuda.device(x.device):
             _lib.spectral_conv(layer.sht._op.plan(x.device, False), layer.isht._op.plan(x.device, False), xc, wc, y, B, Cin, Cout, G,
@@ -43,7 +43,7 @@ class _FusedSpectralConv(torch.autograd.Function):
     def backward(ctx, gy):
         x, w = ctx.saved_tensors
         layer = ctx.layer
-        gy = gy.contiguous()
+        gy = _lib.dense(gy)
         B, Cin = x.shape[0], x.shape[1]
         G, Cig, Cog, L = w.shape
         Cout = G * Cog
@@ -51,7 +51,7 @@ class _FusedSpectralConv(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             # x -> y is real-linear: its transpose is the adjoint inverse transform, the conjugated weights with the
             # channel roles swapped, the adjoint forward transform
-            wt = w.conj().permute(0, 2, 1, 3).contiguous()
+            wt = _lib.dense(w.conj().permute(0, 2, 1, 3))  # (with one channel per group the permutation is a view: the conjugate must be materialised)
             gx = torch.empty_like(x)
             with torch.cuda.device(x.device):
                 _lib.spectral_conv(layer.isht._op.plan(x.device, True), layer.sht._op.plan(x.device, True), gy, wt, gx, B, Cout, Cin, G,

@@ -190,18 +190,18 @@ def kernel_bytes(nf, table_fwd_bytes, table_inv_bytes, slabs):
 # (bytes, fields in the captured launch, True if the traffic grows in proportion to the number of fields, capture).
 # The FFT and transpose kernels only stream per-field data; the Legendre kernels also read the packed table once per
 # launch, so their figure holds for the captured field count only.
-NCU_TRAFFIC = {
-    "fft_analysis": (133.01e6 + 58.22e6, 32, True, "fft_twopass_kernels_32fields"),
-    "fft_synthesis": (98.70e6 + 83.60e6, 32, True, "fft_twopass_kernels_32fields"),
-    "pack_coeffs": (67.86e6 + 26.12e6, 32, True, "coeff_slab_transpose_32fields"),
-    "unpack_coeffs": (72.31e6 + 78.94e6, 32, True, "coeff_slab_transpose_32fields"),
-    "legendre_analysis": (611.80e6 + 135.90e6, 73, False, "legendre_tc_kernel_73fields"),
-    "legendre_synthesis": (551.98e6 + 198.46e6, 73, False, "legendre_tc_kernel_73fields"),
+NCU_TRAFFIC = {  # kernel: (dram bytes read + written per launch, fields of the capture, scales with the field count, summary under profiles/, commit captured at)
+    "fft_analysis": (133.01e6 + 58.22e6, 32, True, "fft_twopass_kernels_32fields", "03be9b6"),
+    "fft_synthesis": (98.70e6 + 83.60e6, 32, True, "fft_twopass_kernels_32fields", "03be9b6"),
+    "pack_coeffs": (67.86e6 + 26.99e6, 32, True, "coeff_slab_transpose_32fields", "03be9b6"),
+    "unpack_coeffs": (72.29e6 + 77.22e6, 32, True, "coeff_slab_transpose_32fields", "03be9b6"),
+    "legendre_analysis": (611.81e6 + 135.42e6, 73, False, "legendre_tc_kernel_73fields", "03be9b6"),
+    "legendre_synthesis": (561.63e6 + 188.40e6, 73, False, "legendre_tc_kernel_73fields", "03be9b6"),
 }
 
 
 def measured_traffic(kernel, nf):
-    b, n, scales, _ = NCU_TRAFFIC[kernel]
+    b, n, scales = NCU_TRAFFIC[kernel][:3]
     if scales:
         return b * nf / n
     return b if nf == n else None
@@ -763,7 +763,7 @@ def run_ours(args):
             "roofline": {
                 "kernel": dom, "bound": "hbm", "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak,
                 "traffic": measured_traffic(dom, nf), "peak_source": peak_src, "algorithmic_bytes": kb[dom],
-                "traffic_source": f"ncu capture '{NCU_TRAFFIC[dom][3]}' of this kernel, scaled by the field count where it is proportional",
+                "traffic_source": f"ncu capture '{NCU_TRAFFIC[dom][3]}' of this kernel (kernels as of commit {NCU_TRAFFIC[dom][4]}), scaled by the field count where it is proportional",
             },
             "e2e": {
                 "value": nf * world * e2e_steps / t_e2e, "unit": "fields/s",

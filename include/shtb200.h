@@ -184,7 +184,30 @@ size_t shtb200_plan_table_bytes(const shtb200_plan *plan);
  */
 int shtb200_rfft_modes(const float *in_dev, void *out_dev, long long nrows, int nlon, int nmodes, float scale, void *stream);
 int shtb200_irfft_modes(const void *in_dev, float *out_dev, long long nrows, int nlon, int nmodes, void *stream);
+/*
+ * The same two transforms on PIECE-MAJOR buffers, the form in which an all-to-all transpose receives / sends a tensor whose
+ * last axis is gathered / scattered (torch_harmonics/distributed/primitives.py:227-289: the chunks of the split axis
+ * travel as separate contiguous blocks): an axis of length n in P pieces is cut into balanced chunks (the first n % P one
+ * longer, as compute_split_shapes does) and chunk j is stored as its own contiguous [nrows, width_j] block, the blocks one
+ * after the other.  `grid_pieces` describes the longitude axis of the real buffer, `mode_pieces` the order axis of the
+ * complex buffer; 1 means plain rows.  The distributed forward transform then needs no copy between the exchange that
+ * gathers the longitudes, the FFT and the exchange that scatters the orders (and the inverse likewise).
+ * shtb200_rows_pieces_supported returns 1 where these calls apply (nlon with a two-pass kernel: 1440, 720, 512; the
+ * longitude pieces equal and a multiple of four wide), else 0 - the caller then transposes through plain rows.
+ */
+int shtb200_rows_pieces_supported(int nlon, int nmodes, int grid_pieces, int mode_pieces);
+int shtb200_rfft_modes_pieces(const float *in_dev, void *out_dev, long long nrows, int nlon, int nmodes, float scale, int grid_pieces, int mode_pieces, void *stream);
+int shtb200_irfft_modes_pieces(const void *in_dev, float *out_dev, long long nrows, int nlon, int nmodes, int mode_pieces, int grid_pieces, void *stream);
 int shtb200_legendre(shtb200_plan *plan, const void *in_dev, void *out_dev, int nfields, int m0, int mloc, void *workspace_dev, size_t workspace_bytes, void *stream);
+/*
+ * shtb200_legendre on piece-major tensors (see shtb200_rfft_modes_pieces): the ROW axis (second to last: latitude or
+ * degree) of the input is stored in `in_pieces` balanced chunks, chunk j as its own contiguous [fields, rows_j, mloc]
+ * block ([fields, 2, rows_j, mloc] for the vector kinds), and the output is written the same way in `out_pieces` chunks -
+ * the layouts in which the polar all-to-all delivers the latitudes and takes the degrees (and the other way round for the
+ * inverse transforms), so that no copy sits between those exchanges and the contraction.  1 / 1 is shtb200_legendre.
+ */
+int shtb200_legendre_pieces(shtb200_plan *plan, const void *in_dev, void *out_dev, int nfields, int m0, int mloc, int in_pieces, int out_pieces, void *workspace_dev,
+                            size_t workspace_bytes, void *stream);
 size_t shtb200_legendre_workspace_bytes(const shtb200_plan *plan, int nfields, int mloc);
 
 #ifdef __cplusplus

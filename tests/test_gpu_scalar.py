@@ -204,6 +204,101 @@ def test_linearity_and_batch_independence():
     assert err(c1, cx[2:3]) <= 1e-6
 
 
+def _split(n, p):
+    q, r = divmod(n, p)
+    return [q + (1 if j < r else 0) for j in range(p)]
+
+
+@pytest.mark.parametrize("nlon,nmodes,nrows,gp,mp", [(1440, 720, 37, 2, 2), (1440, 721, 16, 4, 3), (1440, 100, 1, 8, 1), (720, 361, 50, 4, 8), (720, 400, 21, 1, 7),
+                                                    (512, 257, 33, 8, 2), (512, 96, 15, 2, 5)])
+def test_piece_major_row_transforms(nlon, nmodes, nrows, gp, mp):
+    """Row transforms on piece-major buffers (the receive / send layout of an all-to-all transpose whose last axis is
+    gathered / scattered: chunk j of the axis is its own contiguous (nrows, width_j) block) give bit for bit the plain
+    transforms' results, rearranged."""
+    import ctypes
+
+    import torch
+
+    from torch_harmonics_b200 import _lib
+
+    lib = _lib.load()
+    vp = ctypes.c_void_p
+    assert lib.shtb200_rows_pieces_supported(nlon, nmodes, gp, mp) == 1
+    gen = torch.Generator(device="cuda").manual_seed(nrows)
+    x = torch.randn(nrows, nlon, device="cuda", generator=gen)
+
+    def to_pieces(t, p):
+        return torch.cat([c.reshape(-1) for c in torch.split(t, _split(t.shape[1], p), dim=1)])
+
+    plain = torch.empty(nrows, nmodes, dtype=torch.complex64, device="cuda")
+    assert lib.shtb200_rfft_modes(vp(x.data_ptr()), vp(plain.data_ptr()), nrows, nlon, nmodes, 2.0, None) == 0
+    xin = to_pieces(x, gp)
+    out = torch.full((nrows * nmodes * 2,), float("nan"), device="cuda")
+    assert lib.shtb200_rfft_modes_pieces(vp(xin.data_ptr()), vp(out.data_ptr()), nrows, nlon, nmodes, 2.0, gp, mp, None) == 0
+    torch.cuda.synchronize()
+    expect = torch.cat([torch.view_as_real(c.contiguous()).reshape(-1) for c in torch.split(plain, _split(nmodes, mp), dim=1)])
+    assert torch.equal(out, expect)
+
+    c = torch.view_as_complex(torch.randn(nrows, nmodes, 2, device="cuda", generator=gen))
+    plain_y = torch.empty(nrows, nlon, device="cuda")
+    assert lib.shtb200_irfft_modes(vp(c.data_ptr()), vp(plain_y.data_ptr()), nrows, nlon, nmodes, None) == 0
+    cin = torch.cat([torch.view_as_real(p.contiguous()).reshape(-1) for p in torch.split(c, _split(nmodes, mp), dim=1)])
+    y = torch.full((nrows * nlon,), float("nan"), device="cuda")
+    assert lib.shtb200_irfft_modes_pieces(vp(cin.data_ptr()), vp(y.data_ptr()), nrows, nlon, nmodes, mp, gp, None) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(y, to_pieces(plain_y, gp))
+
+
+def test_piece_major_row_transforms_unsupported_shapes():
+    import ctypes
+
+    import torch
+
+    from torch_harmonics_b200 import _lib
+
+    lib = _lib.load()
+    # no two-pass kernel for nlon; pieces that are not equal multiples of four longitudes; more pieces than orders
+    for nlon, nmodes, gp, mp in ((64, 33, 2, 2), (1440, 720, 7, 1), (720, 361, 16, 1), (512, 257, 1, 300)):
+        assert lib.shtb200_rows_pieces_supported(nlon, nmodes, gp, mp) == 0
+    x = torch.zeros(4, 64, device="cuda")
+    out = torch.zeros(4 * 33 * 2, device="cuda")
+    rc = lib.shtb200_rfft_modes_pieces(ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(out.data_ptr()), 4, 64, 33, 1.0, 2, 2, None)
+    assert rc != 0 and "piece-major" in lib.shtb200_last_error().decode()
+
+
+@pytest.mark.parametrize("pieces_in,pieces_out", [(2, 2), (3, 4), (1, 5), (4, 1)])
+def test_piece_major_legendre_stage(pieces_in, pieces_out):
+    """The contraction stage on piece-major tensors (row axis in balanced chunks, chunk j its own contiguous
+    (fields, rows_j, orders) block: what the polar all-to-all delivers and takes) equals the plain stage bit for bit,
+    rearranged - scalar and vector plans, both directions, orders that do not start at 0."""
+    import torch
+
+    from torch_harmonics_b200 import _lib
+
+    nlat, nlon, grid = 33, 64, "equiangular"
+    w, p, L, M = oracle_tables(nlat, nlon, 20, 20, grid)
+    vw, _, _ = orc.vsht_weights(nlat, nlon, lmax=20, mmax=20, grid=grid)
+    vp, _, _ = orc.ivsht_dpct(nlat, nlon, lmax=20, mmax=20, grid=grid)
+    nf, m0, mloc = 5, 3, 11
+    gen = torch.Generator(device="cuda").manual_seed(9)
+
+    def to_pieces(t, n):  # t: (fields, [2,] rows, orders) complex
+        return torch.cat([torch.view_as_real(c.contiguous()).reshape(-1) for c in torch.split(t, _split(t.shape[-2], n), dim=-2)])
+
+    for kind, table, comp, rows_in, rows_out in ((_lib.SHT, w, (), nlat, L), (_lib.ISHT, p, (), L, nlat), (_lib.VSHT, vw, (2,), nlat, L), (_lib.IVSHT, vp, (2,), L, nlat)):
+        plan = make_plan(kind, nlat, nlon, L, M, table, "auto")
+        x = torch.view_as_complex(torch.randn((nf,) + comp + (rows_in, mloc, 2), device="cuda", generator=gen))
+        ws = torch.empty(plan.legendre_workspace_bytes(nf, mloc), dtype=torch.uint8, device="cuda")
+        plain = torch.full((nf,) + comp + (rows_out, mloc), float("nan"), dtype=torch.complex64, device="cuda")
+        plan.legendre(x, plain, nf, m0, mloc, ws, 0)
+        out = torch.full((plain.numel() * 2,), float("nan"), device="cuda")
+        plan.legendre(to_pieces(x, pieces_in), out, nf, m0, mloc, ws, 0, in_pieces=pieces_in, out_pieces=pieces_out)
+        torch.cuda.synchronize()
+        assert torch.equal(out, to_pieces(plain, pieces_out)), kind
+    with pytest.raises(_lib.ShtLibraryError, match="piece counts"):
+        plan.legendre(x, plain, nf, m0, mloc, ws, 0, in_pieces=L + 1, out_pieces=1)
+
+
 @pytest.mark.parametrize("engine", ENGINES)
 def test_stage_entry_points(engine):
     """rfft / irfft row transforms and the stand-alone Legendre stage used by the distributed modules

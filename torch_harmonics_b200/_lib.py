@@ -67,8 +67,16 @@ def load():
         lib.shtb200_rfft_modes.restype = ci
         lib.shtb200_irfft_modes.argtypes = [vp, vp, cll, ci, ci, vp]
         lib.shtb200_irfft_modes.restype = ci
+        lib.shtb200_rows_pieces_supported.argtypes = [ci, ci, ci, ci]
+        lib.shtb200_rows_pieces_supported.restype = ci
+        lib.shtb200_rfft_modes_pieces.argtypes = [vp, vp, cll, ci, ci, ctypes.c_float, ci, ci, vp]
+        lib.shtb200_rfft_modes_pieces.restype = ci
+        lib.shtb200_irfft_modes_pieces.argtypes = [vp, vp, cll, ci, ci, ci, ci, vp]
+        lib.shtb200_irfft_modes_pieces.restype = ci
         lib.shtb200_legendre.argtypes = [vp, vp, vp, ci, ci, ci, vp, cs, vp]
         lib.shtb200_legendre.restype = ci
+        lib.shtb200_legendre_pieces.argtypes = [vp, vp, vp, ci, ci, ci, ci, ci, vp, cs, vp]
+        lib.shtb200_legendre_pieces.restype = ci
         lib.shtb200_legendre_workspace_bytes.argtypes = [vp, ci, ci]
         lib.shtb200_legendre_workspace_bytes.restype = cs
         lib.shtb200_spectral_conv_workspace_bytes.argtypes = [vp, vp, ci, ci, ci, ci]
@@ -92,6 +100,11 @@ def dense(t):
     bits of a tensor that already is contiguous (``w.conj()``, ``z.conj().imag``), and the raw memory then holds the
     unconjugated values."""
     return t.contiguous().resolve_conj().resolve_neg()
+
+
+def rows_pieces_supported(nlon, nmodes, grid_pieces, mode_pieces):
+    """Whether the row transforms take piece-major buffers for this shape (``shtb200_rows_pieces_supported``)."""
+    return bool(load().shtb200_rows_pieces_supported(nlon, nmodes, grid_pieces, mode_pieces))
 
 
 def spectral_conv(analysis, synthesis, x, weight, y, batch, cin, cout, groups, stream):
@@ -156,11 +169,14 @@ class Plan:
     def legendre_workspace_bytes(self, nfields, mloc):
         return load().shtb200_legendre_workspace_bytes(self.handle, nfields, mloc)
 
-    def legendre(self, inp, out, nfields, m0, mloc, workspace, stream):
-        rc = load().shtb200_legendre(
-            self.handle, ctypes.c_void_p(inp.data_ptr()), ctypes.c_void_p(out.data_ptr()), nfields, m0, mloc, ctypes.c_void_p(workspace.data_ptr()), workspace.numel(), ctypes.c_void_p(stream)
+    def legendre(self, inp, out, nfields, m0, mloc, workspace, stream, in_pieces=1, out_pieces=1):
+        """The contraction stage alone; ``in_pieces`` / ``out_pieces`` > 1: the row axis of the input / output is stored
+        piece-major (``shtb200_legendre_pieces``)."""
+        rc = load().shtb200_legendre_pieces(
+            self.handle, ctypes.c_void_p(inp.data_ptr()), ctypes.c_void_p(out.data_ptr()), nfields, m0, mloc, in_pieces, out_pieces,
+            ctypes.c_void_p(workspace.data_ptr()), workspace.numel(), ctypes.c_void_p(stream)
         )
-        check(rc, "shtb200_legendre")
+        check(rc, "shtb200_legendre_pieces")
 
     def device_status(self):
         """Synchronise and raise if a kernel of this plan gave up on a bounded wait."""

@@ -165,14 +165,14 @@ int execute_full(Plan &pl, const void *in, void *out, int nfields, void *ws, siz
         if ((rc = run_gemm(pl, gp, st))) return rc;
         mark(pl, st);
         // (a vector pair's four columns are the (re, im) pairs of its two output fields: the same slab layout with twice the fields)
-        if ((rc = launch_unpack_coeffs(pl, Z, reinterpret_cast<float2 *>(out), nfields, 0, pl.mmax, st))) return rc;
+        if ((rc = launch_unpack_coeffs(pl, Z, reinterpret_cast<float2 *>(out), nfields, 0, pl.mmax, 1, st))) return rc;
         pl.last_launches += 1;
         mark(pl, st);
     } else {
         float *Ct = reinterpret_cast<float *>(ws);
         float *Y = reinterpret_cast<float *>(reinterpret_cast<char *>(ws) + align256(w.op_bytes));
         const int ncols = (pl.vector ? 4 : 2) * nfields;
-        if ((rc = launch_pack_coeffs(pl, reinterpret_cast<const float2 *>(in), Ct, nfields, 0, pl.mmax, st))) return rc;
+        if ((rc = launch_pack_coeffs(pl, reinterpret_cast<const float2 *>(in), Ct, nfields, 0, pl.mmax, 1, st))) return rc;
         if ((rc = clear_empty_groups(pl, Y, ncols, 0, pl.mmax, st))) return rc;
         mark(pl, st);
         GemmParams gp = gemm_params(pl, nfields, 0, pl.mmax, Ct, Y);
@@ -630,14 +630,30 @@ int shtb200_rfft_modes(const float *in_dev, void *out_dev, long long nrows, int 
     if (nrows < 0 || nlon < 2 || nmodes < 1) return fail(SHTB200_EINVAL, "bad rfft shape");
     if (nrows == 0) return SHTB200_OK;
     if (!in_dev || !out_dev) return fail(SHTB200_EINVAL, "null pointer");
-    return launch_rfft_modes(in_dev, reinterpret_cast<float2 *>(out_dev), nrows, nlon, nmodes, scale, (cudaStream_t)stream);
+    return launch_rfft_modes(in_dev, reinterpret_cast<float2 *>(out_dev), nrows, nlon, nmodes, scale, 1, 1, (cudaStream_t)stream);
+}
+
+int shtb200_rows_pieces_supported(int nlon, int nmodes, int grid_pieces, int mode_pieces) { return rows_pieces_supported(nlon, nmodes, grid_pieces, mode_pieces) ? 1 : 0; }
+
+int shtb200_rfft_modes_pieces(const float *in_dev, void *out_dev, long long nrows, int nlon, int nmodes, float scale, int grid_pieces, int mode_pieces, void *stream) {
+    if (nrows < 0 || nlon < 2 || nmodes < 1 || grid_pieces < 1 || mode_pieces < 1) return fail(SHTB200_EINVAL, "bad rfft shape");
+    if (nrows == 0) return SHTB200_OK;
+    if (!in_dev || !out_dev) return fail(SHTB200_EINVAL, "null pointer");
+    return launch_rfft_modes(in_dev, reinterpret_cast<float2 *>(out_dev), nrows, nlon, nmodes, scale, grid_pieces, mode_pieces, (cudaStream_t)stream);
+}
+
+int shtb200_irfft_modes_pieces(const void *in_dev, float *out_dev, long long nrows, int nlon, int nmodes, int mode_pieces, int grid_pieces, void *stream) {
+    if (nrows < 0 || nlon < 2 || nmodes < 1 || grid_pieces < 1 || mode_pieces < 1) return fail(SHTB200_EINVAL, "bad irfft shape");
+    if (nrows == 0) return SHTB200_OK;
+    if (!in_dev || !out_dev) return fail(SHTB200_EINVAL, "null pointer");
+    return launch_irfft_modes(reinterpret_cast<const float2 *>(in_dev), out_dev, nrows, nlon, nmodes, mode_pieces, grid_pieces, (cudaStream_t)stream);
 }
 
 int shtb200_irfft_modes(const void *in_dev, float *out_dev, long long nrows, int nlon, int nmodes, void *stream) {
     if (nrows < 0 || nlon < 2 || nmodes < 1) return fail(SHTB200_EINVAL, "bad irfft shape");
     if (nrows == 0) return SHTB200_OK;
     if (!in_dev || !out_dev) return fail(SHTB200_EINVAL, "null pointer");
-    return launch_irfft_modes(reinterpret_cast<const float2 *>(in_dev), out_dev, nrows, nlon, nmodes, (cudaStream_t)stream);
+    return launch_irfft_modes(reinterpret_cast<const float2 *>(in_dev), out_dev, nrows, nlon, nmodes, 1, 1, (cudaStream_t)stream);
 }
 
 size_t shtb200_legendre_workspace_bytes(const shtb200_plan *pl, int nfields, int mloc) {
@@ -647,7 +663,17 @@ size_t shtb200_legendre_workspace_bytes(const shtb200_plan *pl, int nfields, int
 }
 
 int shtb200_legendre(shtb200_plan *pl, const void *in_dev, void *out_dev, int nfields, int m0, int mloc, void *workspace_dev, size_t workspace_bytes, void *stream) {
+    return shtb200_legendre_pieces(pl, in_dev, out_dev, nfields, m0, mloc, 1, 1, workspace_dev, workspace_bytes, stream);
+}
+
+int shtb200_legendre_pieces(shtb200_plan *pl, const void *in_dev, void *out_dev, int nfields, int m0, int mloc, int in_pieces, int out_pieces, void *workspace_dev,
+                            size_t workspace_bytes, void *stream) {
     if (!pl) return fail(SHTB200_EINVAL, "plan is null");
+    {
+        const int rows_in = pl->analysis ? pl->nlat : pl->lmax, rows_out = pl->analysis ? pl->lmax : pl->nlat;
+        if (in_pieces < 1 || out_pieces < 1 || in_pieces > rows_in || out_pieces > rows_out || in_pieces > 64 || out_pieces > 64)
+            return fail(SHTB200_EINVAL, "bad piece counts: between 1 and min(64, length of the row axis)");
+    }
     if (nfields < 0 || mloc < 0 || m0 < pl->m_base || m0 + mloc > pl->m_base + pl->mmax) return fail(SHTB200_EINVAL, "bad (nfields, m0, mloc): the orders must lie inside the plan");
     pl->last_launches = 0;
     if (nfields == 0 || mloc == 0) return SHTB200_OK;
@@ -662,21 +688,21 @@ int shtb200_legendre(shtb200_plan *pl, const void *in_dev, void *out_dev, int nf
     if (pl->analysis) {
         float *X = reinterpret_cast<float *>(workspace_dev);
         float *Z = reinterpret_cast<float *>(reinterpret_cast<char *>(workspace_dev) + align256(w.op_bytes));
-        if ((rc = launch_fold_modes(*pl, reinterpret_cast<const float2 *>(in_dev), X, nfields, m0, mloc, st))) return rc;
+        if ((rc = launch_fold_modes(*pl, reinterpret_cast<const float2 *>(in_dev), X, nfields, m0, mloc, in_pieces, st))) return rc;
         {
             GemmParams gp = gemm_params(*pl, nfields, m0, mloc, X, Z);
             if ((rc = run_gemm(*pl, gp, st))) return rc;
-            if ((rc = launch_unpack_coeffs(*pl, Z, reinterpret_cast<float2 *>(out_dev), nfields, m0, mloc, st))) return rc;
+            if ((rc = launch_unpack_coeffs(*pl, Z, reinterpret_cast<float2 *>(out_dev), nfields, m0, mloc, out_pieces, st))) return rc;
         }
         pl->last_launches += 2;
     } else {
         float *Ct = reinterpret_cast<float *>(workspace_dev);
         float *Y = reinterpret_cast<float *>(reinterpret_cast<char *>(workspace_dev) + align256(w.op_bytes));
-        if ((rc = launch_pack_coeffs(*pl, reinterpret_cast<const float2 *>(in_dev), Ct, nfields, m0, mloc, st))) return rc;
+        if ((rc = launch_pack_coeffs(*pl, reinterpret_cast<const float2 *>(in_dev), Ct, nfields, m0, mloc, in_pieces, st))) return rc;
         if ((rc = clear_empty_groups(*pl, Y, (pl->vector ? 4 : 2) * nfields, m0, mloc, st))) return rc;
         GemmParams gp = gemm_params(*pl, nfields, m0, mloc, Ct, Y);
         if ((rc = run_gemm(*pl, gp, st))) return rc;
-        if ((rc = launch_unfold_modes(*pl, Y, reinterpret_cast<float2 *>(out_dev), nfields, m0, mloc, st))) return rc;
+        if ((rc = launch_unfold_modes(*pl, Y, reinterpret_cast<float2 *>(out_dev), nfields, m0, mloc, out_pieces, st))) return rc;
         pl->last_launches += 2;
     }
     return SHTB200_OK;

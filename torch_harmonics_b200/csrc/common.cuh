@@ -196,6 +196,30 @@ int build_fft_plan(int nlon, int mmax_emit, int layout, const int *krow0, FftPla
 int launch_fft_analysis(const Plan &pl, const float *x, float *X, int nfields, cudaStream_t st);
 // synthesis: Y[blocked_row(group, k')][col] -> rows of x
 int launch_fft_synthesis(const Plan &pl, const float *Y, float *x, int nfields, cudaStream_t st);
+// balanced split of n into P pieces (the first n % P one longer): the piece that holds index i -> (first index, width)
+__host__ __device__ __forceinline__ void piece_of(int i, int n, int P, int *start, int *width) {
+    const int q = n / P, rem = n - q * P;
+    int s = 0, w = q + (rem > 0 ? 1 : 0);
+    for (int j = 1; j < P && i >= s + w; ++j) {
+        s += w;
+        w = q + (j < rem ? 1 : 0);
+    }
+    *start = s;
+    *width = w;
+}
+
+// A (nF, R, mloc) tensor whose row axis travels through an all-to-all in P pieces is stored "piece-major": piece j is its
+// own contiguous (nF, width_j, mloc) block, the blocks one after the other.  row index (in units of mloc) of (F, row):
+struct RowPieces {
+    int P = 1, nF = 0;
+};
+__device__ __forceinline__ size_t piece_row(const RowPieces rp, int F, int R, int row) {
+    if (rp.P == 1) return (size_t)F * R + row;
+    int s0, w;
+    piece_of(row, R, rp.P, &s0, &w);
+    return (size_t)rp.nF * s0 + (size_t)F * w + (row - s0);
+}
+
 // register-resident two-pass kernels (fft_twopass.cu); the launchers above pick them when the plan has their tables
 bool twopass_supported(int nlon, int *r1, int *r2);
 int build_twopass_tables(Plan &pl, const std::vector<float> &mscale);
@@ -208,10 +232,12 @@ struct TwoPassRows {
     int *d_err = nullptr;  // device error word for bounded waits that ran out
 };
 int build_twopass_rows_tables(int nlon, unsigned char **d_blob, int *bytes);
-int launch_rows_twopass(const TwoPassRows &tr, bool forward, const void *in, void *out, long long nrows, int nlon, int nmodes, float scale, cudaStream_t st);
+bool rows_pieces_supported(int nlon, int nmodes, int grid_pieces, int mode_pieces);
+int launch_rows_twopass(const TwoPassRows &tr, bool forward, const void *in, void *out, long long nrows, int nlon, int nmodes, float scale, int grid_pieces,
+                        int mode_pieces, cudaStream_t st);
 // plain row transforms for the distributed stages
-int launch_rfft_modes(const float *in, float2 *out, long long nrows, int nlon, int nmodes, float scale, cudaStream_t st);
-int launch_irfft_modes(const float2 *in, float *out, long long nrows, int nlon, int nmodes, cudaStream_t st);
+int launch_rfft_modes(const float *in, float2 *out, long long nrows, int nlon, int nmodes, float scale, int grid_pieces, int mode_pieces, cudaStream_t st);
+int launch_irfft_modes(const float2 *in, float *out, long long nrows, int nlon, int nmodes, int mode_pieces, int grid_pieces, cudaStream_t st);
 
 int launch_gemm_simt(const GemmParams &gp, cudaStream_t st);
 int launch_gemm_tc(const Plan &pl, const GemmParams &gp, cudaStream_t st);
@@ -223,10 +249,11 @@ int launch_pack_table(Plan &pl, const float *table, cudaStream_t st);
 // that degree's largest magnitude over all latitudes (Kh if none does)
 int launch_polar_extent(const Plan &pl, const float *table, float rel, std::vector<int> *first_row);
 // (m0 = first order of the call, an actual order: m_base <= m0, m0 + mloc <= m_base + mmax)
-int launch_pack_coeffs(const Plan &pl, const float2 *c, float *Ct, int nfields, int m0, int mloc, cudaStream_t st);
-int launch_unpack_coeffs(const Plan &pl, const float *Z, float2 *c, int nfields, int m0, int mloc, cudaStream_t st);
-int launch_fold_modes(const Plan &pl, const float2 *Xc, float *X, int nfields, int m0, int mloc, cudaStream_t st);
-int launch_unfold_modes(const Plan &pl, const float *Y, float2 *Xc, int nfields, int m0, int mloc, cudaStream_t st);  // honours group_krow0
+// pieces: the (field, row, order) side is piece-major along its row axis (RowPieces above); 1 = plain
+int launch_pack_coeffs(const Plan &pl, const float2 *c, float *Ct, int nfields, int m0, int mloc, int pieces, cudaStream_t st);
+int launch_unpack_coeffs(const Plan &pl, const float *Z, float2 *c, int nfields, int m0, int mloc, int pieces, cudaStream_t st);
+int launch_fold_modes(const Plan &pl, const float2 *Xc, float *X, int nfields, int m0, int mloc, int pieces, cudaStream_t st);
+int launch_unfold_modes(const Plan &pl, const float *Y, float2 *Xc, int nfields, int m0, int mloc, int pieces, cudaStream_t st);  // honours group_krow0
 
 // spectral convolution on the degree slabs, spherical quadrature (spectral_conv.cu)
 size_t slab_mix_weight_bytes(int cin, int cout, int ngroups, int lmax);

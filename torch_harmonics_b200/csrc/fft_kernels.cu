@@ -949,24 +949,26 @@ static int cached_fft(int nlon, FftPlanDev *fp, TwoPassRows *rows, int **h_err) 
 // Two-pass row transforms when there is a kernel for nlon and the rows are 16-byte aligned; *done says whether it ran.
 // A bounded wait that ran out inside an earlier launch shows in the pinned copy of the error word: the next call fails.
 static int rows_twopass(const TwoPassRows &rows, int *h_err, bool forward, const void *in, void *out, long long nrows, int nlon, int nmodes, float scale,
-                        cudaStream_t st, bool *done) {
+                        int grid_pieces, int mode_pieces, cudaStream_t st, bool *done) {
     *done = false;
     const void *grid = forward ? in : out;
     if (!rows.blob || ((uintptr_t)grid & 15) != 0) return SHTB200_OK;
+    if ((grid_pieces != 1 || mode_pieces != 1) && !rows_pieces_supported(nlon, nmodes, grid_pieces, mode_pieces)) return SHTB200_OK;
     if (*reinterpret_cast<volatile int *>(h_err) != 0) {
         const int v = *h_err;
         *h_err = 0;
         cudaMemsetAsync(rows.d_err, 0, sizeof(int), st);
         return fail(SHTB200_EDEVICE, "a row-transform kernel gave up on a bounded wait (device error word " + std::to_string(v) + ")");
     }
-    int rc = launch_rows_twopass(rows, forward, in, out, nrows, nlon, nmodes, scale, st);
+    int rc = launch_rows_twopass(rows, forward, in, out, nrows, nlon, nmodes, scale, grid_pieces, mode_pieces, st);
     if (rc) return rc;
     SHT_CUDA_CHECK(cudaMemcpyAsync(h_err, rows.d_err, sizeof(int), cudaMemcpyDeviceToHost, st));
     *done = true;
     return SHTB200_OK;
 }
 
-int launch_rfft_modes(const float *in, float2 *out, long long nrows, int nlon, int nmodes, float scale, cudaStream_t st) {
+// grid_pieces / mode_pieces != 1: piece-major buffers (two-pass kernels only; SHTB200_EINVAL where they do not apply)
+int launch_rfft_modes(const float *in, float2 *out, long long nrows, int nlon, int nmodes, float scale, int grid_pieces, int mode_pieces, cudaStream_t st) {
     FftPlanDev fp;
     TwoPassRows rows;
     int *h_err = nullptr;
@@ -974,7 +976,8 @@ int launch_rfft_modes(const float *in, float2 *out, long long nrows, int nlon, i
     if (rc) return rc;
     if (nrows == 0) return SHTB200_OK;
     bool done = false;
-    if ((rc = rows_twopass(rows, h_err, true, in, out, nrows, nlon, nmodes, scale / (float)nlon, st, &done)) != 0 || done) return rc;
+    if ((rc = rows_twopass(rows, h_err, true, in, out, nrows, nlon, nmodes, scale / (float)nlon, grid_pieces, mode_pieces, st, &done)) != 0 || done) return rc;
+    if (grid_pieces != 1 || mode_pieces != 1) return fail(SHTB200_EINVAL, "piece-major row transforms need a two-pass kernel for nlon, 16-byte aligned buffers and pieces that are multiples of four longitudes");
     constexpr int NW = 4;
     size_t smem = fft_smem_bytes(NW, fp);
     if ((rc = set_smem(rfft_rows_kernel<NW>, smem)) != 0) return rc;
@@ -984,7 +987,7 @@ int launch_rfft_modes(const float *in, float2 *out, long long nrows, int nlon, i
     return SHTB200_OK;
 }
 
-int launch_irfft_modes(const float2 *in, float *out, long long nrows, int nlon, int nmodes, cudaStream_t st) {
+int launch_irfft_modes(const float2 *in, float *out, long long nrows, int nlon, int nmodes, int mode_pieces, int grid_pieces, cudaStream_t st) {
     FftPlanDev fp;
     TwoPassRows rows;
     int *h_err = nullptr;
@@ -992,7 +995,8 @@ int launch_irfft_modes(const float2 *in, float *out, long long nrows, int nlon, 
     if (rc) return rc;
     if (nrows == 0) return SHTB200_OK;
     bool done = false;
-    if ((rc = rows_twopass(rows, h_err, false, in, out, nrows, nlon, nmodes, 1.f, st, &done)) != 0 || done) return rc;
+    if ((rc = rows_twopass(rows, h_err, false, in, out, nrows, nlon, nmodes, 1.f, grid_pieces, mode_pieces, st, &done)) != 0 || done) return rc;
+    if (grid_pieces != 1 || mode_pieces != 1) return fail(SHTB200_EINVAL, "piece-major row transforms need a two-pass kernel for nlon, 16-byte aligned buffers and pieces that are multiples of four longitudes");
     constexpr int NW = 4;
     size_t smem = fft_smem_bytes(NW, fp);
     if ((rc = set_smem(irfft_rows_kernel<NW>, smem)) != 0) return rc;

@@ -98,6 +98,10 @@ struct TwoPassArgs {
     long long nrows;
     int nmodes;
     float scale;
+    // ROWS kernels, piece-major buffers (what an all-to-all transpose sends / receives, see distributed/primitives.py):
+    // the longitude (grid_pieces) or order (mode_pieces) axis is cut into balanced pieces (the first n % P pieces one longer)
+    // and piece j is stored as its own contiguous (nrows, width_j) block, the blocks one after the other.  1 = plain rows.
+    int grid_pieces, mode_pieces;
 };
 
 // ROWS: transforms of item `it` that have at least one row
@@ -158,8 +162,19 @@ __global__ void __launch_bounds__(TwoPass<R1, R2>::THREADS, 2) fft_analysis_twop
             const long long r0 = 16LL * it;
             const int nr = (int)min(16LL, a.nrows - r0);
             ptx::mbar_arrive_expect_tx(bar_rows, N * 4u * (uint32_t)nr);
-            for (int u = 0; u < nr; ++u)
-                ptx::bulk_load(ptx::smem_u32(smem_tp + (u >> 1) * TS + (u & 1) * N), a.grid_in + (size_t)(r0 + u) * N, N * 4u, bar_rows);
+            if (a.grid_pieces == 1) {
+                for (int u = 0; u < nr; ++u)
+                    ptx::bulk_load(ptx::smem_u32(smem_tp + (u >> 1) * TS + (u & 1) * N), a.grid_in + (size_t)(r0 + u) * N, N * 4u, bar_rows);
+            } else {  // a row is one segment in every piece (widths are multiples of 4 floats: checked by the launcher)
+                const int q = N / a.grid_pieces, rem = N - q * a.grid_pieces;
+                for (int j = 0, s0 = 0; j < a.grid_pieces; ++j) {
+                    const int w = q + (j < rem ? 1 : 0);
+                    const float *pj = a.grid_in + (size_t)a.nrows * s0 + (size_t)r0 * w;
+                    for (int u = 0; u < nr; ++u)
+                        ptx::bulk_load(ptx::smem_u32(smem_tp + (u >> 1) * TS + (u & 1) * N + s0), pj + (size_t)u * w, w * 4u, bar_rows);
+                    s0 += w;
+                }
+            }
             return;
         }
         int kn, f0, nvalid;
@@ -244,8 +259,21 @@ __global__ void __launch_bounds__(TwoPass<R1, R2>::THREADS, 2) fft_analysis_twop
             const long long ra = 16LL * it + 2 * t;
             const bool va = ra < a.nrows, vb = ra + 1 < a.nrows;
             const int mtop = min(a.nmodes, N / 2 + 1);
+            const bool plain = a.mode_pieces == 1;
             float2 *oa = a.rows_out + (size_t)ra * a.nmodes, *ob = oa + a.nmodes;
             const float sc = 0.5f * a.scale;
+            // where order m of row r goes: plain rows, or the (nrows, width) block of the piece that holds m
+            auto slot = [&](int m, float2 **pa, float2 **pb) {
+                if (plain) {
+                    *pa = oa + m;
+                    *pb = ob + m;
+                } else {
+                    int s0, w;
+                    piece_of(m, a.nmodes, a.mode_pieces, &s0, &w);
+                    *pa = a.rows_out + (size_t)a.nrows * s0 + (size_t)ra * w + (m - s0);
+                    *pb = *pa + w;
+                }
+            };
 #pragma unroll
             for (int i = 0; i <= R2 / 2; ++i) {
                 const int m = q + R1 * i;
@@ -256,12 +284,16 @@ __global__ void __launch_bounds__(TwoPass<R1, R2>::THREADS, 2) fft_analysis_twop
                 if (m >= mtop) continue;
                 const float2 zm = u[i];
                 const float2 zn = (q == 0) ? u[(R2 - i) % R2] : (q == R1 / 2) ? give : got;
-                if (va) oa[m] = make_float2(sc * (zm.x + zn.x), sc * (zm.y - zn.y));
-                if (vb) ob[m] = make_float2(sc * (zm.y + zn.y), sc * (zn.x - zm.x));
+                float2 *pa, *pb;
+                slot(m, &pa, &pb);
+                if (va) *pa = make_float2(sc * (zm.x + zn.x), sc * (zm.y - zn.y));
+                if (vb) *pb = make_float2(sc * (zm.y + zn.y), sc * (zn.x - zm.x));
             }
             for (int m = mtop + (tid >> 3); m < a.nmodes; m += TP::THREADS >> 3) {  // beyond the Nyquist frequency: zeros
-                if (va) oa[m] = make_float2(0.f, 0.f);
-                if (vb) ob[m] = make_float2(0.f, 0.f);
+                float2 *pa, *pb;
+                slot(m, &pa, &pb);
+                if (va) *pa = make_float2(0.f, 0.f);
+                if (vb) *pb = make_float2(0.f, 0.f);
             }
         } else {
             // ---- emit: bins q + R1 i, i <= R2 / 2, are the retained orders; their mirrors come from the partner lane ----
@@ -384,8 +416,15 @@ __global__ void __launch_bounds__(TwoPass<R1, R2>::THREADS, 2) fft_synthesis_two
                     ev[c] = ov[c] = make_float2(0.f, 0.f);
                     if (i <= R2 / 2 && active && m < mtop) {
                         if (ROWS) {
-                            if (va) ev[c] = __ldg(ia + m);
-                            if (vb) ov[c] = __ldg(ib + m);
+                            const float2 *pa = ia + m, *pb = ib + m;
+                            if (a.mode_pieces != 1) {
+                                int s0, w;
+                                piece_of(m, a.nmodes, a.mode_pieces, &s0, &w);
+                                pa = a.rows_in + (size_t)a.nrows * s0 + (size_t)ra * w + (m - s0);
+                                pb = pa + w;
+                            }
+                            if (va) ev[c] = __ldg(pa);
+                            if (vb) ov[c] = __ldg(pb);
                         } else {
                             const int kf = kf_s[m];  // (rows above the group's polar extent were not produced: zeros)
                             const float *pe = yb + (size_t)(2 * m) * gstride;
@@ -471,8 +510,19 @@ __global__ void __launch_bounds__(TwoPass<R1, R2>::THREADS, 2) fft_synthesis_two
             if (tid_now() == 0) {
                 const long long r0 = 16LL * it;
                 const int nr = (int)min(16LL, a.nrows - r0);
-                for (int w = 0; w < nr; ++w)
-                    ptx::bulk_store(a.grid_out + (size_t)(r0 + w) * N, ptx::smem_u32(smem_tp + (w >> 1) * TS + (w & 1) * N), N * 4u);
+                if (a.grid_pieces == 1) {
+                    for (int w = 0; w < nr; ++w)
+                        ptx::bulk_store(a.grid_out + (size_t)(r0 + w) * N, ptx::smem_u32(smem_tp + (w >> 1) * TS + (w & 1) * N), N * 4u);
+                } else {
+                    const int q = N / a.grid_pieces, rem = N - q * a.grid_pieces;
+                    for (int j = 0, s0 = 0; j < a.grid_pieces; ++j) {
+                        const int wd = q + (j < rem ? 1 : 0);
+                        float *pj = a.grid_out + (size_t)a.nrows * s0 + (size_t)r0 * wd;
+                        for (int w = 0; w < nr; ++w)
+                            ptx::bulk_store(pj + (size_t)w * wd, ptx::smem_u32(smem_tp + (w >> 1) * TS + (w & 1) * N + s0), wd * 4u);
+                        s0 += wd;
+                    }
+                }
                 ptx::bulk_commit();
             }
         } else if (tid_now() == 0) {
@@ -616,7 +666,8 @@ int build_twopass_rows_tables(int nlon, unsigned char **d_blob, int *bytes) {
 }
 
 template <int R1, int R2>
-static int launch_rows(const TwoPassRows &tr, bool forward, const void *in, void *out, long long nrows, int nmodes, float scale, cudaStream_t st) {
+static int launch_rows(const TwoPassRows &tr, bool forward, const void *in, void *out, long long nrows, int nmodes, float scale, int grid_pieces, int mode_pieces,
+                       cudaStream_t st) {
     using TP = TwoPass<R1, R2>;
     TwoPassArgs a{};
     a.blob = tr.blob;
@@ -625,6 +676,8 @@ static int launch_rows(const TwoPassRows &tr, bool forward, const void *in, void
     a.nrows = nrows;
     a.nmodes = nmodes;
     a.scale = scale;
+    a.grid_pieces = grid_pieces;
+    a.mode_pieces = mode_pieces;
     const size_t smem = sizeof(float) * kNT * TP::TS + (size_t)tr.blob_bytes + 32;
     const long long nitems = (nrows + 15) / 16;
     if (nitems > 0x7fffffffLL) return fail(SHTB200_EINVAL, "too many rows");
@@ -644,12 +697,23 @@ static int launch_rows(const TwoPassRows &tr, bool forward, const void *in, void
     return SHTB200_OK;
 }
 
+// Piece-major buffers need every piece of the longitude axis to be a multiple of four floats wide (bulk copies move whole
+// 16-byte units) and both splits non-empty.
+bool rows_pieces_supported(int nlon, int nmodes, int grid_pieces, int mode_pieces) {
+    int r1, r2;
+    if (!twopass_supported(nlon, &r1, &r2)) return false;
+    if (grid_pieces < 1 || mode_pieces < 1 || grid_pieces > 64 || mode_pieces > 64 || nmodes < mode_pieces || nlon < grid_pieces) return false;
+    if (grid_pieces > 1 && ((nlon / grid_pieces) % 4 != 0 || nlon % grid_pieces != 0)) return false;
+    return true;
+}
+
 // forward: in = (nrows, nlon) real, out = (nrows, nmodes) complex; else the other way round.  Rows must be 16-byte aligned.
-int launch_rows_twopass(const TwoPassRows &tr, bool forward, const void *in, void *out, long long nrows, int nlon, int nmodes, float scale, cudaStream_t st) {
+int launch_rows_twopass(const TwoPassRows &tr, bool forward, const void *in, void *out, long long nrows, int nlon, int nmodes, float scale, int grid_pieces,
+                        int mode_pieces, cudaStream_t st) {
     switch (nlon) {
-        case 1440: return launch_rows<40, 36>(tr, forward, in, out, nrows, nmodes, scale, st);
-        case 720: return launch_rows<36, 20>(tr, forward, in, out, nrows, nmodes, scale, st);
-        case 512: return launch_rows<32, 16>(tr, forward, in, out, nrows, nmodes, scale, st);
+        case 1440: return launch_rows<40, 36>(tr, forward, in, out, nrows, nmodes, scale, grid_pieces, mode_pieces, st);
+        case 720: return launch_rows<36, 20>(tr, forward, in, out, nrows, nmodes, scale, grid_pieces, mode_pieces, st);
+        case 512: return launch_rows<32, 16>(tr, forward, in, out, nrows, nmodes, scale, grid_pieces, mode_pieces, st);
     }
     return fail(SHTB200_EINVAL, "no two-pass FFT kernel for this nlon");
 }

@@ -98,7 +98,7 @@ __global__ void pack_table_blocks_kernel(TableView tv, float *A, const long long
 
 // Ct[((b0[g] - b0[2 m0]) + kb) * ncols + col][kk]
 __global__ void pack_coeffs_kernel(const float2 *__restrict__ c, float *__restrict__ Ct, const long long *b0, const int *gkb, const int *gkb0, int ncols,
-                                   int lmax, int mloc, int m0, int mbase, int vector) {
+                                   int lmax, int mloc, int m0, int mbase, int vector, RowPieces rp) {
     const int gl = blockIdx.y;             // group inside the call's orders
     const int m = m0 + (gl >> 1), p = gl & 1;
     const int g = gl + 2 * (m0 - mbase);   // group inside the plan
@@ -114,7 +114,7 @@ __global__ void pack_coeffs_kernel(const float2 *__restrict__ c, float *__restri
         if (!vector) {
             const int l = m + p + 2 * (kb * kBK + kk);
             if (l < lmax) {
-                float2 z = c[((size_t)(col >> 1) * lmax + l) * mloc + (m - m0)];
+                float2 z = c[piece_row(rp, col >> 1, lmax, l) * mloc + (m - m0)];
                 v = (col & 1) ? z.y : z.x;
             }
         } else {
@@ -130,7 +130,7 @@ __global__ void pack_coeffs_kernel(const float2 *__restrict__ c, float *__restri
                 } else {   // m / sin(theta) table
                     comp = (cc < 2) ? 1 : 0; im = 1 - (cc & 1); sg = (cc == 0 || cc == 2) ? -1.f : 1.f;
                 }
-                float2 z = c[((size_t)(pair * 2 + comp) * lmax + l) * mloc + (m - m0)];
+                float2 z = c[piece_row(rp, pair * 2 + comp, lmax, l) * mloc + (m - m0)];
                 v = sg * (im ? z.y : z.x);
             }
         }
@@ -157,7 +157,7 @@ __device__ __forceinline__ int tile_swz(int ll) { return 2 * ((ll >> 3) & 7) + (
 
 template <bool TO_SLABS>
 __global__ void __launch_bounds__(256) coeff_slab_transpose_kernel(float2 *__restrict__ c, float *__restrict__ S, const long long *__restrict__ slab0,
-                                                                   const int *__restrict__ gkb, int ncols, int lmax, int mloc, int m0, int nsb, int mbase) {
+                                                                   const int *__restrict__ gkb, int ncols, int lmax, int mloc, int m0, int nsb, int mbase, RowPieces rp) {
     __shared__ float2 T[kTileRows][32];
     const int mb0 = blockIdx.x * 32, f = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -169,7 +169,7 @@ __global__ void __launch_bounds__(256) coeff_slab_transpose_kernel(float2 *__res
         const int t = blockIdx.y - nsb;
         const int hi = m0 + mb0 - 64 * t, lo = max(hi - 64, 0);
         for (int l = lo + warp; l < min(hi, lmax); l += 8)
-            if (mi_l < mloc) c[((size_t)f * lmax + l) * mloc + mi_l] = make_float2(0.f, 0.f);
+            if (mi_l < mloc) c[piece_row(rp, f, lmax, l) * mloc + mi_l] = make_float2(0.f, 0.f);
         return;
     }
     const int sb = blockIdx.y;
@@ -180,14 +180,13 @@ __global__ void __launch_bounds__(256) coeff_slab_transpose_kernel(float2 *__res
     if (TO_SLABS) {
         // all twelve loads of a thread are in flight before the first store
         float2 v[kTileRows / 8];
-        const float2 *crow = c + ((size_t)f * lmax + lbase + warp) * mloc + mi_l;  // row ll = warp, then 8 rows further per step
-        const int d0 = warp - lane, lrem = lmax - lbase - warp;                    // d = l - m - 64 sb; rows left below lmax
+        const int d0 = warp - lane, lrem = lmax - lbase - warp;  // d = l - m - 64 sb; rows left below lmax (row ll = warp, then 8 further per step)
         const bool colok = mi_l < mloc;
 #pragma unroll
         for (int it = 0; it < kTileRows / 8; ++it) {
             const int d = d0 + 8 * it;
             v[it] = make_float2(0.f, 0.f);
-            if (colok && d >= 0 && d < 64 && 8 * it < lrem) v[it] = __ldg(crow + (size_t)(8 * it) * mloc);
+            if (colok && d >= 0 && d < 64 && 8 * it < lrem) v[it] = __ldg(c + piece_row(rp, f, lmax, lbase + warp + 8 * it) * mloc + mi_l);
         }
 #pragma unroll
         for (int it = 0; it < kTileRows / 8; ++it) {
@@ -246,15 +245,15 @@ __global__ void __launch_bounds__(256) coeff_slab_transpose_kernel(float2 *__res
     }
     if (!TO_SLABS) {
         __syncthreads();
-        float2 *crow = c + ((size_t)f * lmax + lbase + warp) * mloc + mi_l;
         const int d0 = warp - lane, lrem = lmax - lbase - warp;
         if (mi_l < mloc) {
 #pragma unroll
             for (int it = 0; it < kTileRows / 8; ++it) {
                 const int ll = warp + 8 * it, d = d0 + 8 * it;
                 if (8 * it >= lrem) break;
-                if (d >= 0 && d < 64) crow[(size_t)(8 * it) * mloc] = T[ll][lane ^ tile_swz(ll)];
-                else if (d < 0 && sb == 0) crow[(size_t)(8 * it) * mloc] = make_float2(0.f, 0.f);  // l < m
+                float2 *crow = c + piece_row(rp, f, lmax, lbase + ll) * mloc + mi_l;
+                if (d >= 0 && d < 64) *crow = T[ll][lane ^ tile_swz(ll)];
+                else if (d < 0 && sb == 0) *crow = make_float2(0.f, 0.f);  // l < m
             }
         }
     }
@@ -269,7 +268,7 @@ __global__ void __launch_bounds__(256) coeff_slab_transpose_kernel(float2 *__res
 // (component / part / sign pattern of torch_harmonics/sht.py:638-643).  One CTA: 32 orders x one slab index x one component field.
 __global__ void __launch_bounds__(256) coeff_slab_transpose_vec_kernel(const float2 *__restrict__ c, float *__restrict__ S, const long long *__restrict__ b0,
                                                                        const int *__restrict__ gkb, const int *__restrict__ gkb0, int ncols, int lmax, int mloc,
-                                                                       int m0, int mbase) {
+                                                                       int m0, int mbase, RowPieces rp) {
     __shared__ float2 T[kTileRows][32];
     const int mb0 = blockIdx.x * 32, sb = blockIdx.y, cf = blockIdx.z;  // cf = 2 pair + component
     const int pair = cf >> 1, comp = cf & 1;
@@ -279,14 +278,13 @@ __global__ void __launch_bounds__(256) coeff_slab_transpose_vec_kernel(const flo
     if (lbase >= lmax) return;  // no degree of this band exists for any order of the tile
     {
         float2 v[kTileRows / 8];
-        const float2 *crow = c + ((size_t)cf * lmax + lbase + warp) * mloc + mi_l;
         const int d0 = warp - lane, lrem = lmax - lbase - warp;
         const bool colok = mi_l < mloc;
 #pragma unroll
         for (int it = 0; it < kTileRows / 8; ++it) {
             const int d = d0 + 8 * it;
             v[it] = make_float2(0.f, 0.f);
-            if (colok && d >= 0 && d < 64 && 8 * it < lrem) v[it] = __ldg(crow + (size_t)(8 * it) * mloc);
+            if (colok && d >= 0 && d < 64 && 8 * it < lrem) v[it] = __ldg(c + piece_row(rp, cf, lmax, lbase + warp + 8 * it) * mloc + mi_l);
         }
 #pragma unroll
         for (int it = 0; it < kTileRows / 8; ++it) {
@@ -323,7 +321,8 @@ __global__ void __launch_bounds__(256) coeff_slab_transpose_vec_kernel(const flo
 // Xc (field, k, mloc) complex -> X[blocked_row(2 mi + p, k')][2 f + ri] (row pitch ncp); rows k' >= Kh of the last
 // 32-row block are written as zeros.  The input is contiguous along the orders, the output along the fields: a CTA moves
 // a 32 (orders) x 32 (fields) tile of one folded latitude through shared memory, so that both sides see 256-byte runs.
-__global__ void __launch_bounds__(256) fold_modes_kernel(const float2 *__restrict__ Xc, float *__restrict__ X, int nfields, int nlat, int Kh, int ncp, int mloc) {
+__global__ void __launch_bounds__(256) fold_modes_kernel(const float2 *__restrict__ Xc, float *__restrict__ X, int nfields, int nlat, int Kh, int ncp, int mloc,
+                                                         RowPieces rp) {
     __shared__ float2 E[32][33], O[32][33];
     const int mi0 = blockIdx.x * 32, k = blockIdx.y, f0 = blockIdx.z * 32;
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
@@ -335,10 +334,10 @@ __global__ void __launch_bounds__(256) fold_modes_kernel(const float2 *__restric
             const int f = f0 + ty + 8 * i;
             float2 e = make_float2(0.f, 0.f), o = e;
             if (f < nfields && mi < mloc) {
-                const float2 a = __ldg(Xc + ((size_t)f * nlat + k) * mloc + mi);
+                const float2 a = __ldg(Xc + piece_row(rp, f, nlat, k) * mloc + mi);
                 e = a;
                 if (ks != k) {
-                    const float2 b = __ldg(Xc + ((size_t)f * nlat + ks) * mloc + mi);
+                    const float2 b = __ldg(Xc + piece_row(rp, f, nlat, ks) * mloc + mi);
                     e = make_float2(a.x + b.x, a.y + b.y);
                     o = make_float2(a.x - b.x, a.y - b.y);
                 }
@@ -364,7 +363,7 @@ __global__ void __launch_bounds__(256) fold_modes_kernel(const float2 *__restric
 // (the layout fft_analysis_kernel<.., 2, ..> emits): columns 4 f .. 4 f + 3 feed (s_re, s_im, t_re, t_im); rows
 // k' < Kh contract against the d/dtheta table and carry the fold of parity 1 - p, rows Kh + k' against the
 // m/sin(theta) table with the fold of parity p; signs as in torch_harmonics/sht.py:488-493.
-__global__ void fold_modes_vec_kernel(const float2 *__restrict__ Xc, float *__restrict__ X, int npairs, int nlat, int Kh, int ncp, int mloc) {
+__global__ void fold_modes_vec_kernel(const float2 *__restrict__ Xc, float *__restrict__ X, int npairs, int nlat, int Kh, int ncp, int mloc, RowPieces rp) {
     const int Ka = 2 * Kh, Kr = (Ka + kBK - 1) / kBK * kBK;
     const int ngroups = 2 * mloc;
     const long long total = (long long)mloc * (Kh + (Kr - Ka)) * npairs;
@@ -381,11 +380,11 @@ __global__ void fold_modes_vec_kernel(const float2 *__restrict__ Xc, float *__re
         const int ks = nlat - 1 - k;
         float2 e[2], o[2];
         for (int comp = 0; comp < 2; ++comp) {
-            const float2 a = Xc[(((size_t)f * 2 + comp) * nlat + k) * mloc + mi];
+            const float2 a = Xc[piece_row(rp, 2 * f + comp, nlat, k) * mloc + mi];
             e[comp] = a;
             o[comp] = make_float2(0.f, 0.f);
             if (ks != k) {
-                const float2 b = Xc[(((size_t)f * 2 + comp) * nlat + ks) * mloc + mi];
+                const float2 b = Xc[piece_row(rp, 2 * f + comp, nlat, ks) * mloc + mi];
                 e[comp] = make_float2(a.x + b.x, a.y + b.y);
                 o[comp] = make_float2(a.x - b.x, a.y - b.y);
             }
@@ -402,7 +401,7 @@ __global__ void fold_modes_vec_kernel(const float2 *__restrict__ Xc, float *__re
 // (rows above krow0[2 (m0 + mi) + p] were not produced by the contraction: they count as zeros; m0 here = first order of
 // the call relative to the plan's first order)
 __global__ void __launch_bounds__(256) unfold_modes_kernel(const float *__restrict__ Y, float2 *__restrict__ Xc, int nfields, int nlat, int Kh, int ncp, int mloc,
-                                                           const int *__restrict__ krow0, int m0) {
+                                                           const int *__restrict__ krow0, int m0, RowPieces rp) {
     __shared__ float2 E[32][33], O[32][33];
     const int mi0 = blockIdx.x * 32, k = blockIdx.y, f0 = blockIdx.z * 32;
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
@@ -429,8 +428,8 @@ __global__ void __launch_bounds__(256) unfold_modes_kernel(const float *__restri
         const int f = f0 + ty + 8 * i;
         if (f >= nfields) continue;
         const float2 e = E[tx][ty + 8 * i], o = O[tx][ty + 8 * i];
-        Xc[((size_t)f * nlat + k) * mloc + mi] = make_float2(e.x + o.x, e.y + o.y);
-        if (ks != k) Xc[((size_t)f * nlat + ks) * mloc + mi] = make_float2(e.x - o.x, e.y - o.y);
+        Xc[piece_row(rp, f, nlat, k) * mloc + mi] = make_float2(e.x + o.x, e.y + o.y);
+        if (ks != k) Xc[piece_row(rp, f, nlat, ks) * mloc + mi] = make_float2(e.x - o.x, e.y - o.y);
     }
 }
 
@@ -475,67 +474,80 @@ int launch_polar_extent(const Plan &pl, const float *table, float rel, std::vect
     return SHTB200_OK;
 }
 
-int launch_pack_coeffs(const Plan &pl, const float2 *c, float *Ct, int nfields, int m0, int mloc, cudaStream_t st) {
+// `pieces` (all four launchers): the (field, row, order) tensor is piece-major along its row axis (see RowPieces); 1 = plain
+int launch_pack_coeffs(const Plan &pl, const float2 *c, float *Ct, int nfields, int m0, int mloc, int pieces, cudaStream_t st) {
     const int ncols = (pl.vector ? 4 : 2) * nfields;
     if (mloc == 0 || ncols == 0) return SHTB200_OK;
+    RowPieces rp;
+    rp.P = pieces;
+    rp.nF = pl.vector ? 2 * nfields : nfields;
     if (!pl.vector && nfields <= 65535) {
         const int nsb = ceil_div(pl.Lh, kBK);  // slabs of the longest group
         dim3 grid(ceil_div(mloc, 32), nsb, nfields);
-        coeff_slab_transpose_kernel<true><<<grid, 256, 0, st>>>(const_cast<float2 *>(c), Ct, pl.d_gb0, pl.d_gkb, ncols, pl.lmax, mloc, m0, nsb, pl.m_base);
+        coeff_slab_transpose_kernel<true><<<grid, 256, 0, st>>>(const_cast<float2 *>(c), Ct, pl.d_gb0, pl.d_gkb, ncols, pl.lmax, mloc, m0, nsb, pl.m_base, rp);
         SHT_CUDA_CHECK(cudaGetLastError());
         return SHTB200_OK;
     }
     if (pl.vector && 2 * nfields <= 65535) {
         dim3 grid(ceil_div(mloc, 32), ceil_div(pl.Lh, kBK), 2 * nfields);
-        coeff_slab_transpose_vec_kernel<<<grid, 256, 0, st>>>(c, Ct, pl.d_gb0, pl.d_gkb, pl.d_gkb0, ncols, pl.lmax, mloc, m0, pl.m_base);
+        coeff_slab_transpose_vec_kernel<<<grid, 256, 0, st>>>(c, Ct, pl.d_gb0, pl.d_gkb, pl.d_gkb0, ncols, pl.lmax, mloc, m0, pl.m_base, rp);
         SHT_CUDA_CHECK(cudaGetLastError());
         return SHTB200_OK;
     }
     const long long per_group = (long long)ceil_div(pl.Lh, kBK) * pl.ncomp * ncols * kBK;
     dim3 grid(grid_x_for(per_group), 2 * mloc);
-    pack_coeffs_kernel<<<grid, 256, 0, st>>>(c, Ct, pl.d_gb0, pl.d_gkb, pl.d_gkb0, ncols, pl.lmax, mloc, m0, pl.m_base, pl.vector ? 1 : 0);
+    pack_coeffs_kernel<<<grid, 256, 0, st>>>(c, Ct, pl.d_gb0, pl.d_gkb, pl.d_gkb0, ncols, pl.lmax, mloc, m0, pl.m_base, pl.vector ? 1 : 0, rp);
     SHT_CUDA_CHECK(cudaGetLastError());
     return SHTB200_OK;
 }
 
-int launch_unpack_coeffs(const Plan &pl, const float *Z, float2 *c, int nfields, int m0, int mloc, cudaStream_t st) {
+int launch_unpack_coeffs(const Plan &pl, const float *Z, float2 *c, int nfields, int m0, int mloc, int pieces, cudaStream_t st) {
     if (mloc == 0 || nfields == 0) return SHTB200_OK;
     if (pl.vector) nfields *= 2;  // a vector pair is two output fields (spheroidal, toroidal) side by side
+    RowPieces rp;
+    rp.P = pieces;
+    rp.nF = nfields;
     if (nfields > 65535) return fail(SHTB200_EINVAL, "too many fields in one call (limit 65535)");
     const int nsb = ceil_div(pl.Lh, kBK);
     // extra tile rows for the degrees above the diagonal of the last order block: l < m0 + 32 (blocks - 1)
     const int nzero = ceil_div(std::min(m0 + 32 * (ceil_div(mloc, 32) - 1), pl.lmax), 64);
     dim3 grid(ceil_div(mloc, 32), nsb + nzero, nfields);
-    coeff_slab_transpose_kernel<false><<<grid, 256, 0, st>>>(c, const_cast<float *>(Z), pl.d_gb0, pl.d_gkb, 2 * nfields, pl.lmax, mloc, m0, nsb, pl.m_base);
+    coeff_slab_transpose_kernel<false><<<grid, 256, 0, st>>>(c, const_cast<float *>(Z), pl.d_gb0, pl.d_gkb, 2 * nfields, pl.lmax, mloc, m0, nsb, pl.m_base, rp);
     SHT_CUDA_CHECK(cudaGetLastError());
     return SHTB200_OK;
 }
 
-int launch_fold_modes(const Plan &pl, const float2 *Xc, float *X, int nfields, int m0, int mloc, cudaStream_t st) {
+int launch_fold_modes(const Plan &pl, const float2 *Xc, float *X, int nfields, int m0, int mloc, int pieces, cudaStream_t st) {
     (void)m0;
+    RowPieces rp;
+    rp.P = pieces;
+    rp.nF = pl.vector ? 2 * nfields : nfields;
     if (pl.vector) {
         const int pad = (int)(round_up(pl.Ka, kBK) - pl.Ka);
         const long long total = (long long)mloc * nfields * (pl.Kh + pad);
         if (total == 0) return SHTB200_OK;
-        fold_modes_vec_kernel<<<grid_x_for(total), 256, 0, st>>>(Xc, X, nfields, pl.nlat, pl.Kh, (int)col_pitch(4 * nfields), mloc);
+        fold_modes_vec_kernel<<<grid_x_for(total), 256, 0, st>>>(Xc, X, nfields, pl.nlat, pl.Kh, (int)col_pitch(4 * nfields), mloc, rp);
         SHT_CUDA_CHECK(cudaGetLastError());
         return SHTB200_OK;
     }
     if (mloc == 0 || nfields == 0) return SHTB200_OK;
     if (ceil_div(nfields, 32) > 65535) return fail(SHTB200_EINVAL, "too many fields in one call");
     dim3 grid(ceil_div(mloc, 32), (unsigned)round_up(pl.Kh, kBK), ceil_div(nfields, 32));
-    fold_modes_kernel<<<grid, 256, 0, st>>>(Xc, X, nfields, pl.nlat, pl.Kh, (int)col_pitch(2 * nfields), mloc);
+    fold_modes_kernel<<<grid, 256, 0, st>>>(Xc, X, nfields, pl.nlat, pl.Kh, (int)col_pitch(2 * nfields), mloc, rp);
     SHT_CUDA_CHECK(cudaGetLastError());
     return SHTB200_OK;
 }
 
-int launch_unfold_modes(const Plan &pl, const float *Y, float2 *Xc, int nfields, int m0, int mloc, cudaStream_t st) {
+int launch_unfold_modes(const Plan &pl, const float *Y, float2 *Xc, int nfields, int m0, int mloc, int pieces, cudaStream_t st) {
     // a vector pair is two complex fields side by side (theta, phi): same kernel on 2 x nfields fields
     const int nf = pl.vector ? 2 * nfields : nfields;
+    RowPieces rp;
+    rp.P = pieces;
+    rp.nF = nf;
     if (nf == 0 || mloc == 0) return SHTB200_OK;
     if (ceil_div(nf, 32) > 65535) return fail(SHTB200_EINVAL, "too many fields in one call");
     dim3 grid(ceil_div(mloc, 32), pl.Kh, ceil_div(nf, 32));
-    unfold_modes_kernel<<<grid, 256, 0, st>>>(Y, Xc, nf, pl.nlat, pl.Kh, (int)col_pitch(2 * nf), mloc, pl.d_krow0, m0 - pl.m_base);
+    unfold_modes_kernel<<<grid, 256, 0, st>>>(Y, Xc, nf, pl.nlat, pl.Kh, (int)col_pitch(2 * nf), mloc, pl.d_krow0, m0 - pl.m_base, rp);
     SHT_CUDA_CHECK(cudaGetLastError());
     return SHTB200_OK;
 }

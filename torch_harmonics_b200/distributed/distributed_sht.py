@@ -22,13 +22,15 @@ from ..quadrature import sht_colatitudes
 from ..sht import _check, _default_engine, _require
 from ..truncation import truncate_sht
 from .primitives import (
+    _pieces_exchange_in,
+    _pieces_exchange_out,
     compute_split_shapes,
     distributed_transpose_azimuth,
     distributed_transpose_polar,
     flatten_and_pad_leading_dims,
     unpad_and_unflatten_leading_dims,
 )
-from .utils import azimuth_group_rank, azimuth_group_size, polar_group_rank, polar_group_size
+from .utils import azimuth_group, azimuth_group_rank, azimuth_group_size, polar_group, polar_group_rank, polar_group_size
 
 
 def _stream(t):
@@ -94,6 +96,66 @@ class _IrfftStage(torch.autograd.Function):
         return _zero_edge_imag(r * w, ctx.nlon), None
 
 
+class _AzimuthRfft(torch.autograd.Function):
+    """The azimuth sandwich of the forward transforms in one step: exchange (fields scattered, longitudes gathered), row
+    FFT, exchange (orders scattered, fields gathered) - ``(n, ..., nlon_local)`` float32 -> ``(n, ..., mmax_local)``
+    complex64.  The FFT kernel reads the first exchange's receive buffer and writes the second one's send buffer in their
+    piece-major form, so no copy sits between the three (the separate transposes concatenate / split one tensor each).
+    The backward pass is the chain of the separate, differentiable steps."""
+
+    @staticmethod
+    def forward(ctx, x, owner, scale):
+        group, A = azimuth_group(), owner.comm_size_azimuth
+        n, mid = x.shape[0], tuple(x.shape[1:-1])
+        ctx.owner, ctx.scale, ctx.n, ctx.lead = owner, scale, n, -x.dim()
+        recv, n_loc = _pieces_exchange_in(_lib.dense(x), owner.lon_shapes, group)
+        rows = n_loc
+        for s in mid:
+            rows *= s
+        spec = torch.empty(rows * owner.mmax * 2, dtype=torch.float32, device=x.device)
+        with torch.cuda.device(x.device):
+            _lib.check(_lib.load().shtb200_rfft_modes_pieces(ctypes.c_void_p(recv.data_ptr()), ctypes.c_void_p(spec.data_ptr()), rows, owner.nlon, owner.mmax, scale, A, A,
+                                                              _stream(x)), "shtb200_rfft_modes_pieces")
+        return _pieces_exchange_out(spec, n_loc, n, mid + (0,), -1, owner.m_shapes, True, group)
+
+    @staticmethod
+    def backward(ctx, g):
+        o, lead = ctx.owner, ctx.lead
+        g = distributed_transpose_azimuth(g, (lead, -1), o.m_shapes)
+        w = _edge_weights(o.mmax, o.nlon, 0.5, g.device) * (ctx.scale / o.nlon)
+        g = _IrfftStage.apply((g * w).contiguous(), o.nlon)
+        return distributed_transpose_azimuth(g, (-1, lead), compute_split_shapes(ctx.n, o.comm_size_azimuth)), None, None
+
+
+class _AzimuthIrfft(torch.autograd.Function):
+    """The azimuth sandwich of the inverse transforms: exchange (fields scattered, orders gathered), inverse row FFT,
+    exchange (longitudes scattered, fields gathered) - ``(n, ..., mmax_local)`` complex64 -> ``(n, ..., nlon_local)``
+    float32, piece-major in between like :class:`_AzimuthRfft`."""
+
+    @staticmethod
+    def forward(ctx, c, owner):
+        group, A = azimuth_group(), owner.comm_size_azimuth
+        n, mid = c.shape[0], tuple(c.shape[1:-1])
+        ctx.owner, ctx.n, ctx.lead = owner, n, -c.dim()
+        recv, n_loc = _pieces_exchange_in(_lib.dense(c), owner.m_shapes, group)
+        rows = n_loc
+        for s in mid:
+            rows *= s
+        grid = torch.empty(rows * owner.nlon, dtype=torch.float32, device=c.device)
+        with torch.cuda.device(c.device):
+            _lib.check(_lib.load().shtb200_irfft_modes_pieces(ctypes.c_void_p(recv.data_ptr()), ctypes.c_void_p(grid.data_ptr()), rows, owner.nlon, owner.mmax, A, A,
+                                                               _stream(c)), "shtb200_irfft_modes_pieces")
+        return _pieces_exchange_out(grid, n_loc, n, mid + (0,), -1, owner.lon_shapes, False, group)
+
+    @staticmethod
+    def backward(ctx, g):
+        o, lead = ctx.owner, ctx.lead
+        g = distributed_transpose_azimuth(g, (lead, -1), o.lon_shapes)
+        r = _RfftStage.apply(g.contiguous(), o.mmax, float(o.nlon))
+        r = _zero_edge_imag(r * _edge_weights(o.mmax, o.nlon, 2.0, g.device), o.nlon)
+        return distributed_transpose_azimuth(r, (-1, lead), compute_split_shapes(ctx.n, o.comm_size_azimuth)), None
+
+
 class _LegendreStage(torch.autograd.Function):
     """Contraction with the packed table for the local orders [m0, m0 + mloc): (N, nlat, mloc) <-> (N, lmax, mloc);
     vector plans carry the component axis, (N, 2, nlat, mloc) <-> (N, 2, lmax, mloc)."""
@@ -115,6 +177,37 @@ class _LegendreStage(torch.autograd.Function):
     @staticmethod
     def backward(ctx, g):
         return _LegendreStage.apply(g.contiguous(), ctx.owner, not ctx.adjoint, ctx.in_rows), None, None, None
+
+
+class _PolarLegendre(torch.autograd.Function):
+    """The polar sandwich in one step: exchange (fields scattered, latitudes / degrees gathered), contraction, exchange
+    (degrees / latitudes scattered, fields gathered) - ``(n, ..., rows_in_local, mloc)`` -> ``(n, ..., rows_out_local, mloc)``
+    complex64.  The contraction's fold / unfold and coefficient kernels read the first exchange's receive buffer and write
+    the second one's send buffer in their piece-major form (``shtb200_legendre_pieces``): no copy in between.  The backward
+    pass is the chain of the separate, differentiable steps."""
+
+    @staticmethod
+    def forward(ctx, x, owner, in_splits, out_splits):
+        group, P = polar_group(), owner.comm_size_polar
+        n, rest, mloc = x.shape[0], list(x.shape[1:]), x.shape[-1]
+        ctx.owner, ctx.n, ctx.lead, ctx.in_splits, ctx.out_splits = owner, n, -x.dim(), in_splits, out_splits
+        recv, n_loc = _pieces_exchange_in(_lib.dense(x), in_splits, group, axis=-2)
+        comp = 1
+        for s in rest[:-2]:
+            comp *= s
+        out = torch.empty(n_loc * comp * sum(out_splits) * mloc * 2, dtype=torch.float32, device=x.device)
+        plan = owner._plan(x.device, False)
+        ws = torch.empty(max(plan.legendre_workspace_bytes(n_loc, mloc), 1), dtype=torch.uint8, device=x.device)
+        with torch.cuda.device(x.device):
+            plan.legendre(recv, out, n_loc, owner._m0, mloc, ws, torch.cuda.current_stream(x.device).cuda_stream, in_pieces=P, out_pieces=P)
+        return _pieces_exchange_out(out, n_loc, n, rest, -2, out_splits, True, group)
+
+    @staticmethod
+    def backward(ctx, g):
+        o, lead = ctx.owner, ctx.lead
+        g = distributed_transpose_polar(g, (lead, -2), ctx.out_splits)
+        g = _LegendreStage.apply(g.contiguous(), o, True, sum(ctx.in_splits))
+        return distributed_transpose_polar(g, (-2, lead), compute_split_shapes(ctx.n, o.comm_size_polar)), None, None, None
 
 
 class _DistributedBase(nn.Module):
@@ -162,6 +255,50 @@ class _DistributedBase(nn.Module):
     # Number of field chunks the inference path pipelines (0 / 1 switches it off) and the smallest local tensor worth it.
     pipeline_chunks = 4
     pipeline_min_bytes = 64 << 20
+
+    fuse_azimuth_fft = True  # exchange - row FFT - exchange without copies in between, where the row kernels support it
+
+    def _rfft_stages(self, lead):
+        """Stages of the forward transforms between the local grid tile and (fields, ..., local orders)."""
+        A = self.comm_size_azimuth
+        if A > 1 and self.fuse_azimuth_fft and _lib.rows_pieces_supported(self.nlon, self.mmax, A, A):
+            return [lambda t, n: _AzimuthRfft.apply(t, self, 2.0 * math.pi)]
+        stages = []
+        if A > 1:  # fields get sharded over the azimuth group, longitudes become local
+            stages.append(lambda t, n: distributed_transpose_azimuth(t, (lead, -1), self.lon_shapes))
+        stages.append(lambda t, n: _RfftStage.apply(t, self.mmax, 2.0 * math.pi))
+        if A > 1:  # orders get sharded, fields local again
+            stages.append(lambda t, n: distributed_transpose_azimuth(t, (-1, lead), compute_split_shapes(n, A)))
+        return stages
+
+    fuse_polar_legendre = True  # exchange - contraction - exchange without copies in between
+
+    def _legendre_stages(self, lead, in_splits, out_splits):
+        """Stages between (fields, ..., local latitudes | degrees, local orders) and (fields, ..., local degrees | latitudes,
+        local orders): ``in_splits`` / ``out_splits`` are the polar group's chunks of the contracted / produced axis."""
+        P = self.comm_size_polar
+        if P > 1 and self.fuse_polar_legendre:
+            return [lambda t, n: _PolarLegendre.apply(t, self, in_splits, out_splits)]
+        stages = []
+        if P > 1:  # fields get sharded over the polar group, the contracted axis becomes local
+            stages.append(lambda t, n: distributed_transpose_polar(t, (lead, -2), in_splits))
+        stages.append(lambda t, n: _LegendreStage.apply(t, self, False, sum(out_splits)))
+        if P > 1:  # the produced axis gets sharded, fields local again
+            stages.append(lambda t, n: distributed_transpose_polar(t, (-2, lead), compute_split_shapes(n, P)))
+        return stages
+
+    def _irfft_stages(self, lead):
+        """Stages of the inverse transforms between (fields, ..., local orders) and the local grid tile."""
+        A = self.comm_size_azimuth
+        if A > 1 and self.fuse_azimuth_fft and _lib.rows_pieces_supported(self.nlon, self.mmax, A, A):
+            return [lambda t, n: _AzimuthIrfft.apply(t, self)]
+        stages = []
+        if A > 1:
+            stages.append(lambda t, n: distributed_transpose_azimuth(t, (lead, -1), self.m_shapes))
+        stages.append(lambda t, n: _IrfftStage.apply(t, self.nlon))
+        if A > 1:
+            stages.append(lambda t, n: distributed_transpose_azimuth(t, (-1, lead), compute_split_shapes(n, A)))
+        return stages
 
     def _run_stages(self, x, stages):
         """Apply the stage functions ``stage(tensor, nfields)`` to the flattened batch ``x`` (fields on axis 0; ``nfields`` is
@@ -232,18 +369,7 @@ class DistributedRealSHT(_DistributedBase):
         _require(x, torch.float32, "DistributedRealSHT")
 
         x, lead_shape, lead_size = flatten_and_pad_leading_dims(x, max(self.comm_size_polar, self.comm_size_azimuth))
-        A, P = self.comm_size_azimuth, self.comm_size_polar
-        stages = []
-        if A > 1:  # fields get sharded over the azimuth group, longitudes become local
-            stages.append(lambda t, n: distributed_transpose_azimuth(t, (-3, -1), self.lon_shapes))
-        stages.append(lambda t, n: _RfftStage.apply(t, self.mmax, 2.0 * math.pi))
-        if A > 1:  # orders get sharded, fields local again
-            stages.append(lambda t, n: distributed_transpose_azimuth(t, (-1, -3), compute_split_shapes(n, A)))
-        if P > 1:  # fields get sharded over the polar group, latitudes become local
-            stages.append(lambda t, n: distributed_transpose_polar(t, (-3, -2), self.lat_shapes))
-        stages.append(lambda t, n: _LegendreStage.apply(t, self, False, self.lmax))
-        if P > 1:  # degrees get sharded, fields local again
-            stages.append(lambda t, n: distributed_transpose_polar(t, (-2, -3), compute_split_shapes(n, P)))
+        stages = self._rfft_stages(-3) + self._legendre_stages(-3, self.lat_shapes, self.l_shapes)
         x = self._run_stages(x, stages)
         return unpad_and_unflatten_leading_dims(x, lead_shape, lead_size)
 
@@ -268,18 +394,7 @@ class DistributedInverseRealSHT(_DistributedBase):
         _require(x, torch.complex64, "DistributedInverseRealSHT")
 
         x, lead_shape, lead_size = flatten_and_pad_leading_dims(x, max(self.comm_size_polar, self.comm_size_azimuth))
-        A, P = self.comm_size_azimuth, self.comm_size_polar
-        stages = []
-        if P > 1:
-            stages.append(lambda t, n: distributed_transpose_polar(t, (-3, -2), self.l_shapes))
-        stages.append(lambda t, n: _LegendreStage.apply(t, self, False, self.nlat))
-        if P > 1:
-            stages.append(lambda t, n: distributed_transpose_polar(t, (-2, -3), compute_split_shapes(n, P)))
-        if A > 1:
-            stages.append(lambda t, n: distributed_transpose_azimuth(t, (-3, -1), self.m_shapes))
-        stages.append(lambda t, n: _IrfftStage.apply(t, self.nlon))
-        if A > 1:
-            stages.append(lambda t, n: distributed_transpose_azimuth(t, (-1, -3), compute_split_shapes(n, A)))
+        stages = self._legendre_stages(-3, self.l_shapes, self.lat_shapes) + self._irfft_stages(-3)
         x = self._run_stages(x, stages)
         return unpad_and_unflatten_leading_dims(x, lead_shape, lead_size)
 
@@ -312,18 +427,7 @@ class DistributedRealVectorSHT(_DistributedBase):
         _require(x, torch.float32, "DistributedRealVectorSHT")
 
         x, lead_shape, lead_size = flatten_and_pad_leading_dims(x, max(self.comm_size_polar, self.comm_size_azimuth), num_trailing_dims=3)
-        A, P = self.comm_size_azimuth, self.comm_size_polar
-        stages = []
-        if A > 1:
-            stages.append(lambda t, n: distributed_transpose_azimuth(t, (-4, -1), self.lon_shapes))
-        stages.append(lambda t, n: _RfftStage.apply(t, self.mmax, 2.0 * math.pi))
-        if A > 1:
-            stages.append(lambda t, n: distributed_transpose_azimuth(t, (-1, -4), compute_split_shapes(n, A)))
-        if P > 1:
-            stages.append(lambda t, n: distributed_transpose_polar(t, (-4, -2), self.lat_shapes))
-        stages.append(lambda t, n: _LegendreStage.apply(t, self, False, self.lmax))
-        if P > 1:
-            stages.append(lambda t, n: distributed_transpose_polar(t, (-2, -4), compute_split_shapes(n, P)))
+        stages = self._rfft_stages(-4) + self._legendre_stages(-4, self.lat_shapes, self.l_shapes)
         x = self._run_stages(x, stages)
         return unpad_and_unflatten_leading_dims(x, lead_shape, lead_size, num_trailing_dims=3)
 
@@ -350,17 +454,6 @@ class DistributedInverseRealVectorSHT(_DistributedBase):
         _require(x, torch.complex64, "DistributedInverseRealVectorSHT")
 
         x, lead_shape, lead_size = flatten_and_pad_leading_dims(x, max(self.comm_size_polar, self.comm_size_azimuth), num_trailing_dims=3)
-        A, P = self.comm_size_azimuth, self.comm_size_polar
-        stages = []
-        if P > 1:
-            stages.append(lambda t, n: distributed_transpose_polar(t, (-4, -2), self.l_shapes))
-        stages.append(lambda t, n: _LegendreStage.apply(t, self, False, self.nlat))
-        if P > 1:
-            stages.append(lambda t, n: distributed_transpose_polar(t, (-2, -4), compute_split_shapes(n, P)))
-        if A > 1:
-            stages.append(lambda t, n: distributed_transpose_azimuth(t, (-4, -1), self.m_shapes))
-        stages.append(lambda t, n: _IrfftStage.apply(t, self.nlon))
-        if A > 1:
-            stages.append(lambda t, n: distributed_transpose_azimuth(t, (-1, -4), compute_split_shapes(n, A)))
+        stages = self._legendre_stages(-4, self.l_shapes, self.lat_shapes) + self._irfft_stages(-4)
         x = self._run_stages(x, stages)
         return unpad_and_unflatten_leading_dims(x, lead_shape, lead_size, num_trailing_dims=3)

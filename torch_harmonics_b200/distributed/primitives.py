@@ -172,6 +172,41 @@ def _transpose(x: torch.Tensor, dim0: int, dim1: int, dim1_split_sizes, group):
     return torch.view_as_complex(out) if is_complex else out
 
 
+def _pieces_exchange_in(x: torch.Tensor, split_sizes, group, axis: int = -1):
+    """First half of a transpose that scatters the LEADING axis and gathers ``axis``, stopped before the concatenation:
+    ``x`` (n, ..., local length of axis, ...) contiguous -> (flat real buffer, n_local) where the buffer holds, one after
+    the other, the blocks (n_local, ..., split_sizes[j], ...) received from the peers j ("piece-major": every block is a
+    contiguous tensor of its own).  No copy on either side."""
+    size, rank = dist.get_world_size(group), dist.get_rank(group)
+    xr = torch.view_as_real(x.resolve_conj()) if x.is_complex() else x
+    xr = xr.contiguous()
+    d0 = compute_split_shapes(x.shape[0], size)
+    per0 = xr.numel() // x.shape[0]
+    other = per0 // x.shape[axis]  # elements per (leading index, index of the gathered axis)
+    recv = _exchange(xr.reshape(-1), [c * per0 for c in d0], [d0[rank] * other * s for s in split_sizes], group)
+    return recv, d0[rank]
+
+
+def _pieces_exchange_out(buf: torch.Tensor, n_local: int, n_total: int, rest_shape, axis: int, split_sizes, is_complex: bool, group):
+    """Second half of a transpose that scatters ``axis`` and gathers the LEADING axis, started from a piece-major buffer:
+    ``buf`` holds the blocks (n_local, *rest_shape) with ``rest_shape[axis] = split_sizes[j]``; block j goes to peer j as it
+    lies, and what comes back is (n_total, *rest_shape) with ``rest_shape[axis] = split_sizes[rank]`` as it lies.  No copy
+    on either side.  ``axis`` counts inside ``rest_shape`` (the entry there is ignored)."""
+    size, rank = dist.get_world_size(group), dist.get_rank(group)
+    rest = list(rest_shape)
+    axis %= len(rest)
+    other = 2 if is_complex else 1
+    for i, s in enumerate(rest):
+        if i != axis:
+            other *= s
+    d0 = compute_split_shapes(n_total, size)
+    rest[axis] = split_sizes[rank]
+    recv = _exchange(buf.reshape(-1), [n_local * other * s for s in split_sizes], [c * other * rest[axis] for c in d0], group)
+    if is_complex:
+        return torch.view_as_complex(recv.view(n_total, *rest, 2))
+    return recv.view(n_total, *rest)
+
+
 class _Transpose(torch.autograd.Function):
     """The transposes move bytes and never compute, so they run on whatever dtype arrives; ``custom_fwd`` /
     ``custom_bwd`` make the backward exchange run under the autocast state the forward one saw

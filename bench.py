@@ -504,6 +504,7 @@ def spatial_record(dev, rank, world, engine, nfields, p_f, p_i):
     t_fwd, _ = timed_blocks(fwd, k, barrier, 0.2, 40, agree=allmax)
     t_inv, _ = timed_blocks(inv, k, barrier, 0.2, 40, agree=allmax)
     t_step, t_fwd, t_inv = allmax(t_step), allmax(t_fwd), allmax(t_inv)
+    was_pipelined = bool(dsht.last_pipelined or disht.last_pipelined)
     # all-to-all volume and time of one forward and one inverse call (unpipelined, so that the events bracket the exchanges only)
     chunks = dsht.pipeline_chunks
     dsht.pipeline_chunks = disht.pipeline_chunks = 0
@@ -540,7 +541,7 @@ def spatial_record(dev, rank, world, engine, nfields, p_f, p_i):
         "fwd_fields_per_s": nf * k / t_fwd, "inv_fields_per_s": nf * k / t_inv, "roundtrip_fields_per_s": nf * k / t_step,
         "fwd_ms": 1e3 * t_fwd / k, "inv_ms": 1e3 * t_inv / k, "roundtrip_ms": 1e3 * t_step / k,
         "fwd_ms_unpipelined": 1e3 * t_fwd_plain / k, "inv_ms_unpipelined": 1e3 * t_inv_plain / k,
-        "pipelined": bool(min(gh, gw) == 1 and chunks >= 2),
+        "pipelined": was_pipelined,
         "all_to_all_forward": af, "all_to_all_inverse": ai,
         "bound": {
             "t_local_hbm_ms": 1e3 * t_local, "t_nvlink_fwd_ms": 1e3 * t_link_f, "t_nvlink_inv_ms": 1e3 * t_link_i, "nvlink_gbs_per_direction": 900.0,

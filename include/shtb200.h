@@ -185,6 +185,13 @@ size_t shtb200_plan_table_bytes(const shtb200_plan *plan);
 int shtb200_rfft_modes(const float *in_dev, void *out_dev, long long nrows, int nlon, int nmodes, float scale, void *stream);
 int shtb200_irfft_modes(const void *in_dev, float *out_dev, long long nrows, int nlon, int nmodes, void *stream);
 /*
+ * Process-wide cap on the number of SMs the library's persistent kernels (FFT, Legendre contraction) size their grids for;
+ * 0 removes it.  Returns the previous value.  For callers that run NCCL collectives beside these kernels on other streams:
+ * a persistent kernel sized for the whole GPU leaves a collective's CTAs nowhere to run until it ends.  Takes effect at the
+ * next launch; results do not depend on it.
+ */
+int shtb200_set_sm_limit(int nsm);
+/*
  * The same two transforms on PIECE-MAJOR buffers, the form in which an all-to-all transpose receives / sends a tensor whose
  * last axis is gathered / scattered (torch_harmonics/distributed/primitives.py:227-289: the chunks of the split axis
  * travel as separate contiguous blocks): an axis of length n in P pieces is cut into balanced chunks (the first n % P one

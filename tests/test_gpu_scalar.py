@@ -266,6 +266,40 @@ def test_piece_major_row_transforms_unsupported_shapes():
     assert rc != 0 and "piece-major" in lib.shtb200_last_error().decode()
 
 
+def test_sm_limit_changes_grids_not_results():
+    """``shtb200_set_sm_limit`` caps the SMs the persistent kernels are sized for (room for collectives running beside
+    them); results are bit for bit those of the unlimited launch, and the setter returns the previous cap."""
+    import torch
+
+    from torch_harmonics_b200 import _lib
+
+    nlat, nlon = 91, 720
+    w, p, L, M = oracle_tables(nlat, nlon, 90, 90, "equiangular")
+    gen = torch.Generator(device="cuda").manual_seed(2)
+    x = torch.randn(40, nlat, nlon, device="cuda", generator=gen)
+    fwd, inv = make_plan(_lib.SHT, nlat, nlon, L, M, w, "auto"), make_plan(_lib.ISHT, nlat, nlon, L, M, p, "auto")
+
+    def roundtrip():
+        c = torch.empty(40, L, M, dtype=torch.complex64, device="cuda")
+        y = torch.empty_like(x)
+        ws = torch.empty(max(fwd.workspace_bytes(40), inv.workspace_bytes(40)), dtype=torch.uint8, device="cuda")
+        fwd.execute(x, c, 40, ws, 0)
+        inv.execute(c, y, 40, ws, 0)
+        torch.cuda.synchronize()
+        return c, y
+
+    assert _lib.set_sm_limit(0) == 0
+    c0, y0 = roundtrip()
+    try:
+        assert _lib.set_sm_limit(24) == 0
+        c1, y1 = roundtrip()
+        assert _lib.set_sm_limit(1) == 24
+        c2, y2 = roundtrip()
+    finally:
+        _lib.set_sm_limit(0)
+    assert torch.equal(c0, c1) and torch.equal(y0, y1) and torch.equal(c0, c2) and torch.equal(y0, y2)
+
+
 @pytest.mark.parametrize("pieces_in,pieces_out", [(2, 2), (3, 4), (1, 5), (4, 1)])
 def test_piece_major_legendre_stage(pieces_in, pieces_out):
     """The contraction stage on piece-major tensors (row axis in balanced chunks, chunk j its own contiguous

@@ -67,6 +67,8 @@ def load():
         lib.shtb200_rfft_modes.restype = ci
         lib.shtb200_irfft_modes.argtypes = [vp, vp, cll, ci, ci, vp]
         lib.shtb200_irfft_modes.restype = ci
+        lib.shtb200_set_sm_limit.argtypes = [ci]
+        lib.shtb200_set_sm_limit.restype = ci
         lib.shtb200_rows_pieces_supported.argtypes = [ci, ci, ci, ci]
         lib.shtb200_rows_pieces_supported.restype = ci
         lib.shtb200_rfft_modes_pieces.argtypes = [vp, vp, cll, ci, ci, ctypes.c_float, ci, ci, vp]
@@ -100,6 +102,11 @@ def dense(t):
     bits of a tensor that already is contiguous (``w.conj()``, ``z.conj().imag``), and the raw memory then holds the
     unconjugated values."""
     return t.contiguous().resolve_conj().resolve_neg()
+
+
+def set_sm_limit(nsm):
+    """Cap the SMs the persistent kernels size their grids for (0 = no cap); returns the previous cap."""
+    return load().shtb200_set_sm_limit(int(nsm))
 
 
 def rows_pieces_supported(nlon, nmodes, grid_pieces, mode_pieces):

@@ -5,6 +5,7 @@
 #include <string.h>
 
 #include <algorithm>
+#include <atomic>
 #include <mutex>
 
 #include "common.cuh"
@@ -199,6 +200,14 @@ int grow(void **p, size_t *have, size_t need) {
 }  // namespace shtb200
 
 using namespace shtb200;
+
+namespace shtb200 {
+static std::atomic<int> g_sm_limit{0};
+int effective_sms(int sm_count) {
+    const int lim = g_sm_limit.load(std::memory_order_relaxed);
+    return lim > 0 ? std::min(sm_count, lim) : sm_count;
+}
+}  // namespace shtb200
 
 extern "C" {
 
@@ -631,6 +640,11 @@ int shtb200_rfft_modes(const float *in_dev, void *out_dev, long long nrows, int 
     if (nrows == 0) return SHTB200_OK;
     if (!in_dev || !out_dev) return fail(SHTB200_EINVAL, "null pointer");
     return launch_rfft_modes(in_dev, reinterpret_cast<float2 *>(out_dev), nrows, nlon, nmodes, scale, 1, 1, (cudaStream_t)stream);
+}
+
+int shtb200_set_sm_limit(int nsm) {
+    const int before = g_sm_limit.exchange(nsm > 0 ? nsm : 0);
+    return before;
 }
 
 int shtb200_rows_pieces_supported(int nlon, int nmodes, int grid_pieces, int mode_pieces) { return rows_pieces_supported(nlon, nmodes, grid_pieces, mode_pieces) ? 1 : 0; }

@@ -196,6 +196,10 @@ int build_fft_plan(int nlon, int mmax_emit, int layout, const int *krow0, FftPla
 int launch_fft_analysis(const Plan &pl, const float *x, float *X, int nfields, cudaStream_t st);
 // synthesis: Y[blocked_row(group, k')][col] -> rows of x
 int launch_fft_synthesis(const Plan &pl, const float *Y, float *x, int nfields, cudaStream_t st);
+// Process-wide cap on the SMs the persistent kernels size their grids for (shtb200_set_sm_limit; 0 = none): a caller that
+// overlaps NCCL collectives with these kernels leaves the collective's CTAs somewhere to run.
+int effective_sms(int sm_count);
+
 // balanced split of n into P pieces (the first n % P one longer): the piece that holds index i -> (first index, width)
 __host__ __device__ __forceinline__ void piece_of(int i, int n, int P, int *start, int *width) {
     const int q = n / P, rem = n - q * P;

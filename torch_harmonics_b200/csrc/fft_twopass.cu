@@ -560,7 +560,7 @@ int launch_twopass(const Plan &pl, bool analysis, const float *in, float *out, i
     const size_t smem = sizeof(float) * kNT * TP::TS + (size_t)pl.tp_blob_bytes + 32;
     if (smem > 113 * 1024) return fail(SHTB200_EINVAL, "two-pass FFT tables do not fit two CTAs per SM");
     const int nitems = pl.Kh * ceil_div(nfields, kNT);
-    const int grid = std::min(2 * pl.sm_count, nitems);
+    const int grid = std::min(2 * effective_sms(pl.sm_count), nitems);
     if (analysis) {
         a.grid_in = in;
         a.op = out;
@@ -681,7 +681,7 @@ static int launch_rows(const TwoPassRows &tr, bool forward, const void *in, void
     const size_t smem = sizeof(float) * kNT * TP::TS + (size_t)tr.blob_bytes + 32;
     const long long nitems = (nrows + 15) / 16;
     if (nitems > 0x7fffffffLL) return fail(SHTB200_EINVAL, "too many rows");
-    const int grid = (int)std::min<long long>(2LL * tr.sm_count, nitems);
+    const int grid = (int)std::min<long long>(2LL * effective_sms(tr.sm_count), nitems);
     if (forward) {
         a.grid_in = static_cast<const float *>(in);
         a.rows_out = static_cast<float2 *>(out);

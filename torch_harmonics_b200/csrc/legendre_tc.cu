@@ -431,7 +431,7 @@ int launch_gemm_tc(const Plan &pl, const GemmParams &gp, cudaStream_t st) {
     // The opt-in to large dynamic shared memory is a per-device attribute of the kernel: set it for the current device
     // (the plan's, made current by the caller) on every launch; the SM count is the plan's device's as well.
     SHT_CUDA_CHECK(cudaFuncSetAttribute(legendre_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    const int sm_count = pl.sm_count;
+    const int sm_count = effective_sms(pl.sm_count);
     TcParams P{};
     P.gp = gp;
     P.bn = std::min<int>(BN_MAX, (int)round_up(gp.ncols, 16));

@@ -255,6 +255,7 @@ class _DistributedBase(nn.Module):
     # Number of field chunks the inference path pipelines (0 / 1 switches it off) and the smallest local tensor worth it.
     pipeline_chunks = 4
     pipeline_min_bytes = 64 << 20
+    last_pipelined = False  # whether the last forward call ran in chunks
 
     fuse_azimuth_fft = True  # exchange - row FFT - exchange without copies in between, where the row kernels support it
 
@@ -309,15 +310,21 @@ class _DistributedBase(nn.Module):
         by stage on streams of their own: NCCL executes the all-to-alls in issue order (chunk 0, chunk 1, ... of one
         stage), while the FFT / Legendre kernels of a chunk run on its stream next to the other chunks' exchanges.
         Only grids with ONE distributed axis are pipelined: with two communicators the exchanges of different chunks would
-        sit on two NCCL streams whose relative order is not the same on every rank."""
+        sit on two NCCL streams whose relative order is not the same on every rank.  And only stage lists that still hold
+        separate transposes: what the pipeline hides are their copies; once the exchanges are fused with the kernels
+        around them (two stages left) nothing remains to hide - the persistent FFT / Legendre kernels fill the GPU, an
+        all-to-all does not run beside them (measured at 1 x 2, 2 048 fields: 18.9 / 18.4 ms plain, 19.5 / 20.4 ms in four
+        chunks, no better with 8 to 48 SMs held back for NCCL)."""
         n = x.shape[0]
         gmax = max(self.comm_size_polar, self.comm_size_azimuth)
         nchunks = min(self.pipeline_chunks, n // max(gmax, 1))
-        if (gmax == 1 or min(self.comm_size_polar, self.comm_size_azimuth) > 1 or nchunks < 2 or torch.is_grad_enabled() and x.requires_grad or not x.is_cuda
+        if (gmax == 1 or min(self.comm_size_polar, self.comm_size_azimuth) > 1 or nchunks < 2 or len(stages) < 3 or torch.is_grad_enabled() and x.requires_grad or not x.is_cuda
                 or x.numel() * x.element_size() < self.pipeline_min_bytes):
+            self.last_pipelined = False
             for st in stages:
                 x = st(x, n)
             return x
+        self.last_pipelined = True
         main = torch.cuda.current_stream(x.device)
         if not hasattr(self, "_streams") or len(self._streams) < nchunks or self._streams[0].device != x.device:
             self._streams = [torch.cuda.Stream(device=x.device) for _ in range(nchunks)]

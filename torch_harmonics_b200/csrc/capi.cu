@@ -385,6 +385,24 @@ static int plan_create_impl(shtb200_plan **plan_out, int kind, int nlat, int nlo
         shtb200_plan_destroy(pl);
         return rc;
     }
+    if (pl->analysis && !pl->vector && !pl->window) {  // degree classes of the slabs (see Plan::d_cls_off)
+        std::vector<std::vector<int>> cls(pl->lmax);
+        for (int g = 0; g < ngroups; ++g)
+            for (int rb = 0; rb < pl->group_kblocks[g]; ++rb) {
+                const int l0 = (g >> 1) + (g & 1) + 2 * kBK * rb;  // (< lmax: a slab exists only for a degree below lmax)
+                cls[l0].push_back((int)(pl->group_b0[g] + rb));
+            }
+        std::vector<int> off(pl->lmax + 1, 0), slabs;
+        for (int l0 = 0; l0 < pl->lmax; ++l0) {
+            slabs.insert(slabs.end(), cls[l0].begin(), cls[l0].end());
+            off[l0 + 1] = (int)slabs.size();
+        }
+        if (slabs.empty()) slabs.push_back(0);
+        if ((rc = upload(&pl->d_cls_off, off)) || (rc = upload(&pl->d_cls_slab, slabs))) {
+            shtb200_plan_destroy(pl);
+            return rc;
+        }
+    }
     if (cudaMalloc(&pl->d_err, sizeof(int)) != cudaSuccess || cudaMemset(pl->d_err, 0, sizeof(int)) != cudaSuccess) {
         shtb200_plan_destroy(pl);
         return fail(SHTB200_ECUDA, "error word allocation failed");
@@ -422,6 +440,8 @@ int shtb200_plan_destroy(shtb200_plan *pl) {
     cudaFree(pl->d_grows);
     cudaFree(pl->d_gkb);
     cudaFree(pl->d_gkb0);
+    cudaFree(pl->d_cls_off);
+    cudaFree(pl->d_cls_slab);
     if (pl->copy_in) cudaStreamDestroy(pl->copy_in);
     if (pl->copy_out) cudaStreamDestroy(pl->copy_out);
     for (cudaEvent_t e : pl->ev_up) cudaEventDestroy(e);

@@ -162,6 +162,10 @@ struct Plan {
     long long *d_ga0 = nullptr, *d_gb0 = nullptr;
     int *d_grows = nullptr, *d_gkb = nullptr, *d_gkb0 = nullptr;
     int negate_seg1 = 0;              // vector adjoints: the m/sin(theta) table enters with the opposite sign
+    // scalar analysis plans: degree classes of the slabs.  Lane i of slab (g = 2 m + p, rb) holds degree m + p + 64 rb + 2 i,
+    // so all slabs with the same l0 = m + p + 64 rb carry the same 32 degrees; class l0 lists them
+    // (d_cls_slab[d_cls_off[l0] .. d_cls_off[l0 + 1])).  A kernel that applies per-degree weights loads them once per class.
+    int *d_cls_off = nullptr, *d_cls_slab = nullptr;
 
     // host-call staging
     void *stage_in = nullptr, *stage_out = nullptr, *stage_ws = nullptr;

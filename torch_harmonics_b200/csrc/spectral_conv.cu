@@ -112,6 +112,90 @@ __global__ void __launch_bounds__(32 * kMixWarps) slab_mix_kernel(const MixArgs 
     }
 }
 
+// The same mixing, register-tiled.  All slabs of one degree class (Plan::d_cls_off) carry the same 32 degrees in their 32
+// lanes, so for a lane the class is ONE small complex matrix product  out[co][n] = sum_ci W[ci][co][l] in[ci][n]  over
+// the columns n = (slab of the class, batch entry).  A thread (lane = degree) keeps a kTileCo x kTileN block of it in
+// registers: every weight it loads serves kTileN columns, every coefficient kTileCo output channels (the kernel above
+// reloads the weights for every slab).  Eight warps of a CTA: four along the output channels, two along the columns.
+// (Eight output channels per thread were measured slower: 158 registers, one CTA per SM.)
+constexpr int kTileCo = 4, kTileN = 4, kWarpsCo = 4, kWarpsN = 2;
+
+struct TiledMixArgs {
+    const float *Zin;
+    float *Zout;
+    const float2 *Wp;
+    const int *cls_off, *cls_slab;
+    int B, Cin, Cout, G, Lh2, lmax;
+};
+
+// grid: (degree classes l0, channel groups x tiles of 16 output channels); block: 8 warps
+__global__ void __launch_bounds__(32 * kWarpsCo * kWarpsN) slab_mix_tiled_kernel(const TiledMixArgs a) {
+    const int l0 = blockIdx.x;
+    const int s_begin = a.cls_off[l0], nslab = a.cls_off[l0 + 1] - s_begin;
+    const int ncol = nslab * a.B;
+    if (ncol == 0) return;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int wc = warp % kWarpsCo, wn = warp / kWarpsCo;
+    const int l = l0 + 2 * lane;
+    const bool valid = l < a.lmax;  // lanes beyond the last degree pad the slab: zeros
+    const int par = l0 & 1, h = (l0 >> 1) + lane;
+    const int Cig = a.Cin / a.G, Cog = a.Cout / a.G;
+    const int tiles = (Cog + kTileCo * kWarpsCo - 1) / (kTileCo * kWarpsCo);
+    const int cg = blockIdx.y / tiles;
+    const int co0 = (blockIdx.y % tiles) * (kTileCo * kWarpsCo) + wc * kTileCo;  // first output channel (inside the group) of this thread
+    if (co0 >= Cog) return;
+    const long long ncols_in = 2LL * a.B * a.Cin, ncols_out = 2LL * a.B * a.Cout;
+    const float2 *wbase = a.Wp + (((long long)par * a.G + cg) * Cig * Cog + co0) * a.Lh2 + h;
+    const long long wstep = (long long)Cog * a.Lh2;  // from one input channel to the next
+
+    for (int n0 = wn * kTileN; n0 < ncol; n0 += kTileN * kWarpsN) {
+        const float *in[kTileN];
+        float *out[kTileN];
+#pragma unroll
+        for (int t = 0; t < kTileN; ++t) {
+            const int n = min(n0 + t, ncol - 1);  // (columns beyond the class repeat the last one; they are not stored)
+            const int slab = a.cls_slab[s_begin + n / a.B], b = n % a.B;
+            in[t] = a.Zin + ((long long)slab * ncols_in + 2LL * ((long long)b * a.Cin + (long long)cg * Cig)) * kBK + lane;
+            out[t] = a.Zout + ((long long)slab * ncols_out + 2LL * ((long long)b * a.Cout + (long long)cg * Cog + co0)) * kBK + lane;
+        }
+        float2 acc[kTileCo][kTileN];
+#pragma unroll
+        for (int j = 0; j < kTileCo; ++j)
+#pragma unroll
+            for (int t = 0; t < kTileN; ++t) acc[j][t] = make_float2(0.f, 0.f);
+        if (valid) {
+            const float2 *w = wbase;
+#pragma unroll 2
+            for (int ci = 0; ci < Cig; ++ci) {
+                float2 ww[kTileCo], u[kTileN];
+#pragma unroll
+                for (int j = 0; j < kTileCo; ++j) ww[j] = (co0 + j < Cog) ? __ldg(w + (long long)j * a.Lh2) : make_float2(0.f, 0.f);
+#pragma unroll
+                for (int t = 0; t < kTileN; ++t) u[t] = make_float2(__ldg(in[t] + (2 * ci) * kBK), __ldg(in[t] + (2 * ci + 1) * kBK));
+#pragma unroll
+                for (int j = 0; j < kTileCo; ++j)
+#pragma unroll
+                    for (int t = 0; t < kTileN; ++t) {
+                        acc[j][t].x = fmaf(ww[j].x, u[t].x, fmaf(-ww[j].y, u[t].y, acc[j][t].x));
+                        acc[j][t].y = fmaf(ww[j].x, u[t].y, fmaf(ww[j].y, u[t].x, acc[j][t].y));
+                    }
+                w += wstep;
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < kTileN; ++t) {
+            if (n0 + t >= ncol) continue;
+#pragma unroll
+            for (int j = 0; j < kTileCo; ++j) {
+                if (co0 + j < Cog) {
+                    out[t][(2 * j) * kBK] = acc[j][t].x;      // (zeros when !valid)
+                    out[t][(2 * j + 1) * kBK] = acc[j][t].y;
+                }
+            }
+        }
+    }
+}
+
 }  // namespace
 
 size_t slab_mix_weight_bytes(int cin, int cout, int ngroups, int lmax) {
@@ -126,6 +210,28 @@ int launch_slab_mix(const Plan &pl, const float *Zin, float *Zout, const float2 
     const long long total = 2 * nrows * Lh2;
     split_weights_kernel<<<(unsigned)std::min<long long>((total + 255) / 256, 8192), 256, 0, st>>>(weight, wsplit, nrows, pl.lmax, Lh2);
     SHT_CUDA_CHECK(cudaGetLastError());
+#ifndef SHTB200_MIX_UNTILED  // build-time switch for A/B measurements against the slab-by-slab kernel below
+    if (pl.d_cls_off) {
+        TiledMixArgs t{};
+        t.Zin = Zin;
+        t.Zout = Zout;
+        t.Wp = wsplit;
+        t.cls_off = pl.d_cls_off;
+        t.cls_slab = pl.d_cls_slab;
+        t.B = batch;
+        t.Cin = cin;
+        t.Cout = cout;
+        t.G = ngroups;
+        t.Lh2 = Lh2;
+        t.lmax = pl.lmax;
+        const int tiles = ngroups * ceil_div(cout / ngroups, kTileCo * kWarpsCo);
+        if (tiles > 65535) return fail(SHTB200_EINVAL, "too many output channels for one spectral-convolution call");
+        dim3 grid((unsigned)pl.lmax, (unsigned)tiles);
+        slab_mix_tiled_kernel<<<grid, 32 * kWarpsCo * kWarpsN, 0, st>>>(t);
+        SHT_CUDA_CHECK(cudaGetLastError());
+        return SHTB200_OK;
+    }
+#endif
     MixArgs a{};
     a.Zin = Zin;
     a.Zout = Zout;

@@ -566,6 +566,19 @@ def run_ours(args):
         # a short collective timeout: a rank that falls out of step ends the run within minutes instead of holding the GPUs
         dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=240))
 
+    if args.record:
+        # one of the side records alone (the small, reproducible command the profile summaries of these workloads name);
+        # prints that record, not the headline line
+        if world > 1:
+            raise SystemExit("--record is a single-GPU option")
+
+        def barrier1():
+            torch.cuda.synchronize()
+
+        rec = spectral_conv_record(dev, args.engine, barrier1) if args.record == "spectral_conv" else config_record(dev, args.record, args.engine, barrier1)
+        print(json.dumps({"record": args.record, **rec}), flush=True)
+        return
+
     nf = args.nfields
     torch.cuda.synchronize()
     t0 = time.perf_counter()
@@ -882,6 +895,7 @@ if __name__ == "__main__":
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--quick", action="store_true", help="headline, e2e and roofline only: skip the incumbent and the other workloads")
     ap.add_argument("--no-spatial", action="store_true", help="N > 1: skip the spatially distributed transforms")
+    ap.add_argument("--record", default=None, choices=["cfg2", "cfg4", "cfg5_one_gpu", "spectral_conv"], help="run one side record alone and print it")
     ap.add_argument("--spatial-fields", type=int, default=2048, help="global batch of the spatially distributed run")
     a = ap.parse_args()
     if a.impl == "reference":

@@ -84,9 +84,55 @@ def exchange_log_stop():
     return [(s, r, e0.elapsed_time(e1)) for s, r, e0, e1 in log]
 
 
+_SIDE_STREAMS = {}
+
+
+def _exchange_split(send, send_counts, recv_counts, recv, group):
+    """The rank's own block as a device copy on a side stream, the other ranks' blocks as one group of NCCL sends and
+    receives: the collective's kernel moves remote bytes only, and the local copy runs beside it at memory speed."""
+    me, size = dist.get_rank(group), dist.get_world_size(group)
+    ranks = dist.get_process_group_ranks(group)
+    soff, roff = [0], [0]
+    for a, b in zip(send_counts, recv_counts):
+        soff.append(soff[-1] + a)
+        roff.append(roff[-1] + b)
+    cur = torch.cuda.current_stream(send.device)
+    side = _SIDE_STREAMS.get(send.device)
+    if side is None:
+        side = _SIDE_STREAMS[send.device] = torch.cuda.Stream(device=send.device)
+    side.wait_stream(cur)
+    with torch.cuda.stream(side):
+        recv[roff[me]:roff[me + 1]].copy_(send[soff[me]:soff[me + 1]])
+    send.record_stream(side)
+    recv.record_stream(side)
+    ops = []
+    for peer in range(size):
+        if peer == me:
+            continue
+        if send_counts[peer]:
+            ops.append(dist.P2POp(dist.isend, send[soff[peer]:soff[peer + 1]], ranks[peer], group))
+        if recv_counts[peer]:
+            ops.append(dist.P2POp(dist.irecv, recv[roff[peer]:roff[peer + 1]], ranks[peer], group))
+    if ops:
+        for req in dist.batch_isend_irecv(ops):
+            req.wait()
+    cur.wait_stream(side)
+
+
 def _exchange(send: torch.Tensor, send_counts, recv_counts, group):
     """Flat all-to-all with per-peer element counts."""
     recv = send.new_empty(sum(recv_counts))
+    if dist.get_backend(group) == "nccl" and config.exchange == "split":
+        if _EXCHANGE_LOG is not None:
+            me = dist.get_rank(group)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+        _exchange_split(send, send_counts, recv_counts, recv, group)
+        if _EXCHANGE_LOG is not None:
+            e1.record()
+            es = send.element_size()
+            _EXCHANGE_LOG.append(((sum(send_counts) - send_counts[me]) * es, (sum(recv_counts) - recv_counts[me]) * es, e0, e1))
+        return recv
     if dist.get_backend(group) == "nccl":
         if _EXCHANGE_LOG is not None:
             me = dist.get_rank(group)

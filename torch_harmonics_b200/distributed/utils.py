@@ -20,6 +20,11 @@ class _DistributedConfig:
 
     def __init__(self):
         self._debug = None
+        # NCCL exchanges: "split" = the rank's own block is a plain device copy on a side stream and only the other ranks'
+        # blocks go through NCCL (one group of sends / receives); "single" = one all_to_all_single including the own block.
+        # Inside the collective's kernel the own block moves at a fraction of memory speed and delays the remote ones:
+        # 5.0 ms against 3.6 - 4.0 ms per exchange of 2 x 2.1 GB between two ranks.
+        self.exchange = "split"
 
     @property
     def debug(self):
@@ -32,7 +37,7 @@ class _DistributedConfig:
         self._debug = bool(value)
 
     def __repr__(self):
-        return f"_DistributedConfig(debug={self.debug})"
+        return f"_DistributedConfig(debug={self.debug}, exchange={self.exchange!r})"
 
 
 config = _DistributedConfig()

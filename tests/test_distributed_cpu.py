@@ -107,6 +107,48 @@ def _worker(rank, world, port, which):
     dist.destroy_process_group()
 
 
+def _pieces_worker(rank, world, port):
+    """The two halves of a copy-free transpose (piece-major buffers) against slices of the full tensor."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import torch_harmonics_b200.distributed as thd
+    from torch_harmonics_b200.distributed.primitives import _pieces_exchange_in, _pieces_exchange_out
+
+    group = dist.new_group(list(range(world)))
+    for shape, axis, dtype in (((9, 5, 14), -1, torch.float32), ((world, 3, 10), -1, torch.complex64), ((7, 2, 11, 6), -2, torch.complex64), ((6, 13, 4), -2, torch.float32)):
+        g = torch.Generator().manual_seed(3)
+        full_in = torch.randn(shape, generator=g, dtype=torch.float64).to(torch.float32)
+        full_out = torch.randn(shape, generator=g, dtype=torch.float64).to(torch.float32)
+        if dtype.is_complex:
+            full_in = torch.complex(full_in, torch.randn(shape, generator=g))
+            full_out = torch.complex(full_out, torch.randn(shape, generator=g))
+        ax = axis % len(shape)
+        n_splits = thd.compute_split_shapes(shape[0], world)
+        a_splits = thd.compute_split_shapes(shape[ax], world)
+        n0 = sum(n_splits[:rank])
+        mine = slice(n0, n0 + n_splits[rank])
+
+        def flat(t):
+            return (torch.view_as_real(t.contiguous()) if t.is_complex() else t.contiguous()).reshape(-1)
+
+        # in: every rank holds all fields and its chunk of `axis`; afterwards its fields, the axis in pieces
+        x_local = thd.split_tensor_along_dim(full_in, ax, world)[rank].contiguous()
+        buf, n_loc = _pieces_exchange_in(x_local, a_splits, group, axis=axis)
+        expect = torch.cat([flat(c) for c in torch.split(full_in[mine], a_splits, dim=ax)])
+        assert n_loc == n_splits[rank] and torch.equal(buf, expect), (shape, axis)
+        # out: every rank holds its fields with the axis in pieces; afterwards all fields and its chunk of the axis
+        pieces = torch.cat([flat(c) for c in torch.split(full_out[mine], a_splits, dim=ax)])
+        out = _pieces_exchange_out(pieces, n_loc, shape[0], shape[1:], ax - 1, a_splits, dtype.is_complex, group)
+        assert torch.equal(out, thd.split_tensor_along_dim(full_out, ax, world)[rank]), (shape, axis)
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3, 4])
+def test_piece_major_exchanges(world):
+    mp.spawn(_pieces_worker, args=(world, _free_port()), nprocs=world, join=True)
+
+
 @pytest.mark.parametrize("which", ["azimuth", "polar"])
 def test_transposes_two_ranks(which):
     mp.spawn(_worker, args=(2, _free_port(), which), nprocs=2, join=True)

@@ -122,7 +122,7 @@ def _exchange_split(send, send_counts, recv_counts, recv, group):
 def _exchange(send: torch.Tensor, send_counts, recv_counts, group):
     """Flat all-to-all with per-peer element counts."""
     recv = send.new_empty(sum(recv_counts))
-    if dist.get_backend(group) == "nccl" and config.exchange == "split":
+    if dist.get_backend(group) == "nccl" and config.exchange == "split" and dist.get_world_size(group) <= config.split_max_group:
         if _EXCHANGE_LOG is not None:
             me = dist.get_rank(group)
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

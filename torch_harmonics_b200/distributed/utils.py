@@ -25,6 +25,9 @@ class _DistributedConfig:
         # Inside the collective's kernel the own block moves at a fraction of memory speed and delays the remote ones:
         # 5.0 ms against 3.6 - 4.0 ms per exchange of 2 x 2.1 GB between two ranks.
         self.exchange = "split"
+        # "split" is applied to groups of up to this many ranks (measured and tested on groups of two, where the own block
+        # is half of the data; in larger groups it is a quarter or less and the exchange stays one all_to_all_single)
+        self.split_max_group = 2
 
     @property
     def debug(self):
